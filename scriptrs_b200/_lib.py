@@ -1,0 +1,95 @@
+"""ctypes loader for libscriptrs_b200.so (the C ABI declared in include/scriptrs_b200.h).
+
+There is no CPU fallback: if the shared library is missing this module raises,
+and creating a context without a B200 fails with SB_UNSUPPORTED_PLATFORM.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libscriptrs_b200.so")
+
+SB_OK = 0
+STATUS_NAMES = {
+    0: "SB_OK", 1: "SB_EMPTY_AUDIO", 2: "SB_AUDIO_TOO_LONG", 3: "SB_MISSING_MODEL_ASSET", 4: "SB_IO",
+    5: "SB_INVALID_VOCABULARY", 6: "SB_INVALID_MODEL_OUTPUT", 7: "SB_BACKEND", 8: "SB_UNSUPPORTED_PLATFORM",
+    9: "SB_CUDA_ERROR", 10: "SB_TIMEOUT", 11: "SB_INVALID_ARGUMENT", 12: "SB_BUFFER_TOO_SMALL",
+}
+
+
+class TranscriptionConfigC(C.Structure):
+    _fields_ = [("sample_rate", C.c_int64), ("feature_size", C.c_int64), ("n_fft", C.c_int64),
+                ("win_length", C.c_int64), ("hop_length", C.c_int64), ("preemphasis", C.c_float),
+                ("max_audio_samples", C.c_int64), ("samples_per_encoder_frame", C.c_int64)]
+
+
+class OverlapConfigC(C.Structure):
+    _fields_ = [("overlap_seconds", C.c_double), ("context_samples", C.c_int64), ("max_model_samples", C.c_int64)]
+
+
+class LongFormConfigC(C.Structure):
+    _fields_ = [("mode", C.c_int32), ("worker_count", C.c_int64), ("transcription", TranscriptionConfigC),
+                ("overlap", OverlapConfigC)]
+
+
+class ChunkTaskC(C.Structure):
+    _fields_ = [("audio_start", C.c_int64), ("audio_end", C.c_int64), ("global_sample_offset", C.c_int64),
+                ("context_samples", C.c_int64)]
+
+
+_lib = None
+
+_VP = C.c_void_p
+_I64 = C.c_int64
+_I32 = C.c_int32
+
+# name -> (restype, argtypes); one entry per symbol declared in include/scriptrs_b200.h
+SIGNATURES = {
+    "sb_last_error": (C.c_char_p, []),
+    "sb_status_string": (C.c_char_p, [_I32]),
+    "sb_default_transcription_config": (None, [C.POINTER(TranscriptionConfigC)]),
+    "sb_default_overlap_config": (None, [C.POINTER(OverlapConfigC)]),
+    "sb_default_longform_config": (None, [C.POINTER(LongFormConfigC)]),
+    "sb_ctx_create": (_I32, [_I32, C.POINTER(_VP)]),
+    "sb_ctx_destroy": (None, [_VP]),
+    "sb_ctx_set_stream": (_I32, [_VP, _VP]),
+    "sb_ctx_synchronize": (_I32, [_VP]),
+    "sb_ctx_kernel_launches": (_I64, [_VP]),
+    "sb_frontend_tables": (_I32, [_VP, _VP]),
+    "sb_frontend_num_frames": (_I64, [_I64]),
+    "sb_frontend_device": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
+    "sb_frontend_host": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
+}
+
+
+class ScriptrsError(RuntimeError):
+    """Mirror of the reference's TranscriptionError (src/error.rs): `.status` is the sb_status code."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+        self.message = message
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m scriptrs_b200.build` "
+                "(there is no CPU fallback for the CUDA path)")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status: int):
+    if status != SB_OK:
+        msg = lib().sb_last_error().decode("utf-8", "replace")
+        raise ScriptrsError(status, msg)

@@ -1,0 +1,234 @@
+// extern "C" layer: context management and the frontend entry points.
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "context.h"
+
+namespace sb {
+
+static thread_local std::string g_last_error;
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+
+int32_t fail(sb_status st, const std::string& msg) {
+    g_last_error = msg;
+    return static_cast<int32_t>(st);
+}
+
+int32_t cuda_fail(cudaError_t e, const char* what) {
+    g_last_error = std::string("CUDA error: ") + cudaGetErrorString(e) + " at " + what;
+    return SB_CUDA_ERROR;
+}
+
+cudaError_t Buffer::ensure(size_t bytes) {
+    if (bytes <= cap) return cudaSuccess;
+    if (p) {
+        cudaError_t e = pinned_host ? cudaFreeHost(p) : cudaFree(p);
+        p = nullptr;
+        cap = 0;
+        if (e != cudaSuccess) return e;
+    }
+    size_t want = bytes + bytes / 8 + 256;
+    cudaError_t e = pinned_host ? cudaMallocHost(&p, want) : cudaMalloc(&p, want);
+    if (e == cudaSuccess) cap = want;
+    return e;
+}
+
+void Buffer::release() {
+    if (p) {
+        if (pinned_host) cudaFreeHost(p);
+        else cudaFree(p);
+    }
+    p = nullptr;
+    cap = 0;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+void sb_model_free_internal(sb_ctx*);
+
+extern "C" {
+
+const char* sb_last_error(void) { return g_last_error.c_str(); }
+
+const char* sb_status_string(int32_t status) {
+    switch (status) {
+        case SB_OK: return "ok";
+        case SB_EMPTY_AUDIO: return "audio input was empty";
+        case SB_AUDIO_TOO_LONG: return "audio exceeds the single-chunk limit";
+        case SB_MISSING_MODEL_ASSET: return "missing model asset";
+        case SB_IO: return "i/o error";
+        case SB_INVALID_VOCABULARY: return "invalid vocabulary";
+        case SB_INVALID_MODEL_OUTPUT: return "invalid model output";
+        case SB_BACKEND: return "backend failure";
+        case SB_UNSUPPORTED_PLATFORM: return "unsupported platform";
+        case SB_CUDA_ERROR: return "CUDA error";
+        case SB_TIMEOUT: return "device-side wait timed out";
+        case SB_INVALID_ARGUMENT: return "invalid argument";
+        case SB_BUFFER_TOO_SMALL: return "buffer too small";
+        default: return "unknown status";
+    }
+}
+
+void sb_default_transcription_config(sb_transcription_config* c) {
+    c->sample_rate = 16000;
+    c->feature_size = 128;
+    c->n_fft = 512;
+    c->win_length = 400;
+    c->hop_length = 160;
+    c->preemphasis = 0.97f;
+    c->max_audio_samples = 240000;
+    c->samples_per_encoder_frame = 1280;
+}
+
+void sb_default_overlap_config(sb_overlap_config* c) {
+    c->overlap_seconds = 2.0;
+    c->context_samples = 1280;
+    c->max_model_samples = 240000;
+}
+
+void sb_default_longform_config(sb_longform_config* c) {
+    c->mode = 0;
+    c->worker_count = 4;
+    sb_default_transcription_config(&c->transcription);
+    sb_default_overlap_config(&c->overlap);
+}
+
+int32_t sb_ctx_create(int32_t device, sb_ctx** out) {
+    if (!out) return fail(SB_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return fail(SB_UNSUPPORTED_PLATFORM, "no CUDA device: this library has no CPU fallback");
+    if (device < 0 || device >= count) return fail(SB_INVALID_ARGUMENT, "device index out of range");
+    SB_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    SB_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return fail(SB_UNSUPPORTED_PLATFORM, "kernels are built for sm_100a only");
+    sb_ctx* c = new sb_ctx();
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    c->pcm_stage.pinned_host = false;
+    SB_CUDA(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
+    c->stream = c->own_stream;
+    FrontendTables host_tables;
+    if (!build_frontend_tables(&host_tables, nullptr)) {
+        delete c;
+        return fail(SB_INVALID_MODEL_OUTPUT, "mel filterbank rows exceed the tap budget");
+    }
+    SB_CUDA(cudaMalloc(&c->d_tables, sizeof(FrontendTables)));
+    SB_CUDA(cudaMemcpy(c->d_tables, &host_tables, sizeof(FrontendTables), cudaMemcpyHostToDevice));
+    SB_CUDA(frontend_configure());
+    *out = c;
+    return SB_OK;
+}
+
+void sb_ctx_destroy(sb_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    sb_model_free_internal(c);
+    c->clip_off.release();
+    c->frame_off.release();
+    c->col_mean.release();
+    c->col_std.release();
+    c->pcm_stage.release();
+    c->feat_stage.release();
+    if (c->d_tables) cudaFree(c->d_tables);
+    if (c->own_stream) cudaStreamDestroy(c->own_stream);
+    delete c;
+}
+
+int32_t sb_ctx_set_stream(sb_ctx* c, void* stream) {
+    if (!c) return fail(SB_INVALID_ARGUMENT, "ctx is null");
+    c->stream = stream ? static_cast<cudaStream_t>(stream) : c->own_stream;
+    return SB_OK;
+}
+
+int32_t sb_ctx_synchronize(sb_ctx* c) {
+    if (!c) return fail(SB_INVALID_ARGUMENT, "ctx is null");
+    SB_CUDA(cudaSetDevice(c->device));
+    SB_CUDA(cudaStreamSynchronize(c->stream));
+    return SB_OK;
+}
+
+int64_t sb_ctx_kernel_launches(const sb_ctx* c) { return c ? c->launches : 0; }
+
+int32_t sb_frontend_tables(float* window, float* filterbank) {
+    if (window) hann_window_host(window, kWin);
+    if (filterbank) mel_filterbank_host(filterbank, kNfft, kMels, kSampleRate);
+    return SB_OK;
+}
+
+int64_t sb_frontend_num_frames(int64_t n_samples) { return n_samples <= 0 ? 0 : frames_for_samples(n_samples); }
+
+int32_t sb_frontend_device(sb_ctx* c, const float* d_pcm, const int64_t* clip_offsets, int64_t n_clips,
+                           float preemphasis, int32_t normalize, float* d_feats, int64_t* frame_offsets) {
+    if (!c || !clip_offsets || !d_pcm || !d_feats) return fail(SB_INVALID_ARGUMENT, "null argument");
+    if (n_clips <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");
+    if (n_clips > 65535) return fail(SB_INVALID_ARGUMENT, "at most 65535 clips per call");
+    std::vector<int64_t> fo(static_cast<size_t>(n_clips) + 1);
+    fo[0] = 0;
+    int64_t max_frames = 0;
+    for (int64_t i = 0; i < n_clips; ++i) {
+        const int64_t n = clip_offsets[i + 1] - clip_offsets[i];
+        if (n <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // frontend.rs:105
+        const int64_t t = frames_for_samples(n);
+        fo[i + 1] = fo[i] + t;
+        if (t > max_frames) max_frames = t;
+    }
+    if (max_frames > (int64_t)65535 * 32) return fail(SB_INVALID_ARGUMENT, "clip too long for one launch");
+    if (frame_offsets) std::memcpy(frame_offsets, fo.data(), sizeof(int64_t) * fo.size());
+    SB_CUDA(cudaSetDevice(c->device));
+    const size_t off_bytes = sizeof(int64_t) * (static_cast<size_t>(n_clips) + 1);
+    SB_CUDA(c->clip_off.ensure(off_bytes));
+    SB_CUDA(c->frame_off.ensure(off_bytes));
+    SB_CUDA(c->col_mean.ensure(sizeof(float) * kMels * static_cast<size_t>(n_clips)));
+    SB_CUDA(c->col_std.ensure(sizeof(float) * kMels * static_cast<size_t>(n_clips)));
+    SB_CUDA(cudaMemcpyAsync(c->clip_off.p, clip_offsets, off_bytes, cudaMemcpyHostToDevice, c->stream));
+    SB_CUDA(cudaMemcpyAsync(c->frame_off.p, fo.data(), off_bytes, cudaMemcpyHostToDevice, c->stream));
+    // The offset vectors are pageable host memory: the copies above have staged them
+    // before returning, so the call stays asynchronous on the context's stream.
+    SB_CUDA(frontend_launch(d_pcm, c->clip_off.as<int64_t>(), c->frame_off.as<int64_t>(), (int)n_clips,
+                            (int)max_frames, preemphasis, c->d_tables, d_feats, c->col_mean.as<float>(),
+                            c->col_std.as<float>(), normalize != 0, c->stream));
+    c->launches += normalize ? 3 : 1;
+    return SB_OK;
+}
+
+int32_t sb_frontend_host(sb_ctx* c, const float* pcm, const int64_t* clip_offsets, int64_t n_clips,
+                         float preemphasis, int32_t normalize, float* feats, int64_t* frame_offsets) {
+    if (!c || !clip_offsets || !pcm || !feats) return fail(SB_INVALID_ARGUMENT, "null argument");
+    if (n_clips <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");
+    const int64_t base = clip_offsets[0];
+    const int64_t total = clip_offsets[n_clips] - base;
+    if (total <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");
+    int64_t frames = 0;
+    std::vector<int64_t> rel(static_cast<size_t>(n_clips) + 1);
+    for (int64_t i = 0; i <= n_clips; ++i) rel[i] = clip_offsets[i] - base;
+    for (int64_t i = 0; i < n_clips; ++i) {
+        const int64_t n = rel[i + 1] - rel[i];
+        if (n <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");
+        frames += frames_for_samples(n);
+    }
+    SB_CUDA(cudaSetDevice(c->device));
+    SB_CUDA(c->pcm_stage.ensure(sizeof(float) * static_cast<size_t>(total)));
+    SB_CUDA(c->feat_stage.ensure(sizeof(float) * kMels * static_cast<size_t>(frames)));
+    SB_CUDA(cudaMemcpyAsync(c->pcm_stage.p, pcm + base, sizeof(float) * static_cast<size_t>(total),
+                            cudaMemcpyHostToDevice, c->stream));
+    int32_t st = sb_frontend_device(c, c->pcm_stage.as<float>(), rel.data(), n_clips, preemphasis, normalize,
+                                    c->feat_stage.as<float>(), frame_offsets);
+    if (st != SB_OK) return st;
+    SB_CUDA(cudaMemcpyAsync(feats, c->feat_stage.p, sizeof(float) * kMels * static_cast<size_t>(frames),
+                            cudaMemcpyDeviceToHost, c->stream));
+    SB_CUDA(cudaStreamSynchronize(c->stream));
+    return SB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,49 @@
+// Per-GPU context: stream, constant tables, grow-only workspaces, error reporting.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/scriptrs_b200.h"
+#include "frontend.h"
+
+namespace sb {
+
+// Thread-local last-error message (sb_last_error()).
+void set_error(const std::string& msg);
+int32_t fail(sb_status st, const std::string& msg);
+int32_t cuda_fail(cudaError_t e, const char* what);
+
+#define SB_CUDA(expr)                                       \
+    do {                                                    \
+        cudaError_t _e = (expr);                            \
+        if (_e != cudaSuccess) return ::sb::cuda_fail(_e, #expr); \
+    } while (0)
+
+// Device (or pinned host) buffer that only ever grows.
+struct Buffer {
+    void* p = nullptr;
+    size_t cap = 0;
+    bool pinned_host = false;
+    cudaError_t ensure(size_t bytes);
+    void release();
+    template <typename T>
+    T* as() const { return static_cast<T*>(p); }
+};
+
+struct Model;  // encoder + predictor + joint weights (model.h)
+
+}  // namespace sb
+
+struct sb_ctx {
+    int device = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    int64_t launches = 0;
+    sb::FrontendTables* d_tables = nullptr;
+    // frontend workspaces
+    sb::Buffer clip_off, frame_off, col_mean, col_std, pcm_stage, feat_stage;
+    sb::Model* model = nullptr;
+};
