@@ -130,6 +130,21 @@ int32_t sb_frontend_device(sb_ctx* ctx, const float* d_pcm, const int64_t* clip_
 int32_t sb_frontend_host(sb_ctx* ctx, const float* pcm, const int64_t* clip_offsets, int64_t n_clips,
                          float preemphasis, int32_t normalize, float* feats, int64_t* frame_offsets);
 
+/* ------------------------------------------------------------------ GEMM */
+
+/* Tensor-core GEMM building block of the encoder: out = epilogue(A[M x K] * W[N x K]^T).
+ * No counterpart in the reference, whose encoder arithmetic is inside a CoreML blob
+ * (src/coreml.rs:75-135); exported so that the kernel can be tested and profiled alone.
+ *   d_a, d_w   device pointers, row-major bf16 (fp8 = 0) or e4m3 (fp8 = 1); W in nn.Linear layout
+ *   d_bias     [N] f32 or NULL;  d_row_scale [M] / d_col_scale [N] f32 or NULL (fp8 only)
+ *   act        0 none, 1 SiLU, 2 ReLU
+ *   out_mode   0: bf16 out = act(.)   1: f32 out = alpha * act(.)   2: f32 out += alpha * act(.)
+ * Requires N % 128 == 0 and K % 64 == 0 (bf16) or K % 128 == 0 (fp8).  Asynchronous on the
+ * context's stream; a device-side wait that ran out is reported by sb_ctx_synchronize. */
+int32_t sb_gemm(sb_ctx* ctx, const void* d_a, const void* d_w, const float* d_bias, const float* d_row_scale,
+                const float* d_col_scale, void* d_out, int64_t M, int64_t N, int64_t K, int32_t fp8, int32_t act,
+                int32_t out_mode, float alpha);
+
 #ifdef __cplusplus
 }
 #endif

@@ -61,6 +61,7 @@ SIGNATURES = {
     "sb_frontend_num_frames": (_I64, [_I64]),
     "sb_frontend_device": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
     "sb_frontend_host": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
+    "sb_gemm": (_I32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I64, _I64, _I32, _I32, _I32, C.c_float]),
 }
 
 

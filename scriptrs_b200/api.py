@@ -139,3 +139,11 @@ class ParakeetFeatureExtractor:
                                             float(self.config.preemphasis), int(normalize), C.c_void_p(d_feats),
                                             _ptr(fo)))
         return fo
+
+
+def gemm(ctx: Context, d_a: int, d_w: int, d_out: int, M: int, N: int, K: int, d_bias: int = 0, act: int = 0,
+         out_mode: int = 0, alpha: float = 1.0, fp8: bool = False, d_row_scale: int = 0, d_col_scale: int = 0):
+    """out = epilogue(A[M,K] @ W[N,K]^T) on the tcgen05 GEMM; device pointers; asynchronous."""
+    check(_lib.lib().sb_gemm(ctx.handle, C.c_void_p(d_a), C.c_void_p(d_w), C.c_void_p(d_bias or None),
+                             C.c_void_p(d_row_scale or None), C.c_void_p(d_col_scale or None), C.c_void_p(d_out),
+                             M, N, K, int(fp8), act, out_mode, float(alpha)))

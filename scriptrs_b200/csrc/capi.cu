@@ -6,6 +6,7 @@
 #include <vector>
 
 #include "context.h"
+#include "gemm.h"
 
 namespace sb {
 
@@ -125,6 +126,11 @@ int32_t sb_ctx_create(int32_t device, sb_ctx** out) {
     SB_CUDA(cudaMalloc(&c->d_tables, sizeof(FrontendTables)));
     SB_CUDA(cudaMemcpy(c->d_tables, &host_tables, sizeof(FrontendTables), cudaMemcpyHostToDevice));
     SB_CUDA(frontend_configure());
+    SB_CUDA(cudaMalloc(&c->d_error, sizeof(int)));
+    SB_CUDA(cudaMemset(c->d_error, 0, sizeof(int)));
+    const char* why = nullptr;
+    cudaError_t ge = gemm_configure(&why);
+    if (ge != cudaSuccess) return fail(SB_CUDA_ERROR, std::string("GEMM set-up failed: ") + (why ? why : cudaGetErrorString(ge)));
     *out = c;
     return SB_OK;
 }
@@ -141,6 +147,7 @@ void sb_ctx_destroy(sb_ctx* c) {
     c->pcm_stage.release();
     c->feat_stage.release();
     if (c->d_tables) cudaFree(c->d_tables);
+    if (c->d_error) cudaFree(c->d_error);
     if (c->own_stream) cudaStreamDestroy(c->own_stream);
     delete c;
 }
@@ -155,6 +162,12 @@ int32_t sb_ctx_synchronize(sb_ctx* c) {
     if (!c) return fail(SB_INVALID_ARGUMENT, "ctx is null");
     SB_CUDA(cudaSetDevice(c->device));
     SB_CUDA(cudaStreamSynchronize(c->stream));
+    int err = 0;
+    SB_CUDA(cudaMemcpy(&err, c->d_error, sizeof(int), cudaMemcpyDeviceToHost));
+    if (err) {
+        SB_CUDA(cudaMemset(c->d_error, 0, sizeof(int)));
+        return fail(SB_TIMEOUT, "a bounded device-side wait ran out (kernel aborted cleanly)");
+    }
     return SB_OK;
 }
 
@@ -228,6 +241,24 @@ int32_t sb_frontend_host(sb_ctx* c, const float* pcm, const int64_t* clip_offset
     SB_CUDA(cudaMemcpyAsync(feats, c->feat_stage.p, sizeof(float) * kMels * static_cast<size_t>(frames),
                             cudaMemcpyDeviceToHost, c->stream));
     SB_CUDA(cudaStreamSynchronize(c->stream));
+    return SB_OK;
+}
+
+int32_t sb_gemm(sb_ctx* c, const void* d_a, const void* d_w, const float* d_bias, const float* d_row_scale,
+                const float* d_col_scale, void* d_out, int64_t M, int64_t N, int64_t K, int32_t fp8, int32_t act,
+                int32_t out_mode, float alpha) {
+    if (!c || !d_a || !d_w || !d_out) return fail(SB_INVALID_ARGUMENT, "null argument");
+    if (M < 0 || N <= 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+        return fail(SB_INVALID_ARGUMENT, "bad GEMM shape");
+    SB_CUDA(cudaSetDevice(c->device));
+    GemmArgs g{};
+    g.a = d_a; g.w = d_w; g.bias = d_bias; g.row_scale = d_row_scale; g.col_scale = d_col_scale; g.out = d_out;
+    g.M = (int)M; g.N = (int)N; g.K = (int)K; g.ldo = (int)N; g.act = act; g.out_mode = out_mode; g.alpha = alpha;
+    g.fp8 = fp8 != 0;
+    cudaError_t e = gemm_launch(g, c->sm_count, c->d_error, c->stream);
+    if (e == cudaErrorInvalidValue) return fail(SB_INVALID_ARGUMENT, "GEMM shape or alignment not supported");
+    SB_CUDA(e);
+    if (M > 0) c->launches += 1;
     return SB_OK;
 }
 

@@ -43,6 +43,7 @@ struct sb_ctx {
     int sm_count = 0;
     int64_t launches = 0;
     sb::FrontendTables* d_tables = nullptr;
+    int* d_error = nullptr;  // set by a kernel whose bounded wait ran out
     // frontend workspaces
     sb::Buffer clip_off, frame_off, col_mean, col_std, pcm_stage, feat_stage;
     sb::Model* model = nullptr;

@@ -1,0 +1,417 @@
+// Persistent tcgen05 GEMM for sm_100a:  out = epilogue(A[M x K] * W[N x K]^T).
+//
+// Used for every position-wise projection of the FastConformer encoder (feed-forward,
+// QKV / output, convolution-module pointwise, sub-sampling pointwise and linear) and the
+// joint network's encoder projection.  Operands are K-major bf16 (or e4m3), accumulation
+// is fp32 in tensor memory.
+//
+// One CTA per SM, 192 threads, warp-specialised:
+//   warp 0      TMA producer: 128-byte-swizzled [128 x 64] A tiles and [BN x 64] W tiles
+//               through a multi-stage shared-memory ring (full / empty mbarriers)
+//   warp 1      allocates tensor memory, issues tcgen05.mma (M = 128, N = BN, K = 16 per
+//               instruction, four per stage) from one lane; tcgen05.commit releases ring
+//               slots and publishes finished accumulators
+//   warps 2..5  epilogue: tcgen05.ld of the 128 x BN fp32 accumulator (one row per thread),
+//               scales / bias / activation / residual, vectorised stores.  Two accumulator
+//               buffers (2 x BN columns of tensor memory) let the epilogue of tile i overlap
+//               the main loop of tile i + 1.
+// Every wait on an mbarrier is bounded by a cycle budget; when it runs out the kernel sets
+// *error, drains, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gemm.h"
+
+namespace sb {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBKBytes = 128;  // one 128-byte swizzle row per operand row and stage
+constexpr int kGemmThreads = 192;
+constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 1.9 GHz
+
+template <int BN>
+struct Cfg {
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kABytes = kBM * kBKBytes;
+    static constexpr int kBBytes = BN * kBKBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarBytes = 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the budget runs out
+// or another role has already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <bool FP8>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    if constexpr (FP8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+// Instruction descriptor: fp32 accumulate, A and B K-major, M = 128, N = BN.
+template <int BN, bool FP8>
+__device__ __forceinline__ uint32_t make_idesc() {
+    const uint32_t fmt = FP8 ? 0u : 1u;  // kind::f8f6f4: 0 = e4m3; kind::f16: 1 = bf16
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+    if (act == kActSilu) return x / (1.0f + __expf(-x));
+    if (act == kActRelu) return fmaxf(x, 0.0f);
+    return x;
+}
+
+struct EpiParams {
+    const float* bias;
+    const float* row_scale;
+    const float* col_scale;
+    void* out;
+    int M, N, K, ldo, act, out_mode;
+    float alpha;
+};
+
+template <int BN, bool FP8>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, EpiParams ep,
+            int* __restrict__ error) {
+    using C = Cfg<BN>;
+    constexpr int S = C::kStages;
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    unsigned char* base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
+    const uint32_t a_base = base;
+    const uint32_t b_base = base + S * C::kABytes;
+    const uint32_t bar_base = base + S * C::kStageBytes;
+    // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2], then tmem pointer and abort flag
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * S + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * S + 2 + a); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + S * C::kStageBytes + 8 * (2 * S + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (ep.M + kBM - 1) / kBM;
+    const int n_tiles = ep.N / BN;
+    const int num_tiles = m_tiles * n_tiles;
+    const int k_tiles = ep.K / (FP8 ? 128 : 64);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m0 = (t / n_tiles) * kBM, n0 = (t % n_tiles) * BN;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), C::kStageBytes);
+                    const int kc = kt * (FP8 ? 128 : 64);
+                    tma_load_2d(a_base + s * C::kABytes, &tma_a, full_bar(s), kc, m0);
+                    tma_load_2d(b_base + s * C::kBBytes, &tma_b, full_bar(s), kc, n0);
+                }
+            }
+            if (!ok) {
+                // give copies already in flight time to land before the CTA exits
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc<BN, FP8>();
+            uint32_t it = 0, lt = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+                const int acc = lt & 1;
+                const uint32_t acc_ph = (lt >> 1) & 1;
+                if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1;
+                    if (!mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t adesc = make_smem_desc(a_base + s * C::kABytes);
+                    const uint64_t bdesc = make_smem_desc(b_base + s * C::kBBytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        // 32 bytes of K per instruction: +2 in the 16-byte start-address field
+                        tc_mma<FP8>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kt | k) ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(s));
+                }
+                if (ok) tc_commit(tfull_bar(acc));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+        uint32_t lt = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+            const int acc = lt & 1;
+            const uint32_t acc_ph = (lt >> 1) & 1;
+            const int m0 = (t / n_tiles) * kBM, n0 = (t % n_tiles) * BN;
+            if (!mbar_wait(tfull_bar(acc), acc_ph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + quad * 32 + lane;
+            const bool row_ok = row < ep.M;
+            const float rs = (FP8 && ep.row_scale && row_ok) ? ep.row_scale[row] : 1.0f;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(taddr + c, v);
+                tmem_wait_ld();
+                if (c + 32 >= BN) {
+                    // accumulator fully read: hand the buffer back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(acc));
+                }
+                if (!row_ok) continue;
+                const int col0 = n0 + c;
+                float x[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float f = __uint_as_float(v[j]);
+                    if (FP8) f *= rs * (ep.col_scale ? __ldg(ep.col_scale + col0 + j) : 1.0f);
+                    if (ep.bias) f += __ldg(ep.bias + col0 + j);
+                    x[j] = apply_act(f, ep.act);
+                }
+                if (ep.out_mode == kOutBf16) {
+                    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out) + (size_t)row * ep.ldo + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 pk;
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(x[j], x[j + 1]);
+                        __nv_bfloat162 p1 = __floats2bfloat162_rn(x[j + 2], x[j + 3]);
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(x[j + 4], x[j + 5]);
+                        __nv_bfloat162 p3 = __floats2bfloat162_rn(x[j + 6], x[j + 7]);
+                        pk.x = *reinterpret_cast<uint32_t*>(&p0);
+                        pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                        pk.z = *reinterpret_cast<uint32_t*>(&p2);
+                        pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                        *reinterpret_cast<uint4*>(o + j) = pk;
+                    }
+                } else {
+                    float* o = reinterpret_cast<float*>(ep.out) + (size_t)row * ep.ldo + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        float4 r;
+                        if (ep.out_mode == kOutResidual) {
+                            r = *reinterpret_cast<const float4*>(o + j);
+                            r.x = fmaf(ep.alpha, x[j], r.x);
+                            r.y = fmaf(ep.alpha, x[j + 1], r.y);
+                            r.z = fmaf(ep.alpha, x[j + 2], r.z);
+                            r.w = fmaf(ep.alpha, x[j + 3], r.w);
+                        } else {
+                            r = make_float4(ep.alpha * x[j], ep.alpha * x[j + 1], ep.alpha * x[j + 2],
+                                            ep.alpha * x[j + 3]);
+                        }
+                        *reinterpret_cast<float4*>(o + j) = r;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(error, 1);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int k_elems, int elem_bytes, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)k_elems, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)k_elems * elem_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)(kBKBytes / elem_bytes), (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    CUresult r = g_encode(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int BN, bool FP8>
+cudaError_t launch_t(const GemmArgs& g, int sm_count, int* d_error, cudaStream_t stream) {
+    alignas(64) CUtensorMap ma, mb;
+    const int eb = FP8 ? 1 : 2;
+    if (!make_map(&ma, g.a, g.M, g.K, eb, kBM) || !make_map(&mb, g.w, g.N, g.K, eb, BN)) return cudaErrorInvalidValue;
+    EpiParams ep{g.bias, g.row_scale, g.col_scale, g.out, g.M, g.N, g.K, g.ldo, g.act, g.out_mode, g.alpha};
+    const int tiles = ((g.M + kBM - 1) / kBM) * (g.N / BN);
+    const int grid = tiles < sm_count ? tiles : sm_count;
+    gemm_kernel<BN, FP8><<<grid, kGemmThreads, Cfg<BN>::kSmemBytes, stream>>>(ma, mb, ep, d_error);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t gemm_configure(const char** why) {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+            if (why) *why = "cuTensorMapEncodeTiled is not available from the driver";
+            return e != cudaSuccess ? e : cudaErrorNotSupported;
+        }
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    cudaError_t e;
+#define SB_SET(BN, F8)                                                                                      \
+    e = cudaFuncSetAttribute(gemm_kernel<BN, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+                             Cfg<BN>::kSmemBytes);                                                          \
+    if (e != cudaSuccess) {                                                                                 \
+        if (why) *why = "shared-memory opt-in for the GEMM kernel failed";                                  \
+        return e;                                                                                           \
+    }
+    SB_SET(256, false) SB_SET(128, false) SB_SET(256, true) SB_SET(128, true)
+#undef SB_SET
+    return cudaSuccess;
+}
+
+cudaError_t gemm_launch(const GemmArgs& g, int sm_count, int* d_error, cudaStream_t stream) {
+    if (!g_encode) return cudaErrorNotReady;
+    if (g.M <= 0) return cudaSuccess;
+    const int kq = g.fp8 ? 128 : 64;
+    if (g.N % 128 != 0 || g.K % kq != 0 || g.K <= 0) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.w) & 15) ||
+        (reinterpret_cast<uintptr_t>(g.out) & 15) || (g.ldo & 7))
+        return cudaErrorInvalidValue;
+    // BN = 256 when it divides N and still leaves at least one tile per SM; else 128.
+    const int m_tiles = (g.M + kBM - 1) / kBM;
+    const bool wide = (g.N % 256 == 0) && (m_tiles * (g.N / 256) >= sm_count);
+    if (g.fp8) return wide ? launch_t<256, true>(g, sm_count, d_error, stream) : launch_t<128, true>(g, sm_count, d_error, stream);
+    return wide ? launch_t<256, false>(g, sm_count, d_error, stream) : launch_t<128, false>(g, sm_count, d_error, stream);
+}
+
+}  // namespace sb

@@ -1,0 +1,37 @@
+// Tensor-core GEMM for the encoder / joint projections (see gemm.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sb {
+
+enum GemmAct : int { kActNone = 0, kActSilu = 1, kActRelu = 2 };
+enum GemmOut : int {
+    kOutBf16 = 0,      // out[M x N] bf16 = act(acc * scales + bias)
+    kOutF32 = 1,       // out[M x N] f32  = act(acc * scales + bias) * alpha
+    kOutResidual = 2,  // out[M x N] f32 += alpha * act(acc * scales + bias)
+};
+
+struct GemmArgs {
+    const void* a;           // [M x K] row-major, bf16 (or e4m3 when fp8)
+    const void* w;           // [N x K] row-major (nn.Linear layout), same type
+    const float* bias;       // [N] or null
+    const float* row_scale;  // fp8 only: per-row activation scale [M], or null
+    const float* col_scale;  // fp8 only: per-output-channel weight scale [N], or null
+    void* out;
+    int M, N, K;
+    int ldo;                 // leading dimension of out in elements
+    int act;
+    int out_mode;
+    float alpha;
+    bool fp8;
+};
+
+// One-time set-up (driver entry point for tensor maps, shared-memory opt-in).
+cudaError_t gemm_configure(const char** why);
+// Launches the tcgen05 GEMM on `stream`.  `d_error` is a device int that the kernel
+// sets non-zero if a bounded wait ran out.  Returns cudaErrorInvalidValue for shapes
+// the kernel does not cover (N % 128 != 0, K % 64 (bf16) / 128 (fp8) != 0).
+cudaError_t gemm_launch(const GemmArgs& g, int sm_count, int* d_error, cudaStream_t stream);
+
+}  // namespace sb
