@@ -27,10 +27,10 @@ def test_bf16_store_modes(ctx, M, N, K):
     a = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
     w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
     bias = torch.randn(N, device="cuda", generator=g) * 0.1
-    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
     acc = a.float() @ w.float().t()
     # f32 store, no activation: only the accumulation order differs
     out = torch.full((M, N), float("nan"), device="cuda")
+    torch.cuda.synchronize()  # the context launches on its own stream
     sb.gemm(ctx, a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, d_bias=bias.data_ptr(), out_mode=1)
     ctx.synchronize()
     ref = ref_epilogue(acc, bias, 0)
@@ -39,6 +39,7 @@ def test_bf16_store_modes(ctx, M, N, K):
     assert err < 1e-5, float(err)
     # bf16 store with SiLU
     outb = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
     sb.gemm(ctx, a.data_ptr(), w.data_ptr(), outb.data_ptr(), M, N, K, d_bias=bias.data_ptr(), act=1, out_mode=0)
     ctx.synchronize()
     ref = ref_epilogue(acc, bias, 1)
@@ -47,13 +48,13 @@ def test_bf16_store_modes(ctx, M, N, K):
     # residual accumulate with ReLU and alpha = 0.5
     res0 = torch.randn(M, N, device="cuda", generator=g)
     res = res0.clone()
+    torch.cuda.synchronize()
     sb.gemm(ctx, a.data_ptr(), w.data_ptr(), res.data_ptr(), M, N, K, d_bias=bias.data_ptr(), act=2, out_mode=2,
             alpha=0.5)
     ctx.synchronize()
     ref = res0 + 0.5 * ref_epilogue(acc, bias, 2)
     err = (res - ref).norm() / ref.norm()
     assert err < 1e-5, float(err)
-    ctx.set_stream(None)
 
 
 def test_rows_beyond_m_are_untouched(ctx):
@@ -63,10 +64,9 @@ def test_rows_beyond_m_are_untouched(ctx):
     a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
     w = torch.randn(N, K, device="cuda").to(torch.bfloat16)
     out = torch.full((M + 126, N), 7.0, device="cuda")
-    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
     sb.gemm(ctx, a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, out_mode=1)
     ctx.synchronize()
-    ctx.set_stream(None)
     assert (out[M:] == 7.0).all()
     ref = a.float() @ w.float().t()
     assert (out[:M] - ref).norm() / ref.norm() < 1e-5
