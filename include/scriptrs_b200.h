@@ -130,6 +130,54 @@ int32_t sb_frontend_device(sb_ctx* ctx, const float* d_pcm, const int64_t* clip_
 int32_t sb_frontend_host(sb_ctx* ctx, const float* pcm, const int64_t* clip_offsets, int64_t n_clips,
                          float preemphasis, int32_t normalize, float* feats, int64_t* frame_offsets);
 
+/* ------------------------------------------------------------------ model */
+
+/* One named fp32 tensor in host memory. */
+typedef struct sb_tensor {
+    const char* name;
+    const float* data;
+    int64_t numel;
+} sb_tensor;
+
+/* What to load.  The network shape is fixed to Parakeet-TDT-0.6B (128 mels, 256 sub-sampling
+ * channels, d_model 1024, 8 heads, FF 4096, depthwise k = 9; predictor 2 x LSTM(640), joint 640,
+ * 1025 tokens + 5 durations); the number of Conformer blocks is free so that tests can run a
+ * shallow stack. */
+typedef struct sb_model_desc {
+    int32_t encoder_layers; /* 24 */
+    int32_t scale_input;    /* multiply the sub-sampling output by sqrt(d_model) */
+    int32_t has_encoder;
+    int32_t has_decoder;
+} sb_model_desc;
+
+/* Uploads the weights to the context's GPU in the layouts the kernels use (bf16 GEMM operands,
+ * fused QKV, BatchNorm folded into the depthwise taps, projected relative-position table).
+ * Replaces ParakeetModel::from_bundle (src/model.rs:22-35) / ModelBundle (src/models.rs:31-104).
+ * Tensor names: "subsampling.layers.{0,2,3,5,6}.{weight,bias}", "subsampling.linear.*",
+ * "layers.<i>.{feed_forward1,feed_forward2}.linear{1,2}.*", "layers.<i>.self_attn.{q,k,v,o}_proj.*",
+ * "layers.<i>.self_attn.{relative_k_proj.weight,bias_u,bias_v}", "layers.<i>.conv.{pointwise_conv1,
+ * depthwise_conv,pointwise_conv2}.*", "layers.<i>.conv.norm.{weight,bias,running_mean,running_var}",
+ * "layers.<i>.norm_{feed_forward1,self_att,conv,feed_forward2,out}.*", "predictor.embedding",
+ * "predictor.lstm.{weight_ih,weight_hh,bias_ih,bias_hh}" (layers stacked, gate order i,f,g,o),
+ * "joint.{enc,pred,out}.{weight,bias}".  A missing tensor fails with SB_MISSING_MODEL_ASSET. */
+int32_t sb_model_load(sb_ctx* ctx, const sb_model_desc* desc, const sb_tensor* tensors, int64_t n_tensors);
+
+/* ---------------------------------------------------------------- encoder */
+
+/* Encoder frames for a number of feature frames: three times L <- (L - 1) / 2 + 1
+ * (1501 -> 188, the reference's ENCODER_SUBSAMPLING = 8, src/constants.rs:4). */
+int64_t sb_encoder_num_frames(int64_t feature_frames);
+
+/* Batched ParakeetModelInner::run_encoder (src/model.rs:327-342; CoreML contract src/coreml.rs:75-135).
+ *   d_feats        device, packed [sum_i T_i x 128] f32 (the output of sb_frontend_device)
+ *   frame_offsets  host, n_clips + 1 prefix sums of T_i
+ *   d_out          device, packed [sum_i T'_i x 1024] f32, time-major per clip
+ *   enc_offsets    host, n_clips + 1, written with the prefix sums of T'_i
+ * Each clip is encoded with its exact length (no padding frames), which is what the reference's
+ * blob does with `mel_length`.  T_i may not exceed 1501 (T' <= 188).  Asynchronous on the stream. */
+int32_t sb_encode_device(sb_ctx* ctx, const float* d_feats, const int64_t* frame_offsets, int64_t n_clips,
+                         float* d_out, int64_t* enc_offsets);
+
 /* ------------------------------------------------------------------ GEMM */
 
 /* Tensor-core GEMM building block of the encoder: out = epilogue(A[M x K] * W[N x K]^T).

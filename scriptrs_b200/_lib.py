@@ -34,6 +34,15 @@ class LongFormConfigC(C.Structure):
                 ("overlap", OverlapConfigC)]
 
 
+class TensorC(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("data", C.c_void_p), ("numel", C.c_int64)]
+
+
+class ModelDescC(C.Structure):
+    _fields_ = [("encoder_layers", C.c_int32), ("scale_input", C.c_int32), ("has_encoder", C.c_int32),
+                ("has_decoder", C.c_int32)]
+
+
 class ChunkTaskC(C.Structure):
     _fields_ = [("audio_start", C.c_int64), ("audio_end", C.c_int64), ("global_sample_offset", C.c_int64),
                 ("context_samples", C.c_int64)]
@@ -61,6 +70,9 @@ SIGNATURES = {
     "sb_frontend_num_frames": (_I64, [_I64]),
     "sb_frontend_device": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
     "sb_frontend_host": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
+    "sb_model_load": (_I32, [_VP, C.POINTER(ModelDescC), C.POINTER(TensorC), _I64]),
+    "sb_encoder_num_frames": (_I64, [_I64]),
+    "sb_encode_device": (_I32, [_VP, _VP, _VP, _I64, _VP, _VP]),
     "sb_gemm": (_I32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I64, _I64, _I32, _I32, _I32, C.c_float]),
 }
 

@@ -147,3 +147,28 @@ def gemm(ctx: Context, d_a: int, d_w: int, d_out: int, M: int, N: int, K: int, d
     check(_lib.lib().sb_gemm(ctx.handle, C.c_void_p(d_a), C.c_void_p(d_w), C.c_void_p(d_bias or None),
                              C.c_void_p(d_row_scale or None), C.c_void_p(d_col_scale or None), C.c_void_p(d_out),
                              M, N, K, int(fp8), act, out_mode, float(alpha)))
+
+
+def load_model(ctx: Context, weights: dict, encoder_layers: int, scale_input: bool = False,
+               has_encoder: bool = True, has_decoder: bool = False):
+    """Uploads a dict of named float32 arrays (see sb_model_load for the names)."""
+    keep = {k: np.ascontiguousarray(v, np.float32) for k, v in weights.items()}
+    arr = (_lib.TensorC * max(len(keep), 1))()
+    for i, (k, v) in enumerate(keep.items()):
+        arr[i] = _lib.TensorC(k.encode(), v.ctypes.data, v.size)
+    desc = _lib.ModelDescC(encoder_layers, int(scale_input), int(has_encoder), int(has_decoder))
+    check(_lib.lib().sb_model_load(ctx.handle, C.byref(desc), arr, len(keep)))
+
+
+def encoder_num_frames(feature_frames: int) -> int:
+    return int(_lib.lib().sb_encoder_num_frames(feature_frames))
+
+
+def encode_device(ctx: Context, d_feats: int, frame_offsets: np.ndarray, d_out: int) -> np.ndarray:
+    """Packed features -> packed encoder output; device pointers; returns the T' prefix sums."""
+    frame_offsets = np.ascontiguousarray(frame_offsets, np.int64)
+    n = frame_offsets.size - 1
+    eo = np.zeros(n + 1, np.int64)
+    check(_lib.lib().sb_encode_device(ctx.handle, C.c_void_p(d_feats), _ptr(frame_offsets), n, C.c_void_p(d_out),
+                                      _ptr(eo)))
+    return eo

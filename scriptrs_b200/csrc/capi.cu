@@ -6,7 +6,9 @@
 #include <vector>
 
 #include "context.h"
+#include "encoder.h"
 #include "gemm.h"
+#include "model.h"
 
 namespace sb {
 
@@ -131,6 +133,8 @@ int32_t sb_ctx_create(int32_t device, sb_ctx** out) {
     const char* why = nullptr;
     cudaError_t ge = gemm_configure(&why);
     if (ge != cudaSuccess) return fail(SB_CUDA_ERROR, std::string("GEMM set-up failed: ") + (why ? why : cudaGetErrorString(ge)));
+    SB_CUDA(encoder_configure());
+    c->enc_ws = new EncoderWorkspace();
     *out = c;
     return SB_OK;
 }
@@ -241,6 +245,36 @@ int32_t sb_frontend_host(sb_ctx* c, const float* pcm, const int64_t* clip_offset
     SB_CUDA(cudaMemcpyAsync(feats, c->feat_stage.p, sizeof(float) * kMels * static_cast<size_t>(frames),
                             cudaMemcpyDeviceToHost, c->stream));
     SB_CUDA(cudaStreamSynchronize(c->stream));
+    return SB_OK;
+}
+
+int32_t sb_model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensors, int64_t n_tensors) {
+    return model_load(c, desc, tensors, n_tensors);
+}
+
+int64_t sb_encoder_num_frames(int64_t feature_frames) {
+    return feature_frames <= 0 ? 0 : encoder_out_frames((int)feature_frames);
+}
+
+int32_t sb_encode_device(sb_ctx* c, const float* d_feats, const int64_t* frame_offsets, int64_t n_clips,
+                         float* d_out, int64_t* enc_offsets) {
+    if (!c || !d_feats || !frame_offsets || !d_out) return fail(SB_INVALID_ARGUMENT, "null argument");
+    if (!c->model || !c->model->has_encoder) return fail(SB_MISSING_MODEL_ASSET, "no encoder weights loaded");
+    if (n_clips <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");
+    if (n_clips > 65535) return fail(SB_INVALID_ARGUMENT, "at most 65535 clips per call");
+    for (int64_t i = 0; i < n_clips; ++i) {
+        const int64_t t = frame_offsets[i + 1] - frame_offsets[i];
+        if (t <= 0) return fail(SB_EMPTY_AUDIO, "clip without feature frames");
+        if (t > 1501)  // model.rs:259-264: feature frames beyond the encoder's window
+            return fail(SB_INVALID_MODEL_OUTPUT, "feature frame count " + std::to_string(t) + " exceeded encoder target 1501");
+    }
+    SB_CUDA(cudaSetDevice(c->device));
+    std::vector<int> eo(static_cast<size_t>(n_clips) + 1);
+    cudaError_t e = encoder_forward(c, *c->model, d_feats, frame_offsets, (int)n_clips, d_out, eo.data(), *c->enc_ws,
+                                    c->workspace_budget);
+    SB_CUDA(e);
+    if (enc_offsets)
+        for (int64_t i = 0; i <= n_clips; ++i) enc_offsets[i] = eo[i];
     return SB_OK;
 }
 

@@ -32,7 +32,9 @@ struct Buffer {
     T* as() const { return static_cast<T*>(p); }
 };
 
-struct Model;  // encoder + predictor + joint weights (model.h)
+struct Model;             // encoder + predictor + joint weights (model.h)
+struct EncoderWorkspace;  // encoder.h
+int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensors, int64_t n_tensors);
 
 }  // namespace sb
 
@@ -47,4 +49,6 @@ struct sb_ctx {
     // frontend workspaces
     sb::Buffer clip_off, frame_off, col_mean, col_std, pcm_stage, feat_stage;
     sb::Model* model = nullptr;
+    sb::EncoderWorkspace* enc_ws = nullptr;
+    size_t workspace_budget = (size_t)12 << 30;  // bytes of encoder intermediates per group of clips
 };

@@ -1,0 +1,448 @@
+// FastConformer encoder (Parakeet-TDT-0.6B shape) on sm_100a.
+//
+// The reference runs this network as an opaque CoreML blob behind
+// ParakeetModelInner::run_encoder (src/model.rs:327-342, I/O contract src/coreml.rs:75-135):
+// normalised log-mel [T x 128] in, [T' x 1024] out with T' = ceil-halved three times.
+// Here a batch of clips is packed row-wise (variable length, no padding): all position-wise
+// projections run as tcgen05 GEMMs over the packed rows (gemm.cu); the kernels in this file
+// cover what is not a GEMM and respect clip boundaries.
+//
+//   sub_conv0_kernel     conv2d(1 -> 256, k3, s2, p1) + ReLU, channels-last bf16 output
+//   sub_dw_kernel        depthwise conv2d(k3, s2, p1) + bias (feeds the pointwise GEMM)
+//   layernorm_kernel     one warp per 1024-wide row, fp32 statistics, bf16 or f32 output
+//   relpos_attention_kernel  per (clip, head): scores = ((q + u) k^T + (q + v) p^T[i - j]) / sqrt(128),
+//                        softmax, PV; the relative shift is index arithmetic, never materialised
+//   glu_dwconv_kernel    GLU + depthwise conv k = 9 ('same' within the clip) + folded BatchNorm + SiLU
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "encoder.h"
+#include "gemm.h"
+
+namespace sb {
+
+namespace {
+
+__device__ __forceinline__ int find_clip(const int* __restrict__ off, int n, int row) {
+    // largest c with off[c] <= row
+    int lo = 0, hi = n;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (off[mid] <= row) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// ---------------------------------------------------------------- sub-sampling
+// feats f32 [sum T x 128] -> y0 bf16 [sum T1 x 64 x 256], one CTA per output time row.
+__global__ void __launch_bounds__(256)
+sub_conv0_kernel(const float* __restrict__ feats, const int64_t* __restrict__ t0_off, const int* __restrict__ t1_off,
+                 int n_clips, const float* __restrict__ w, const float* __restrict__ b, bf16* __restrict__ out) {
+    __shared__ float in[3][kMels + 2];
+    const int g1 = blockIdx.x;
+    const int clip = find_clip(t1_off, n_clips, g1);
+    const int t1 = g1 - t1_off[clip];
+    const int64_t base = t0_off[clip];
+    const int T = (int)(t0_off[clip + 1] - base);
+    for (int i = threadIdx.x; i < 3 * (kMels + 2); i += 256) {
+        const int dt = i / (kMels + 2), f = i % (kMels + 2) - 1;
+        const int r = 2 * t1 - 1 + dt;
+        float v = 0.0f;
+        if (r >= 0 && r < T && f >= 0 && f < kMels) v = feats[(base + r) * kMels + f];
+        in[dt][f + 1] = v;
+    }
+    __syncthreads();
+    const int c = threadIdx.x;
+    float wr[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) wr[i] = w[c * 9 + i];
+    const float bias = b[c];
+    bf16* o = out + (size_t)g1 * 64 * kSubC + c;
+#pragma unroll 4
+    for (int f1 = 0; f1 < 64; ++f1) {
+        float acc = bias;
+#pragma unroll
+        for (int dt = 0; dt < 3; ++dt)
+#pragma unroll
+            for (int df = 0; df < 3; ++df) acc = fmaf(wr[dt * 3 + df], in[dt][2 * f1 + df], acc);
+        o[(size_t)f1 * kSubC] = __float2bfloat16(fmaxf(acc, 0.0f));
+    }
+}
+
+// in bf16 [sum Tin x Fin x 256] -> out bf16 [sum Tout x Fin/2 x 256]; one CTA per output time row,
+// 128 threads, two channels each.  w is tap-major [9 x 256].
+__global__ void __launch_bounds__(128)
+sub_dw_kernel(const bf16* __restrict__ in, const int* __restrict__ tin_off, const int* __restrict__ tout_off,
+              int n_clips, int fin, const float* __restrict__ w, const float* __restrict__ b, bf16* __restrict__ out) {
+    const int go = blockIdx.x;
+    const int clip = find_clip(tout_off, n_clips, go);
+    const int to = go - tout_off[clip];
+    const int in_base = tin_off[clip];
+    const int Tin = tin_off[clip + 1] - in_base;
+    const int fout = fin >> 1;
+    const int c = threadIdx.x * 2;
+    float w0[9], w1[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) {
+        w0[i] = w[i * kSubC + c];
+        w1[i] = w[i * kSubC + c + 1];
+    }
+    const float b0 = b[c], b1 = b[c + 1];
+    for (int fo = 0; fo < fout; ++fo) {
+        float a0 = b0, a1 = b1;
+#pragma unroll
+        for (int dt = 0; dt < 3; ++dt) {
+            const int r = 2 * to - 1 + dt;
+            if (r < 0 || r >= Tin) continue;
+#pragma unroll
+            for (int df = 0; df < 3; ++df) {
+                const int f = 2 * fo - 1 + df;
+                if (f < 0 || f >= fin) continue;
+                const __nv_bfloat162 v =
+                    *reinterpret_cast<const __nv_bfloat162*>(in + ((size_t)(in_base + r) * fin + f) * kSubC + c);
+                a0 = fmaf(w0[dt * 3 + df], __low2float(v), a0);
+                a1 = fmaf(w1[dt * 3 + df], __high2float(v), a1);
+            }
+        }
+        *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)go * fout + fo) * kSubC + c) = __floats2bfloat162_rn(a0, a1);
+    }
+}
+
+// ---------------------------------------------------------------- LayerNorm
+// One warp per row of 1024.  OUT_F32: write f32 (in place allowed), else bf16.
+template <bool OUT_F32>
+__global__ void __launch_bounds__(256)
+layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                 void* __restrict__ out, int rows) {
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * kDModel);
+    float4 v[8];
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        v[k] = xr[lane + 32 * k];
+        s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mean = s * (1.0f / kDModel);
+    float q = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
+        q += (a * a + b * b) + (c * c + d * d);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    const float rstd = rsqrtf(q * (1.0f / kDModel) + 1e-5f);
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(beta);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float4 g = g4[lane + 32 * k], b = b4[lane + 32 * k];
+        float4 y;
+        y.x = (v[k].x - mean) * rstd * g.x + b.x;
+        y.y = (v[k].y - mean) * rstd * g.y + b.y;
+        y.z = (v[k].z - mean) * rstd * g.z + b.z;
+        y.w = (v[k].w - mean) * rstd * g.w + b.w;
+        if (OUT_F32) {
+            reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)row * kDModel)[lane + 32 * k] = y;
+        } else {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(y.x, y.y), p1 = __floats2bfloat162_rn(y.z, y.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&p0);
+            pk.y = *reinterpret_cast<uint32_t*>(&p1);
+            reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + (size_t)row * kDModel)[lane + 32 * k] = pk;
+        }
+    }
+}
+
+// ---------------------------------------------------------------- relative-position attention
+constexpr int kAttThreads = 256;
+constexpr int kRowStride = kHeadDim + 2;  // bf16 elements; 65 words -> conflict-free column walks
+
+__device__ __forceinline__ float dot128(const float* __restrict__ q, const bf16* __restrict__ row) {
+    float acc = 0.0f;
+    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(row);
+#pragma unroll 16
+    for (int d = 0; d < kHeadDim / 2; ++d) {
+        const float2 f = __bfloat1622float2(r2[d]);
+        acc = fmaf(q[2 * d], f.x, acc);
+        acc = fmaf(q[2 * d + 1], f.y, acc);
+    }
+    return acc;
+}
+
+// qkv bf16 [rows x 3072]; pos bf16 [kPosRows x 1024] (row p <-> relative position 187 - p);
+// out bf16 [rows x 1024].  grid (heads, clips).
+__global__ void __launch_bounds__(kAttThreads)
+relpos_attention_kernel(const bf16* __restrict__ qkv, const int* __restrict__ t3_off, const bf16* __restrict__ pos,
+                        const float* __restrict__ bias_u, const float* __restrict__ bias_v, bf16* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char att_smem[];
+    const int head = blockIdx.x, clip = blockIdx.y;
+    const int r0 = t3_off[clip];
+    const int t = t3_off[clip + 1] - r0;
+    if (t <= 0) return;
+    bf16* Ks = reinterpret_cast<bf16*>(att_smem);
+    bf16* Vs = Ks + (size_t)kMaxEncFrames * kRowStride;
+    bf16* Ps = Vs + (size_t)kMaxEncFrames * kRowStride;                 // 2t - 1 rows
+    float* wbuf = reinterpret_cast<float*>(Ps + (size_t)kPosRows * kRowStride);  // per warp: qu[128], qv[128], p[192]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // stage K, V (this head) and the 2t - 1 position rows for relative positions t-1 .. -(t-1)
+    for (int i = tid; i < t * (kHeadDim / 2); i += kAttThreads) {
+        const int j = i / (kHeadDim / 2), d2 = i % (kHeadDim / 2);
+        const bf16* src = qkv + (size_t)(r0 + j) * (3 * kDModel) + head * kHeadDim + 2 * d2;
+        *reinterpret_cast<__nv_bfloat162*>(Ks + j * kRowStride + 2 * d2) =
+            *reinterpret_cast<const __nv_bfloat162*>(src + kDModel);
+        *reinterpret_cast<__nv_bfloat162*>(Vs + j * kRowStride + 2 * d2) =
+            *reinterpret_cast<const __nv_bfloat162*>(src + 2 * kDModel);
+    }
+    const int p0 = (kMaxEncFrames - 1) - (t - 1);  // table row of relative position t - 1
+    for (int i = tid; i < (2 * t - 1) * (kHeadDim / 2); i += kAttThreads) {
+        const int pl = i / (kHeadDim / 2), d2 = i % (kHeadDim / 2);
+        *reinterpret_cast<__nv_bfloat162*>(Ps + pl * kRowStride + 2 * d2) =
+            *reinterpret_cast<const __nv_bfloat162*>(pos + (size_t)(p0 + pl) * kDModel + head * kHeadDim + 2 * d2);
+    }
+    __syncthreads();
+
+    float* qu = wbuf + warp * (2 * kHeadDim + 192);
+    float* qv = qu + kHeadDim;
+    float* pr = qv + kHeadDim;
+    const float scale = 0.08838834764831845f;  // 1 / sqrt(128)
+    for (int i = warp; i < t; i += kAttThreads / 32) {
+        const bf16* qrow = qkv + (size_t)(r0 + i) * (3 * kDModel) + head * kHeadDim;
+        for (int d = lane; d < kHeadDim; d += 32) {
+            const float q = __bfloat162float(qrow[d]);
+            qu[d] = q + bias_u[head * kHeadDim + d];
+            qv[d] = q + bias_v[head * kHeadDim + d];
+        }
+        __syncwarp();
+        float mx = -INFINITY;
+        for (int j = lane; j < t; j += 32) {
+            const float ac = dot128(qu, Ks + j * kRowStride);
+            // relative position i - j lives in local row (t - 1) - (i - j)
+            const float bd = dot128(qv, Ps + ((t - 1) - i + j) * kRowStride);
+            const float s = (ac + bd) * scale;
+            pr[j] = s;
+            mx = fmaxf(mx, s);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.0f;
+        for (int j = lane; j < t; j += 32) {
+            const float e = __expf(pr[j] - mx);
+            pr[j] = e;
+            sum += e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float inv = 1.0f / sum;
+        __syncwarp();
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        for (int j = 0; j < t; ++j) {
+            const float p = pr[j];
+            const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(Vs + j * kRowStride + 4 * lane);
+            const float2 f0 = __bfloat1622float2(v2[0]), f1 = __bfloat1622float2(v2[1]);
+            a0 = fmaf(p, f0.x, a0); a1 = fmaf(p, f0.y, a1); a2 = fmaf(p, f1.x, a2); a3 = fmaf(p, f1.y, a3);
+        }
+        __nv_bfloat162 o0 = __floats2bfloat162_rn(a0 * inv, a1 * inv), o1 = __floats2bfloat162_rn(a2 * inv, a3 * inv);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&o0);
+        pk.y = *reinterpret_cast<uint32_t*>(&o1);
+        *reinterpret_cast<uint2*>(out + (size_t)(r0 + i) * kDModel + head * kHeadDim + 4 * lane) = pk;
+        __syncwarp();
+    }
+}
+
+constexpr size_t kAttSmemBytes = ((size_t)(2 * kMaxEncFrames + kPosRows) * kRowStride) * sizeof(bf16) +
+                                 (size_t)(kAttThreads / 32) * (2 * kHeadDim + 192) * sizeof(float);
+
+// ---------------------------------------------------------------- GLU + depthwise conv + BN + SiLU
+// in bf16 [rows x 2048] -> out bf16 [rows x 1024].  grid (time blocks of 32, clips, 4 channel blocks).
+constexpr int kDwRows = 32;
+__global__ void __launch_bounds__(256)
+glu_dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, const float* __restrict__ w,
+                  const float* __restrict__ b, bf16* __restrict__ out) {
+    const int clip = blockIdx.y;
+    const int r0 = t3_off[clip];
+    const int t = t3_off[clip + 1] - r0;
+    const int tb = blockIdx.x * kDwRows;
+    if (tb >= t) return;
+    const int c = blockIdx.z * 256 + threadIdx.x;
+    float wr[kConvK];
+#pragma unroll
+    for (int k = 0; k < kConvK; ++k) wr[k] = w[k * kDModel + c];
+    const float bias = b[c];
+    float g[kDwRows + kConvK - 1];
+#pragma unroll
+    for (int r = 0; r < kDwRows + kConvK - 1; ++r) {
+        const int tt = tb - (kConvK - 1) / 2 + r;
+        float v = 0.0f;
+        if (tt >= 0 && tt < t) {
+            const bf16* p = in + (size_t)(r0 + tt) * (2 * kDModel) + c;
+            const float a = __bfloat162float(p[0]), gate = __bfloat162float(p[kDModel]);
+            v = a / (1.0f + __expf(-gate));
+        }
+        g[r] = v;
+    }
+#pragma unroll
+    for (int r = 0; r < kDwRows; ++r) {
+        if (tb + r >= t) break;
+        float acc = bias;
+#pragma unroll
+        for (int k = 0; k < kConvK; ++k) acc = fmaf(wr[k], g[r + k], acc);
+        out[(size_t)(r0 + tb + r) * kDModel + c] = __float2bfloat16(acc / (1.0f + __expf(-acc)));
+    }
+}
+
+cudaError_t run_gemm(sb_ctx* c, const void* a, const bf16* w, const float* bias, void* out, int M, int N, int K, int act,
+                     int mode, float alpha) {
+    GemmArgs g{};
+    g.a = a; g.w = w; g.bias = bias; g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = N; g.act = act; g.out_mode = mode;
+    g.alpha = alpha; g.fp8 = false;
+    c->launches += 1;
+    return gemm_launch(g, c->sm_count, c->d_error, c->stream);
+}
+
+#define ENC_CUDA(expr)                       \
+    do {                                     \
+        cudaError_t _e = (expr);             \
+        if (_e != cudaSuccess) return _e;    \
+    } while (0)
+
+}  // namespace
+
+cudaError_t encoder_configure() {
+    return cudaFuncSetAttribute(relpos_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)kAttSmemBytes);
+}
+
+int encoder_out_frames(int mel_frames) {
+    int t = mel_frames;
+    for (int i = 0; i < 3; ++i) t = (t - 1) / 2 + 1;
+    return t;
+}
+
+// Runs the encoder on clips [c0, c1) of a packed feature batch.  frame_off: host prefix sums of mel
+// frames per clip (size n + 1, relative to d_feats).  d_out receives [sum T' x 1024] f32 for the group,
+// written at row enc_off[c0].
+static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats, const int64_t* frame_off, int c0, int c1,
+                                const int* enc_off_all, float* d_out, EncoderWorkspace& ws) {
+    const int n = c1 - c0;
+    std::vector<int64_t> t0(n + 1);
+    std::vector<int> t1(n + 1), t2(n + 1), t3(n + 1);
+    t0[0] = frame_off[c0];
+    t1[0] = t2[0] = t3[0] = 0;
+    for (int i = 0; i < n; ++i) {
+        const int T = (int)(frame_off[c0 + i + 1] - frame_off[c0 + i]);
+        const int a = (T - 1) / 2 + 1, b = (a - 1) / 2 + 1, d = (b - 1) / 2 + 1;
+        t0[i + 1] = t0[i] + T;
+        t1[i + 1] = t1[i] + a;
+        t2[i + 1] = t2[i] + b;
+        t3[i + 1] = t3[i] + d;
+    }
+    const int R1 = t1[n], R2 = t2[n], R3 = t3[n];
+    const int max_t3 = [&] { int mx = 0; for (int i = 0; i < n; ++i) mx = std::max(mx, t3[i + 1] - t3[i]); return mx; }();
+    if (max_t3 > kMaxEncFrames) return cudaErrorInvalidValue;
+    cudaStream_t st = c->stream;
+    // offsets -> device (one buffer: t0 as int64, then three int arrays)
+    const size_t off_bytes = sizeof(int64_t) * (n + 1) + 3 * sizeof(int) * (n + 1) + 64;
+    ENC_CUDA(ws.offsets.ensure(off_bytes));
+    int64_t* d_t0 = ws.offsets.as<int64_t>();
+    int* d_t1 = reinterpret_cast<int*>(d_t0 + (n + 1));
+    int* d_t2 = d_t1 + (n + 1);
+    int* d_t3 = d_t2 + (n + 1);
+    ENC_CUDA(cudaMemcpyAsync(d_t0, t0.data(), sizeof(int64_t) * (n + 1), cudaMemcpyHostToDevice, st));
+    ENC_CUDA(cudaMemcpyAsync(d_t1, t1.data(), sizeof(int) * (n + 1), cudaMemcpyHostToDevice, st));
+    ENC_CUDA(cudaMemcpyAsync(d_t2, t2.data(), sizeof(int) * (n + 1), cudaMemcpyHostToDevice, st));
+    ENC_CUDA(cudaMemcpyAsync(d_t3, t3.data(), sizeof(int) * (n + 1), cudaMemcpyHostToDevice, st));
+
+    ENC_CUDA(ws.y0.ensure((size_t)R1 * 64 * kSubC * sizeof(bf16)));
+    ENC_CUDA(ws.y1.ensure((size_t)R2 * 32 * kSubC * sizeof(bf16)));
+    ENC_CUDA(ws.y2.ensure((size_t)R2 * 32 * kSubC * sizeof(bf16)));
+    ENC_CUDA(ws.y3.ensure((size_t)R3 * 16 * kSubC * sizeof(bf16)));
+    ENC_CUDA(ws.y4.ensure((size_t)R3 * 16 * kSubC * sizeof(bf16)));
+    ENC_CUDA(ws.x.ensure((size_t)R3 * kDModel * sizeof(float)));
+    ENC_CUDA(ws.a.ensure((size_t)R3 * kDModel * sizeof(bf16)));
+    ENC_CUDA(ws.h.ensure((size_t)R3 * kFF * sizeof(bf16)));
+    ENC_CUDA(ws.att.ensure((size_t)R3 * kDModel * sizeof(bf16)));
+
+    // sub-sampling
+    sub_conv0_kernel<<<R1, 256, 0, st>>>(d_feats, d_t0, d_t1, n, m.sub0_w, m.sub0_b, ws.y0.as<bf16>());
+    sub_dw_kernel<<<R2, 128, 0, st>>>(ws.y0.as<bf16>(), d_t1, d_t2, n, 64, m.dw1_w, m.dw1_b, ws.y1.as<bf16>());
+    c->launches += 2;
+    ENC_CUDA(run_gemm(c, ws.y1.p, m.pw1_w, m.pw1_b, ws.y2.p, R2 * 32, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
+    sub_dw_kernel<<<R3, 128, 0, st>>>(ws.y2.as<bf16>(), d_t2, d_t3, n, 32, m.dw2_w, m.dw2_b, ws.y3.as<bf16>());
+    c->launches += 1;
+    ENC_CUDA(run_gemm(c, ws.y3.p, m.pw2_w, m.pw2_b, ws.y4.p, R3 * 16, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
+    float* x = ws.x.as<float>();
+    ENC_CUDA(run_gemm(c, ws.y4.p, m.lin_w, m.lin_b, x, R3, kDModel, 16 * kSubC, kActNone, kOutF32, m.xscale));
+
+    const int ln_grid = (R3 + 7) / 8;
+    bf16* a = ws.a.as<bf16>();
+    bf16* h = ws.h.as<bf16>();
+    bf16* att = ws.att.as<bf16>();
+    for (int l = 0; l < m.layers; ++l) {
+        const LayerWeights& L = m.L[l];
+        // x += 0.5 * FF1(LN x)
+        layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_ff1_g, L.ln_ff1_b, a, R3);
+        ENC_CUDA(run_gemm(c, a, L.ff1_w1, L.ff1_b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
+        ENC_CUDA(run_gemm(c, h, L.ff1_w2, L.ff1_b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
+        // x += MHA(LN x)
+        layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_att_g, L.ln_att_b, a, R3);
+        ENC_CUDA(run_gemm(c, a, L.qkv_w, L.qkv_b, h, R3, 3 * kDModel, kDModel, kActNone, kOutBf16, 1.0f));
+        relpos_attention_kernel<<<dim3(kHeads, n), kAttThreads, kAttSmemBytes, st>>>(h, d_t3, L.pos_proj, L.bias_u,
+                                                                                    L.bias_v, att);
+        ENC_CUDA(run_gemm(c, att, L.o_w, L.o_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
+        // x += Conv(LN x)
+        layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_conv_g, L.ln_conv_b, a, R3);
+        ENC_CUDA(run_gemm(c, a, L.pw1_w, L.pw1_b, h, R3, 2 * kDModel, kDModel, kActNone, kOutBf16, 1.0f));
+        glu_dwconv_kernel<<<dim3((max_t3 + kDwRows - 1) / kDwRows, n, kDModel / 256), 256, 0, st>>>(h, d_t3, L.dw_w,
+                                                                                                   L.dw_b, att);
+        ENC_CUDA(run_gemm(c, att, L.pw2_w, L.pw2_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
+        // x += 0.5 * FF2(LN x)
+        layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_ff2_g, L.ln_ff2_b, a, R3);
+        ENC_CUDA(run_gemm(c, a, L.ff2_w1, L.ff2_b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
+        ENC_CUDA(run_gemm(c, h, L.ff2_w2, L.ff2_b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
+        // x = LN_out(x); the last block writes straight into the caller's buffer
+        float* dst = (l == m.layers - 1) ? d_out + (size_t)enc_off_all[c0] * kDModel : x;
+        layernorm_kernel<true><<<ln_grid, 256, 0, st>>>(x, L.ln_out_g, L.ln_out_b, dst, R3);
+        c->launches += 7;
+    }
+    if (m.layers == 0)
+        ENC_CUDA(cudaMemcpyAsync(d_out + (size_t)enc_off_all[c0] * kDModel, x, (size_t)R3 * kDModel * sizeof(float),
+                                 cudaMemcpyDeviceToDevice, st));
+    return cudaGetLastError();
+}
+
+cudaError_t encoder_forward(sb_ctx* c, const Model& m, const float* d_feats, const int64_t* frame_off, int n_clips,
+                            float* d_out, int* enc_off, EncoderWorkspace& ws, size_t workspace_budget_bytes) {
+    enc_off[0] = 0;
+    for (int i = 0; i < n_clips; ++i)
+        enc_off[i + 1] = enc_off[i] + encoder_out_frames((int)(frame_off[i + 1] - frame_off[i]));
+    // group clips so that the largest intermediate (conv0 output: T/2 x 64 x 256 bf16 per clip) fits the budget
+    int c0 = 0;
+    while (c0 < n_clips) {
+        size_t bytes = 0;
+        int c1 = c0;
+        while (c1 < n_clips) {
+            const size_t T = (size_t)(frame_off[c1 + 1] - frame_off[c1]);
+            const size_t need = ((T + 1) / 2) * 64 * kSubC * sizeof(bf16) * 2;  // y0 plus the rest, roughly
+            if (c1 > c0 && bytes + need > workspace_budget_bytes) break;
+            bytes += need;
+            ++c1;
+        }
+        ENC_CUDA(encode_group(c, m, d_feats, frame_off, c0, c1, enc_off, d_out, ws));
+        c0 = c1;
+    }
+    return cudaSuccess;
+}
+
+}  // namespace sb

@@ -1,4 +1,265 @@
-// Model weights owned by a context (filled in by the encoder / decoder units).
-#include "context.h"
+// Model loading: named fp32 host tensors -> device-resident weights in the layouts the kernels use.
+//
+// Stands where the reference builds its model from a bundle (ParakeetModel::from_bundle,
+// src/model.rs:22-35; asset layout src/models.rs:5-8).  Tensor names are those of the published
+// FastConformer / Parakeet checkpoints ("subsampling.layers.0.weight", "layers.3.self_attn.q_proj.weight",
+// ...) plus "predictor.*" / "joint.*" for the TDT decoder.
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
 
-void sb_model_free_internal(sb_ctx* c) { (void)c; }
+#include "context.h"
+#include "encoder.h"
+#include "gemm.h"
+#include "model.h"
+
+namespace sb {
+
+namespace {
+
+struct Loader {
+    std::map<std::string, std::pair<const float*, int64_t>> t;
+    Model* m;
+    std::string err;
+
+    const float* get(const std::string& name, int64_t numel) {
+        auto it = t.find(name);
+        if (it == t.end()) {
+            if (err.empty()) err = "missing model asset: " + name;
+            return nullptr;
+        }
+        if (it->second.second != numel) {
+            if (err.empty())
+                err = "tensor " + name + " has " + std::to_string(it->second.second) + " elements, expected " +
+                      std::to_string(numel);
+            return nullptr;
+        }
+        return it->second.first;
+    }
+
+    void* dalloc(size_t bytes) {
+        void* p = nullptr;
+        if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess) {
+            if (err.empty()) err = "cudaMalloc failed while loading the model";
+            return nullptr;
+        }
+        m->allocations.push_back(p);
+        return p;
+    }
+
+    float* up_f32(const float* h, size_t n) {
+        if (!h) return nullptr;
+        float* d = static_cast<float*>(dalloc(n * sizeof(float)));
+        if (d && cudaMemcpy(d, h, n * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess && err.empty())
+            err = "cudaMemcpy failed while loading the model";
+        return d;
+    }
+
+    bf16* up_bf16(const float* h, size_t n) {
+        if (!h) return nullptr;
+        std::vector<bf16> tmp(n);
+        for (size_t i = 0; i < n; ++i) tmp[i] = __float2bfloat16(h[i]);
+        bf16* d = static_cast<bf16*>(dalloc(n * sizeof(bf16)));
+        if (d && cudaMemcpy(d, tmp.data(), n * sizeof(bf16), cudaMemcpyHostToDevice) != cudaSuccess && err.empty())
+            err = "cudaMemcpy failed while loading the model";
+        return d;
+    }
+
+    float* f32(const std::string& name, int64_t n) { return up_f32(get(name, n), (size_t)n); }
+    bf16* b16(const std::string& name, int64_t n) { return up_bf16(get(name, n), (size_t)n); }
+
+    // [C x 9] (channel-major, as conv weights are stored) -> tap-major [9 x C], optionally scaled per channel
+    float* tap_major(const float* h, int C, int taps, const std::vector<float>* scale) {
+        if (!h) return nullptr;
+        std::vector<float> tmp((size_t)C * taps);
+        for (int c = 0; c < C; ++c)
+            for (int k = 0; k < taps; ++k) tmp[(size_t)k * C + c] = h[(size_t)c * taps + k] * (scale ? (*scale)[c] : 1.0f);
+        return up_f32(tmp.data(), tmp.size());
+    }
+};
+
+}  // namespace
+
+void model_free(Model* m) {
+    if (!m) return;
+    for (void* p : m->allocations) cudaFree(p);
+    delete m;
+}
+
+// Fills the relative-position table: row p holds the sinusoidal embedding of relative position
+// (kMaxEncFrames - 1) - p, sin and cos interleaved over the 512 frequencies.
+static void build_pos_table(std::vector<float>& pos) {
+    pos.resize((size_t)kPosRows * kDModel);
+    for (int p = 0; p < kPosRows; ++p) {
+        const float r = (float)((kMaxEncFrames - 1) - p);
+        for (int i = 0; i < kDModel / 2; ++i) {
+            const float inv_freq = 1.0f / powf(10000.0f, (float)(2 * i) / (float)kDModel);
+            const float ang = r * inv_freq;
+            pos[(size_t)p * kDModel + 2 * i] = sinf(ang);
+            pos[(size_t)p * kDModel + 2 * i + 1] = cosf(ang);
+        }
+    }
+}
+
+int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensors, int64_t n_tensors) {
+    if (!c || !desc || (!tensors && n_tensors > 0)) return fail(SB_INVALID_ARGUMENT, "null argument");
+    if (desc->encoder_layers < 0 || desc->encoder_layers > 256) return fail(SB_INVALID_ARGUMENT, "bad layer count");
+    SB_CUDA(cudaSetDevice(c->device));
+    Model* m = new Model();
+    Loader ld;
+    ld.m = m;
+    for (int64_t i = 0; i < n_tensors; ++i) {
+        if (!tensors[i].name || !tensors[i].data) {
+            model_free(m);
+            return fail(SB_INVALID_ARGUMENT, "tensor entry with null name or data");
+        }
+        ld.t[tensors[i].name] = {tensors[i].data, tensors[i].numel};
+    }
+    m->layers = desc->encoder_layers;
+    m->xscale = desc->scale_input ? sqrtf((float)kDModel) : 1.0f;
+
+    if (desc->has_encoder) {
+        const int C = kSubC;
+        m->sub0_w = ld.f32("subsampling.layers.0.weight", C * 9);
+        m->sub0_b = ld.f32("subsampling.layers.0.bias", C);
+        m->dw1_w = ld.tap_major(ld.get("subsampling.layers.2.weight", C * 9), C, 9, nullptr);
+        m->dw1_b = ld.f32("subsampling.layers.2.bias", C);
+        m->pw1_w = ld.b16("subsampling.layers.3.weight", C * C);
+        m->pw1_b = ld.f32("subsampling.layers.3.bias", C);
+        m->dw2_w = ld.tap_major(ld.get("subsampling.layers.5.weight", C * 9), C, 9, nullptr);
+        m->dw2_b = ld.f32("subsampling.layers.5.bias", C);
+        m->pw2_w = ld.b16("subsampling.layers.6.weight", C * C);
+        m->pw2_b = ld.f32("subsampling.layers.6.bias", C);
+        // Linear over the flattened (channel-major c * 16 + f) features; our activations are (f * 256 + c).
+        if (const float* lw = ld.get("subsampling.linear.weight", (int64_t)kDModel * 16 * C)) {
+            std::vector<float> perm((size_t)kDModel * 16 * C);
+            for (int n = 0; n < kDModel; ++n)
+                for (int ch = 0; ch < C; ++ch)
+                    for (int f = 0; f < 16; ++f)
+                        perm[(size_t)n * 16 * C + f * C + ch] = lw[(size_t)n * 16 * C + ch * 16 + f];
+            m->lin_w = ld.up_bf16(perm.data(), perm.size());
+        }
+        m->lin_b = ld.f32("subsampling.linear.bias", kDModel);
+
+        std::vector<float> pos;
+        build_pos_table(pos);
+        bf16* d_pos = ld.up_bf16(pos.data(), pos.size());
+
+        m->L.resize(m->layers);
+        const int64_t d = kDModel, ff = kFF;
+        for (int l = 0; l < m->layers && ld.err.empty(); ++l) {
+            LayerWeights& L = m->L[l];
+            const std::string p = "layers." + std::to_string(l) + ".";
+            L.ln_ff1_g = ld.f32(p + "norm_feed_forward1.weight", d); L.ln_ff1_b = ld.f32(p + "norm_feed_forward1.bias", d);
+            L.ln_att_g = ld.f32(p + "norm_self_att.weight", d);      L.ln_att_b = ld.f32(p + "norm_self_att.bias", d);
+            L.ln_conv_g = ld.f32(p + "norm_conv.weight", d);         L.ln_conv_b = ld.f32(p + "norm_conv.bias", d);
+            L.ln_ff2_g = ld.f32(p + "norm_feed_forward2.weight", d); L.ln_ff2_b = ld.f32(p + "norm_feed_forward2.bias", d);
+            L.ln_out_g = ld.f32(p + "norm_out.weight", d);           L.ln_out_b = ld.f32(p + "norm_out.bias", d);
+            L.ff1_w1 = ld.b16(p + "feed_forward1.linear1.weight", ff * d); L.ff1_b1 = ld.f32(p + "feed_forward1.linear1.bias", ff);
+            L.ff1_w2 = ld.b16(p + "feed_forward1.linear2.weight", d * ff); L.ff1_b2 = ld.f32(p + "feed_forward1.linear2.bias", d);
+            L.ff2_w1 = ld.b16(p + "feed_forward2.linear1.weight", ff * d); L.ff2_b1 = ld.f32(p + "feed_forward2.linear1.bias", ff);
+            L.ff2_w2 = ld.b16(p + "feed_forward2.linear2.weight", d * ff); L.ff2_b2 = ld.f32(p + "feed_forward2.linear2.bias", d);
+            const float* qw = ld.get(p + "self_attn.q_proj.weight", d * d);
+            const float* kw = ld.get(p + "self_attn.k_proj.weight", d * d);
+            const float* vw = ld.get(p + "self_attn.v_proj.weight", d * d);
+            const float* qb = ld.get(p + "self_attn.q_proj.bias", d);
+            const float* kb = ld.get(p + "self_attn.k_proj.bias", d);
+            const float* vb = ld.get(p + "self_attn.v_proj.bias", d);
+            if (qw && kw && vw && qb && kb && vb) {
+                std::vector<float> w3((size_t)3 * d * d), b3((size_t)3 * d);
+                std::memcpy(w3.data(), qw, sizeof(float) * d * d);
+                std::memcpy(w3.data() + d * d, kw, sizeof(float) * d * d);
+                std::memcpy(w3.data() + 2 * d * d, vw, sizeof(float) * d * d);
+                std::memcpy(b3.data(), qb, sizeof(float) * d);
+                std::memcpy(b3.data() + d, kb, sizeof(float) * d);
+                std::memcpy(b3.data() + 2 * d, vb, sizeof(float) * d);
+                L.qkv_w = ld.up_bf16(w3.data(), w3.size());
+                L.qkv_b = ld.up_f32(b3.data(), b3.size());
+            }
+            L.o_w = ld.b16(p + "self_attn.o_proj.weight", d * d);
+            L.o_b = ld.f32(p + "self_attn.o_proj.bias", d);
+            L.bias_u = ld.f32(p + "self_attn.bias_u", d);
+            L.bias_v = ld.f32(p + "self_attn.bias_v", d);
+            // position projection W_r * pos for every relative position, once
+            bf16* wr = ld.b16(p + "self_attn.relative_k_proj.weight", d * d);
+            L.pos_proj = static_cast<bf16*>(ld.dalloc((size_t)kPosRows * d * sizeof(bf16)));
+            if (wr && L.pos_proj && d_pos) {
+                GemmArgs g{};
+                g.a = d_pos; g.w = wr; g.out = L.pos_proj; g.M = kPosRows; g.N = (int)d; g.K = (int)d; g.ldo = (int)d;
+                g.act = kActNone; g.out_mode = kOutBf16; g.alpha = 1.0f;
+                cudaError_t e = gemm_launch(g, c->sm_count, c->d_error, c->stream);
+                if (e != cudaSuccess && ld.err.empty()) ld.err = std::string("position projection failed: ") + cudaGetErrorString(e);
+            }
+            L.pw1_w = ld.b16(p + "conv.pointwise_conv1.weight", 2 * d * d);
+            L.pw1_b = ld.f32(p + "conv.pointwise_conv1.bias", 2 * d);
+            L.pw2_w = ld.b16(p + "conv.pointwise_conv2.weight", d * d);
+            L.pw2_b = ld.f32(p + "conv.pointwise_conv2.bias", d);
+            // fold BatchNorm (eval) into the depthwise taps and bias
+            const float* dw = ld.get(p + "conv.depthwise_conv.weight", d * kConvK);
+            const float* db = ld.get(p + "conv.depthwise_conv.bias", d);
+            const float* g = ld.get(p + "conv.norm.weight", d);
+            const float* be = ld.get(p + "conv.norm.bias", d);
+            const float* mu = ld.get(p + "conv.norm.running_mean", d);
+            const float* var = ld.get(p + "conv.norm.running_var", d);
+            if (dw && db && g && be && mu && var) {
+                std::vector<float> scale(d), shift(d);
+                for (int64_t ch = 0; ch < d; ++ch) {
+                    scale[ch] = g[ch] / sqrtf(var[ch] + 1e-5f);
+                    shift[ch] = (db[ch] - mu[ch]) * scale[ch] + be[ch];
+                }
+                L.dw_w = ld.tap_major(dw, (int)d, kConvK, &scale);
+                L.dw_b = ld.up_f32(shift.data(), shift.size());
+            }
+        }
+        m->has_encoder = true;
+    }
+
+    if (desc->has_decoder && ld.err.empty()) {
+        const int64_t H = kPredHidden, G = 4 * H, Lr = kPredLayers, J = kJointDim;
+        m->embedding = ld.f32("predictor.embedding", (int64_t)kVocab * H);
+        m->w_ih = ld.f32("predictor.lstm.weight_ih", Lr * G * H);
+        m->w_hh = ld.f32("predictor.lstm.weight_hh", Lr * G * H);
+        const float* bi = ld.get("predictor.lstm.bias_ih", Lr * G);
+        const float* bh = ld.get("predictor.lstm.bias_hh", Lr * G);
+        if (bi && bh) {
+            std::vector<float> bsum((size_t)(Lr * G));
+            for (size_t i = 0; i < bsum.size(); ++i) bsum[i] = bi[i] + bh[i];
+            m->b_gates = ld.up_f32(bsum.data(), bsum.size());
+        }
+        m->w_enc = ld.f32("joint.enc.weight", J * kDModel);
+        m->enc_proj_w = ld.b16("joint.enc.weight", J * kDModel);
+        m->b_enc = ld.f32("joint.enc.bias", J);
+        m->w_pred = ld.f32("joint.pred.weight", J * H);
+        m->b_pred = ld.f32("joint.pred.bias", J);
+        m->w_out = ld.f32("joint.out.weight", (int64_t)kJointOut * J);
+        m->b_out = ld.f32("joint.out.bias", kJointOut);
+        m->has_decoder = true;
+    }
+
+    cudaError_t se = cudaStreamSynchronize(c->stream);
+    if (!ld.err.empty() || se != cudaSuccess) {
+        const bool missing = ld.err.rfind("missing model asset", 0) == 0;
+        std::string msg = ld.err.empty() ? std::string("CUDA error: ") + cudaGetErrorString(se) : ld.err;
+        model_free(m);
+        return fail(missing ? SB_MISSING_MODEL_ASSET : (se != cudaSuccess ? SB_CUDA_ERROR : SB_INVALID_MODEL_OUTPUT), msg);
+    }
+    if (c->model) model_free(c->model);
+    c->model = m;
+    return SB_OK;
+}
+
+}  // namespace sb
+
+void sb_model_free_internal(sb_ctx* c) {
+    if (c && c->model) {
+        sb::model_free(c->model);
+        c->model = nullptr;
+    }
+    if (c && c->enc_ws) {
+        c->enc_ws->release();
+        delete c->enc_ws;
+        c->enc_ws = nullptr;
+    }
+}

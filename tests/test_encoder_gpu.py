@@ -1,0 +1,86 @@
+"""CUDA FastConformer encoder (through the C ABI) against the fp32 CPU oracle, same seeded weights.
+
+Tolerance: relative L2 error <= 2e-2 on the encoder output for the bf16 path."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+from oracle import encoder_oracle as eo
+
+BF16_TOL = 2e-2
+
+
+def run_gpu(ctx, feats_list):
+    import scriptrs_b200 as sb
+
+    fo = np.zeros(len(feats_list) + 1, np.int64)
+    fo[1:] = np.cumsum([f.shape[0] for f in feats_list])
+    d_feats = torch.from_numpy(np.concatenate(feats_list)).cuda()
+    n_out = sum(sb.encoder_num_frames(f.shape[0]) for f in feats_list)
+    d_out = torch.full((n_out, 1024), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    offs = sb.encode_device(ctx, d_feats.data_ptr(), fo, d_out.data_ptr())
+    ctx.synchronize()
+    out = d_out.cpu().numpy()
+    return [out[offs[i]:offs[i + 1]] for i in range(len(feats_list))]
+
+
+@pytest.mark.parametrize("layers", [0, 1, 2])
+def test_shallow_stacks_match_oracle(ctx, layers):
+    import scriptrs_b200 as sb
+
+    cfg = eo.EncoderConfig(layers=layers)
+    w = eo.seeded_weights(cfg, seed=11, std=0.02, plain_norms=False)
+    sb.load_model(ctx, w, encoder_layers=layers)
+    rng = np.random.default_rng(layers)
+    feats = [rng.standard_normal((t, 128)).astype(np.float32) for t in (203, 1001, 9, 64, 1497, 1)]
+    got = run_gpu(ctx, feats)
+    for f, g in zip(feats, got):
+        r = eo.encoder_forward(w, f, cfg)
+        assert g.shape == r.shape == (eo.subsampled_length(f.shape[0]), 1024)
+        assert np.isfinite(g).all()
+        err = np.linalg.norm(g - r) / np.linalg.norm(r)
+        assert err <= BF16_TOL, (layers, f.shape[0], err)
+
+
+def test_scale_input_and_batch_independence(ctx):
+    import scriptrs_b200 as sb
+
+    cfg = eo.EncoderConfig(layers=1, scale_input=True)
+    w = eo.seeded_weights(cfg, seed=12, std=0.02, plain_norms=False)
+    sb.load_model(ctx, w, encoder_layers=1, scale_input=True)
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((333, 128)).astype(np.float32)
+    b = rng.standard_normal((120, 128)).astype(np.float32)
+    alone = run_gpu(ctx, [a])[0]
+    together = run_gpu(ctx, [b, a, b])
+    assert np.array_equal(alone, together[1])       # a clip's result does not depend on its neighbours
+    assert np.array_equal(together[0], together[2])
+    r = eo.encoder_forward(w, a, cfg)
+    assert np.linalg.norm(alone - r) / np.linalg.norm(r) <= BF16_TOL
+
+
+def test_missing_tensor_is_reported(ctx):
+    import scriptrs_b200 as sb
+
+    cfg = eo.EncoderConfig(layers=1)
+    w = eo.seeded_weights(cfg, seed=1)
+    del w["layers.0.conv.norm.running_var"]
+    with pytest.raises(sb.ScriptrsError) as e:
+        sb.load_model(ctx, w, encoder_layers=1)
+    assert e.value.status == 3 and "running_var" in e.value.message
+
+
+def test_too_many_feature_frames_is_rejected(ctx):
+    import scriptrs_b200 as sb
+
+    cfg = eo.EncoderConfig(layers=0)
+    sb.load_model(ctx, eo.seeded_weights(cfg, seed=1), encoder_layers=0)
+    d = torch.zeros(1502, 128, device="cuda")
+    o = torch.zeros(200, 1024, device="cuda")
+    with pytest.raises(sb.ScriptrsError) as e:
+        sb.encode_device(ctx, d.data_ptr(), np.array([0, 1502], np.int64), o.data_ptr())
+    assert e.value.status == 6
