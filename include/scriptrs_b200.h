@@ -178,6 +178,28 @@ int64_t sb_encoder_num_frames(int64_t feature_frames);
 int32_t sb_encode_device(sb_ctx* ctx, const float* d_feats, const int64_t* frame_offsets, int64_t n_clips,
                          float* d_out, int64_t* enc_offsets);
 
+/* ----------------------------------------------------------------- decode */
+
+/* Batched ParakeetModel::greedy_decode (src/model.rs:64-95) with the state machine of
+ * GreedyDecodeState (src/model.rs:98-214); the predictor (run_decoder, src/model.rs:344-364) and the
+ * joint decision (run_joint, src/model.rs:366-384: token arg-max over 1025, duration arg-max over 5,
+ * confidence = max softmax) run inside one persistent kernel for the whole batch.
+ *   d_enc         device, packed [sum_i T'_i x 1024] f32, time-major per clip
+ *   enc_offsets   host, n_clips + 1 prefix sums of T'_i
+ *   max_tokens    capacity per clip of the four output arrays (host, [n_clips x max_tokens]);
+ *                 a clip can emit at most 10 * T' tokens
+ *   n_tokens      host [n_clips]: tokens emitted per clip (RawTranscription lengths)
+ *   logits_trace  optional host [n_clips x trace_cap x 1030]: the joint logits of every loop
+ *                 iteration, for replaying the reference's control flow; n_steps (optional, host
+ *                 [n_clips]) receives the iterations per clip
+ * frame_indices are encoder-frame indices local to the clip, recorded before the advance
+ * (src/model.rs:190-193).  Blocking: results are on the host when the call returns.
+ * SB_BUFFER_TOO_SMALL if a clip emitted more than max_tokens. */
+int32_t sb_tdt_decode_device(sb_ctx* ctx, const float* d_enc, const int64_t* enc_offsets, int64_t n_clips,
+                             int64_t max_tokens, uint32_t* token_ids, int64_t* frame_indices, int64_t* durations,
+                             float* confidences, int64_t* n_tokens, float* logits_trace, int64_t trace_cap,
+                             int64_t* n_steps);
+
 /* ------------------------------------------------------------------ GEMM */
 
 /* Tensor-core GEMM building block of the encoder: out = epilogue(A[M x K] * W[N x K]^T).

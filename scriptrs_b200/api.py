@@ -172,3 +172,33 @@ def encode_device(ctx: Context, d_feats: int, frame_offsets: np.ndarray, d_out: 
     check(_lib.lib().sb_encode_device(ctx.handle, C.c_void_p(d_feats), _ptr(frame_offsets), n, C.c_void_p(d_out),
                                       _ptr(eo)))
     return eo
+
+
+def tdt_decode_device(ctx: Context, d_enc: int, enc_offsets: np.ndarray, max_tokens: int | None = None,
+                      trace_cap: int = 0):
+    """Greedy TDT decode of packed encoder output on the device.  Returns a list of dicts
+    (tokens, frames, durations, conf[, logits, steps]) per clip, like the reference's RawTranscription."""
+    enc_offsets = np.ascontiguousarray(enc_offsets, np.int64)
+    n = enc_offsets.size - 1
+    lens = np.diff(enc_offsets)
+    if max_tokens is None:
+        max_tokens = int(max(1, MAX_TOKENS_PER_STEP * int(lens.max(initial=1))))
+    tok = np.zeros((n, max_tokens), np.uint32)
+    frm = np.zeros((n, max_tokens), np.int64)
+    dur = np.zeros((n, max_tokens), np.int64)
+    conf = np.zeros((n, max_tokens), np.float32)
+    cnt = np.zeros(n, np.int64)
+    steps = np.zeros(n, np.int64)
+    trace = np.zeros((n, trace_cap, 1030), np.float32) if trace_cap else None
+    check(_lib.lib().sb_tdt_decode_device(ctx.handle, C.c_void_p(d_enc), _ptr(enc_offsets), n, max_tokens, _ptr(tok),
+                                          _ptr(frm), _ptr(dur), _ptr(conf), _ptr(cnt), _ptr(trace), trace_cap,
+                                          _ptr(steps)))
+    out = []
+    for i in range(n):
+        k = int(cnt[i])
+        d = dict(tokens=tok[i, :k].copy(), frames=frm[i, :k].copy(), durations=dur[i, :k].copy(),
+                 conf=conf[i, :k].copy(), steps=int(steps[i]))
+        if trace is not None:
+            d["logits"] = trace[i, : int(steps[i])]
+        out.append(d)
+    return out

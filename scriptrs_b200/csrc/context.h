@@ -34,6 +34,7 @@ struct Buffer {
 
 struct Model;             // encoder + predictor + joint weights (model.h)
 struct EncoderWorkspace;  // encoder.h
+struct DecodeWorkspace;   // pipeline.cu
 int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensors, int64_t n_tensors);
 
 }  // namespace sb
@@ -50,5 +51,6 @@ struct sb_ctx {
     sb::Buffer clip_off, frame_off, col_mean, col_std, pcm_stage, feat_stage;
     sb::Model* model = nullptr;
     sb::EncoderWorkspace* enc_ws = nullptr;
+    sb::DecodeWorkspace* dec_ws = nullptr;
     size_t workspace_budget = (size_t)12 << 30;  // bytes of encoder intermediates per group of clips
 };

@@ -14,6 +14,7 @@
 #include "encoder.h"
 #include "gemm.h"
 #include "model.h"
+#include "pipeline.h"
 
 namespace sb {
 
@@ -257,6 +258,7 @@ void sb_model_free_internal(sb_ctx* c) {
         sb::model_free(c->model);
         c->model = nullptr;
     }
+    sb::decode_workspace_free(c);
     if (c && c->enc_ws) {
         c->enc_ws->release();
         delete c->enc_ws;
