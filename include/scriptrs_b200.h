@@ -200,6 +200,108 @@ int32_t sb_tdt_decode_device(sb_ctx* ctx, const float* d_enc, const int64_t* enc
                              float* confidences, int64_t* n_tokens, float* logits_trace, int64_t trace_cap,
                              int64_t* n_steps);
 
+/* -------------------------------------------------------- long-form host logic */
+
+/* OverlapChunkConfig::{chunk,overlap,stride}_samples (src/long_form/planner.rs:104-122):
+ * 238080 / 32000 / 206080 with the defaults. */
+int64_t sb_overlap_chunk_samples(const sb_overlap_config* cfg);
+int64_t sb_overlap_overlap_samples(const sb_overlap_config* cfg);
+int64_t sb_overlap_stride_samples(const sb_overlap_config* cfg);
+
+/* build_fast_execution_plan (src/long_form.rs:439-459): OverlapChunkConfig::plan
+ * (src/long_form/planner.rs:124-136) followed by push_overlap_task (src/long_form.rs:566-582), which
+ * prepends up to context_samples of left context to every chunk but the first.  *n_tasks receives
+ * the task count; tasks may be NULL to size the buffer. */
+int32_t sb_plan_fast(const sb_overlap_config* cfg, int64_t audio_len, sb_chunk_task* tasks, int64_t cap,
+                     int64_t* n_tasks);
+
+/* parallel_worker_count (src/long_form.rs:594-600). */
+int64_t sb_parallel_worker_count(int64_t task_count, int64_t requested_workers);
+
+/* apply_time_offsets (src/pipeline.rs:219-252), in place on the four arrays; *n_out = tokens kept. */
+int32_t sb_apply_time_offsets(uint32_t* token_ids, int64_t* frame_indices, int64_t* durations, float* confidences,
+                              int64_t n, int64_t frame_offset, int64_t context_frames, int64_t* n_out);
+
+/* merge_overlapping_windows (src/long_form/merge.rs:3-13): left fold over the windows in order.
+ * Window w is elements [win_off[w], win_off[w+1]) of the input arrays.  Same result as the
+ * reference; cost proportional to the overlaps, not to the transcript length. */
+int32_t sb_merge_windows(const uint32_t* token_ids, const int64_t* frame_indices, const int64_t* durations,
+                         const float* confidences, const int64_t* win_off, int64_t n_windows, uint32_t* out_token_ids,
+                         int64_t* out_frame_indices, int64_t* out_durations, float* out_confidences, int64_t out_cap,
+                         int64_t* n_out);
+
+/* ----------------------------------------------------------- vocabulary and text */
+
+typedef struct sb_vocab sb_vocab;
+typedef struct sb_result sb_result;       /* TranscriptionResult (src/types.rs:28-49) */
+typedef struct sb_raw_batch sb_raw_batch; /* one RawTranscription (src/decode.rs:6-11) per task */
+
+/* Vocabulary::from_file (src/vocab.rs:15-52): lines "<token> <id>"; the blank is the id of "<blk>" /
+ * "<blank>", else the last id.  SB_IO if the file cannot be read, SB_INVALID_VOCABULARY if malformed. */
+int32_t sb_vocab_load(const char* path, sb_vocab** out);
+int32_t sb_vocab_from_text(const char* text, int64_t len, sb_vocab** out);
+void sb_vocab_free(sb_vocab* vocab);
+int64_t sb_vocab_size(const sb_vocab* vocab);
+int64_t sb_vocab_blank_id(const sb_vocab* vocab); /* Vocabulary::blank_id (src/vocab.rs:58-60) */
+
+/* ParakeetTdtDecoder::decode (src/decode.rs:39-104).  confidences may hold fewer than n entries
+ * (missing ones read as 0, src/decode.rs:80). */
+int32_t sb_text_decode(const sb_vocab* vocab, const uint32_t* token_ids, const int64_t* frame_indices,
+                       const float* confidences, int64_t n, int64_t n_confidences, double duration_seconds,
+                       sb_result** out);
+
+/* TranscriptionResult accessors; strings stay valid until sb_result_free. */
+const char* sb_result_text(const sb_result* r);
+double sb_result_duration(const sb_result* r);
+int64_t sb_result_num_tokens(const sb_result* r);
+int64_t sb_result_num_chunks(const sb_result* r);
+int32_t sb_result_token(const sb_result* r, int64_t i, uint32_t* token_id, const char** text, double* start,
+                        double* end, float* confidence); /* TimedToken (src/types.rs:1-14) */
+int32_t sb_result_chunk(const sb_result* r, int64_t i, double* start, double* end,
+                        const char** text);               /* TranscriptChunk (src/types.rs:16-26) */
+void sb_result_free(sb_result* r);
+
+int64_t sb_raw_batch_size(const sb_raw_batch* b);
+int32_t sb_raw_batch_get(const sb_raw_batch* b, int64_t i, int64_t* n, const uint32_t** token_ids,
+                         const int64_t** frame_indices, const int64_t** durations, const float** confidences);
+void sb_raw_batch_free(sb_raw_batch* b);
+
+/* ------------------------------------------------------------------ pipelines */
+
+/* transcribe_task (src/long_form.rs:584-592) for a whole list of tasks at once: ChunkPreparer::prepare
+ * (src/pipeline.rs:200-216) + transcribe_prepared_raw (src/pipeline.rs:121-138), i.e. frontend ->
+ * encoder -> greedy decode -> apply_time_offsets, batched on this context's GPU.  `audio` is the whole
+ * recording in host memory (pinned memory makes the copy faster); task i covers
+ * audio[audio_start, audio_end).  An empty task fails with SB_EMPTY_AUDIO, one longer than
+ * cfg->max_audio_samples with SB_AUDIO_TOO_LONG.  cfg may be NULL for the defaults. */
+int32_t sb_transcribe_chunks(sb_ctx* ctx, const float* audio, int64_t n_samples, const sb_chunk_task* tasks,
+                             int64_t n_tasks, const sb_transcription_config* cfg, sb_raw_batch** out);
+
+/* TranscriptionPipeline::run_with_config (src/pipeline.rs:81-89): one chunk of at most
+ * cfg->max_audio_samples samples (SB_AUDIO_TOO_LONG beyond, SB_EMPTY_AUDIO if empty). */
+int32_t sb_pipeline_run(sb_ctx* ctx, const sb_vocab* vocab, const float* audio, int64_t n_samples,
+                        const sb_transcription_config* cfg, sb_result** out);
+
+/* LongFormTranscriptionPipeline::run_with_config (src/long_form.rs:153-166), Fast mode: audio of at
+ * most max_audio_samples goes through the single-chunk path, longer audio is planned into overlap
+ * chunks, transcribed on this GPU, merged and decoded (src/long_form.rs:218-245,344-419). */
+int32_t sb_longform_run(sb_ctx* ctx, const sb_vocab* vocab, const float* audio, int64_t n_samples,
+                        const sb_longform_config* cfg, sb_result** out);
+
+/* The same over several GPUs of one process: run_parallel_regions (src/long_form.rs:266-314) with
+ * min(worker_count, n_ctx, tasks) workers, each worker being one context's GPU with its own host
+ * thread; tasks are dealt in contiguous blocks and results are reassembled in task order
+ * (src/long_form.rs:316-342).  The first failing worker fails the call. */
+int32_t sb_longform_run_multi(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio,
+                              int64_t n_samples, const sb_longform_config* cfg, sb_result** out);
+
+/* Tail of the long-form path for callers that ran sb_transcribe_chunks themselves (one process per
+ * GPU): decode_overlap_tasks + build_chunk + build_result (src/long_form.rs:404-419,622-647) over
+ * the per-task token streams, concatenated in task order. */
+int32_t sb_longform_finish(const sb_vocab* vocab, int64_t audio_len, const uint32_t* token_ids,
+                           const int64_t* frame_indices, const int64_t* durations, const float* confidences,
+                           const int64_t* win_off, int64_t n_windows, sb_result** out);
+
 /* ------------------------------------------------------------------ GEMM */
 
 /* Tensor-core GEMM building block of the encoder: out = epilogue(A[M x K] * W[N x K]^T).

@@ -74,6 +74,36 @@ SIGNATURES = {
     "sb_encoder_num_frames": (_I64, [_I64]),
     "sb_encode_device": (_I32, [_VP, _VP, _VP, _I64, _VP, _VP]),
     "sb_tdt_decode_device": (_I32, [_VP, _VP, _VP, _I64, _I64, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _VP]),
+    "sb_overlap_chunk_samples": (_I64, [C.POINTER(OverlapConfigC)]),
+    "sb_overlap_overlap_samples": (_I64, [C.POINTER(OverlapConfigC)]),
+    "sb_overlap_stride_samples": (_I64, [C.POINTER(OverlapConfigC)]),
+    "sb_plan_fast": (_I32, [C.POINTER(OverlapConfigC), _I64, _VP, _I64, C.POINTER(_I64)]),
+    "sb_parallel_worker_count": (_I64, [_I64, _I64]),
+    "sb_apply_time_offsets": (_I32, [_VP, _VP, _VP, _VP, _I64, _I64, _I64, C.POINTER(_I64)]),
+    "sb_merge_windows": (_I32, [_VP, _VP, _VP, _VP, _VP, _I64, _VP, _VP, _VP, _VP, _I64, C.POINTER(_I64)]),
+    "sb_vocab_load": (_I32, [C.c_char_p, C.POINTER(_VP)]),
+    "sb_vocab_from_text": (_I32, [C.c_char_p, _I64, C.POINTER(_VP)]),
+    "sb_vocab_free": (None, [_VP]),
+    "sb_vocab_size": (_I64, [_VP]),
+    "sb_vocab_blank_id": (_I64, [_VP]),
+    "sb_text_decode": (_I32, [_VP, _VP, _VP, _VP, _I64, _I64, C.c_double, C.POINTER(_VP)]),
+    "sb_result_text": (C.c_char_p, [_VP]),
+    "sb_result_duration": (C.c_double, [_VP]),
+    "sb_result_num_tokens": (_I64, [_VP]),
+    "sb_result_num_chunks": (_I64, [_VP]),
+    "sb_result_token": (_I32, [_VP, _I64, C.POINTER(C.c_uint32), C.POINTER(C.c_char_p), C.POINTER(C.c_double),
+                               C.POINTER(C.c_double), C.POINTER(C.c_float)]),
+    "sb_result_chunk": (_I32, [_VP, _I64, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_char_p)]),
+    "sb_result_free": (None, [_VP]),
+    "sb_raw_batch_size": (_I64, [_VP]),
+    "sb_raw_batch_get": (_I32, [_VP, _I64, C.POINTER(_I64), C.POINTER(_VP), C.POINTER(_VP), C.POINTER(_VP),
+                                C.POINTER(_VP)]),
+    "sb_raw_batch_free": (None, [_VP]),
+    "sb_transcribe_chunks": (_I32, [_VP, _VP, _I64, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),
+    "sb_pipeline_run": (_I32, [_VP, _VP, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),
+    "sb_longform_run": (_I32, [_VP, _VP, _VP, _I64, C.POINTER(LongFormConfigC), C.POINTER(_VP)]),
+    "sb_longform_run_multi": (_I32, [C.POINTER(_VP), _I64, _VP, _VP, _I64, C.POINTER(LongFormConfigC), C.POINTER(_VP)]),
+    "sb_longform_finish": (_I32, [_VP, _I64, _VP, _VP, _VP, _VP, _VP, _I64, C.POINTER(_VP)]),
     "sb_gemm": (_I32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I64, _I64, _I32, _I32, _I32, C.c_float]),
 }
 

@@ -9,6 +9,7 @@
 #include "encoder.h"
 #include "gemm.h"
 #include "model.h"
+#include "pipeline.h"
 
 namespace sb {
 
@@ -54,6 +55,43 @@ void Buffer::release() {
 using namespace sb;
 
 void sb_model_free_internal(sb_ctx*);
+
+namespace sb {
+
+// Shared by the public frontend entry points and the chunk pipeline.  Asynchronous on the stream.
+int32_t frontend_run(sb_ctx* c, const float* d_pcm, const int64_t* clip_start, const int64_t* clip_len,
+                     int64_t n_clips, float preemphasis, bool normalize, float* d_feats, int64_t* frame_offsets) {
+    if (n_clips > 65535) return fail(SB_INVALID_ARGUMENT, "at most 65535 clips per call");
+    const size_t n1 = static_cast<size_t>(n_clips) + 1;
+    std::vector<int64_t> meta(3 * n1);  // starts | lens | frame prefix sums
+    int64_t* fo = meta.data() + 2 * n1;
+    fo[0] = 0;
+    int64_t max_frames = 0;
+    for (int64_t i = 0; i < n_clips; ++i) {
+        if (clip_len[i] <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // frontend.rs:105
+        meta[i] = clip_start[i];
+        meta[n1 + i] = clip_len[i];
+        const int64_t t = frames_for_samples(clip_len[i]);
+        fo[i + 1] = fo[i] + t;
+        if (t > max_frames) max_frames = t;
+    }
+    if (max_frames > (int64_t)65535 * 32) return fail(SB_INVALID_ARGUMENT, "clip too long for one launch");
+    if (frame_offsets) std::memcpy(frame_offsets, fo, sizeof(int64_t) * n1);
+    SB_CUDA(cudaSetDevice(c->device));
+    SB_CUDA(c->clip_off.ensure(sizeof(int64_t) * 3 * n1));
+    SB_CUDA(c->col_mean.ensure(sizeof(float) * kMels * static_cast<size_t>(n_clips)));
+    SB_CUDA(c->col_std.ensure(sizeof(float) * kMels * static_cast<size_t>(n_clips)));
+    // pageable source: the copy is staged before the call returns, so the vector may go out of scope
+    SB_CUDA(cudaMemcpyAsync(c->clip_off.p, meta.data(), sizeof(int64_t) * 3 * n1, cudaMemcpyHostToDevice, c->stream));
+    const int64_t* d_meta = c->clip_off.as<int64_t>();
+    SB_CUDA(frontend_launch(d_pcm, d_meta, d_meta + n1, d_meta + 2 * n1, (int)n_clips, (int)max_frames, preemphasis,
+                            c->d_tables, d_feats, c->col_mean.as<float>(), c->col_std.as<float>(), normalize,
+                            c->stream));
+    c->launches += normalize ? 3 : 1;
+    return SB_OK;
+}
+
+}  // namespace sb
 
 extern "C" {
 
@@ -150,6 +188,7 @@ void sb_ctx_destroy(sb_ctx* c) {
     c->col_std.release();
     c->pcm_stage.release();
     c->feat_stage.release();
+    c->enc_stage.release();
     if (c->d_tables) cudaFree(c->d_tables);
     if (c->d_error) cudaFree(c->d_error);
     if (c->own_stream) cudaStreamDestroy(c->own_stream);
@@ -189,34 +228,13 @@ int32_t sb_frontend_device(sb_ctx* c, const float* d_pcm, const int64_t* clip_of
                            float preemphasis, int32_t normalize, float* d_feats, int64_t* frame_offsets) {
     if (!c || !clip_offsets || !d_pcm || !d_feats) return fail(SB_INVALID_ARGUMENT, "null argument");
     if (n_clips <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");
-    if (n_clips > 65535) return fail(SB_INVALID_ARGUMENT, "at most 65535 clips per call");
-    std::vector<int64_t> fo(static_cast<size_t>(n_clips) + 1);
-    fo[0] = 0;
-    int64_t max_frames = 0;
+    std::vector<int64_t> start(static_cast<size_t>(n_clips)), len(static_cast<size_t>(n_clips));
     for (int64_t i = 0; i < n_clips; ++i) {
-        const int64_t n = clip_offsets[i + 1] - clip_offsets[i];
-        if (n <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // frontend.rs:105
-        const int64_t t = frames_for_samples(n);
-        fo[i + 1] = fo[i] + t;
-        if (t > max_frames) max_frames = t;
+        start[i] = clip_offsets[i];
+        len[i] = clip_offsets[i + 1] - clip_offsets[i];
     }
-    if (max_frames > (int64_t)65535 * 32) return fail(SB_INVALID_ARGUMENT, "clip too long for one launch");
-    if (frame_offsets) std::memcpy(frame_offsets, fo.data(), sizeof(int64_t) * fo.size());
-    SB_CUDA(cudaSetDevice(c->device));
-    const size_t off_bytes = sizeof(int64_t) * (static_cast<size_t>(n_clips) + 1);
-    SB_CUDA(c->clip_off.ensure(off_bytes));
-    SB_CUDA(c->frame_off.ensure(off_bytes));
-    SB_CUDA(c->col_mean.ensure(sizeof(float) * kMels * static_cast<size_t>(n_clips)));
-    SB_CUDA(c->col_std.ensure(sizeof(float) * kMels * static_cast<size_t>(n_clips)));
-    SB_CUDA(cudaMemcpyAsync(c->clip_off.p, clip_offsets, off_bytes, cudaMemcpyHostToDevice, c->stream));
-    SB_CUDA(cudaMemcpyAsync(c->frame_off.p, fo.data(), off_bytes, cudaMemcpyHostToDevice, c->stream));
-    // The offset vectors are pageable host memory: the copies above have staged them
-    // before returning, so the call stays asynchronous on the context's stream.
-    SB_CUDA(frontend_launch(d_pcm, c->clip_off.as<int64_t>(), c->frame_off.as<int64_t>(), (int)n_clips,
-                            (int)max_frames, preemphasis, c->d_tables, d_feats, c->col_mean.as<float>(),
-                            c->col_std.as<float>(), normalize != 0, c->stream));
-    c->launches += normalize ? 3 : 1;
-    return SB_OK;
+    return frontend_run(c, d_pcm, start.data(), len.data(), n_clips, preemphasis, normalize != 0, d_feats,
+                        frame_offsets);
 }
 
 int32_t sb_frontend_host(sb_ctx* c, const float* pcm, const int64_t* clip_offsets, int64_t n_clips,

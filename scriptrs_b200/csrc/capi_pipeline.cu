@@ -1,0 +1,361 @@
+// extern "C" layer, part 2: host logic (planner, offsets, merge, text), result objects and the
+// chunk / single-chunk / long-form pipelines.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "context.h"
+#include "encoder.h"
+#include "host/longform.h"
+#include "model.h"
+#include "pipeline.h"
+
+struct sb_vocab { sb::Vocabulary v; };
+struct sb_result { sb::TranscriptionResult r; };
+struct sb_raw_batch { std::vector<sb::RawTokens> items; };
+
+namespace sb {
+
+namespace {
+
+RawTokens raw_from_arrays(const uint32_t* tok, const int64_t* frm, const int64_t* dur, const float* conf, int64_t a,
+                          int64_t b) {
+    RawTokens r;
+    r.token_ids.assign(tok + a, tok + b);
+    r.frame_indices.assign(frm + a, frm + b);
+    r.durations.assign(dur + a, dur + b);
+    r.confidences.assign(conf + a, conf + b);
+    return r;
+}
+
+// Frontend -> encoder -> decoder for a set of tasks over one host PCM buffer; the reference's
+// transcribe_task (src/long_form.rs:584-592) for a whole batch at once.
+int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const sb_chunk_task* tasks, int64_t n_tasks,
+                         const sb_transcription_config& cfg, std::vector<RawTokens>* out) {
+    out->clear();
+    if (n_tasks == 0) return SB_OK;
+    if (!c->model || !c->model->has_encoder || !c->model->has_decoder)
+        return fail(SB_MISSING_MODEL_ASSET, "encoder and decoder weights must be loaded first");
+    int64_t lo = n_samples, hi = 0;
+    for (int64_t i = 0; i < n_tasks; ++i) {
+        const sb_chunk_task& t = tasks[i];
+        if (t.audio_start < 0 || t.audio_end > n_samples || t.audio_end < t.audio_start)
+            return fail(SB_INVALID_ARGUMENT, "task range outside the audio");
+        const int64_t len = t.audio_end - t.audio_start;
+        if (len == 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // pipeline.rs:202
+        if (len > cfg.max_audio_samples) {                                      // pipeline.rs:205-210
+            char msg[160];
+            std::snprintf(msg, sizeof msg, "audio exceeds the single-chunk limit: actual=%.2fs max=%.2fs",
+                          (double)len / (double)cfg.sample_rate, (double)cfg.max_audio_samples / (double)cfg.sample_rate);
+            return fail(SB_AUDIO_TOO_LONG, msg);
+        }
+        lo = std::min(lo, t.audio_start);
+        hi = std::max(hi, t.audio_end);
+    }
+    SB_CUDA(cudaSetDevice(c->device));
+    cudaStream_t st = c->stream;
+    // PCM span of this batch -> device
+    SB_CUDA(c->pcm_stage.ensure(sizeof(float) * (size_t)(hi - lo)));
+    SB_CUDA(cudaMemcpyAsync(c->pcm_stage.p, pcm + lo, sizeof(float) * (size_t)(hi - lo), cudaMemcpyHostToDevice, st));
+    std::vector<int64_t> start(n_tasks), len(n_tasks), fo(n_tasks + 1), eo(n_tasks + 1);
+    int64_t frames = 0, enc_rows = 0, max_enc = 0;
+    for (int64_t i = 0; i < n_tasks; ++i) {
+        start[i] = tasks[i].audio_start - lo;
+        len[i] = tasks[i].audio_end - tasks[i].audio_start;
+        const int64_t t = frames_for_samples(len[i]);
+        frames += t;
+        const int64_t e = encoder_out_frames((int)t);
+        enc_rows += e;
+        max_enc = std::max(max_enc, e);
+    }
+    SB_CUDA(c->feat_stage.ensure(sizeof(float) * kMels * (size_t)frames));
+    SB_CUDA(c->enc_stage.ensure(sizeof(float) * kDModel * (size_t)enc_rows));
+    if (n_tasks > 65535) return fail(SB_INVALID_ARGUMENT, "more than 65535 tasks in one batch");
+    {
+        int32_t s = frontend_run(c, c->pcm_stage.as<float>(), start.data(), len.data(), n_tasks, cfg.preemphasis, true,
+                                 c->feat_stage.as<float>(), fo.data());
+        if (s != SB_OK) return s;
+    }
+    std::vector<int> eoi(n_tasks + 1);
+    cudaError_t e = encoder_forward(c, *c->model, c->feat_stage.as<float>(), fo.data(), (int)n_tasks,
+                                    c->enc_stage.as<float>(), eoi.data(), *c->enc_ws, c->workspace_budget);
+    SB_CUDA(e);
+    for (int64_t i = 0; i <= n_tasks; ++i) eo[i] = eoi[i];
+    const int64_t max_tokens = std::max<int64_t>(1, kMaxSymbols * max_enc);
+    std::vector<uint32_t> tok((size_t)n_tasks * max_tokens);
+    std::vector<int64_t> frm((size_t)n_tasks * max_tokens), dur((size_t)n_tasks * max_tokens), cnt(n_tasks);
+    std::vector<float> conf((size_t)n_tasks * max_tokens);
+    int32_t s = tdt_decode(c, c->enc_stage.as<float>(), eo.data(), n_tasks, max_tokens, tok.data(), frm.data(),
+                           dur.data(), conf.data(), cnt.data(), nullptr, 0, nullptr);
+    if (s != SB_OK) return s;
+    out->resize(n_tasks);
+    for (int64_t i = 0; i < n_tasks; ++i) {
+        const int64_t o = i * max_tokens;
+        (*out)[i] = raw_from_arrays(tok.data(), frm.data(), dur.data(), conf.data(), o, o + cnt[i]);
+        // pipeline.rs:132-136
+        apply_time_offsets((*out)[i], tasks[i].global_sample_offset / cfg.samples_per_encoder_frame,
+                           tasks[i].context_samples / cfg.samples_per_encoder_frame);
+    }
+    return SB_OK;
+}
+
+int32_t check_config(const sb_transcription_config& t) {
+    if (t.sample_rate != 16000 || t.feature_size != 128 || t.n_fft != 512 || t.win_length != 400 ||
+        t.hop_length != 160 || t.samples_per_encoder_frame != 1280 || t.max_audio_samples > 240000 ||
+        t.max_audio_samples <= 0)
+        return fail(SB_INVALID_ARGUMENT,
+                    "the kernels are specialised for 16 kHz / 128 mels / n_fft 512 / win 400 / hop 160 / 1280 samples "
+                    "per encoder frame and at most 240000 samples per chunk");
+    return SB_OK;
+}
+
+}  // namespace
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+// ------------------------------------------------------------------ planner / offsets / merge
+int64_t sb_overlap_chunk_samples(const sb_overlap_config* c) { return c ? overlap_chunk_samples(*c) : 0; }
+int64_t sb_overlap_overlap_samples(const sb_overlap_config* c) { return c ? overlap_overlap_samples(*c) : 0; }
+int64_t sb_overlap_stride_samples(const sb_overlap_config* c) { return c ? overlap_stride_samples(*c) : 0; }
+
+int32_t sb_plan_fast(const sb_overlap_config* cfg, int64_t audio_len, sb_chunk_task* tasks, int64_t cap,
+                     int64_t* n_tasks) {
+    if (!cfg || !n_tasks) return fail(SB_INVALID_ARGUMENT, "null argument");
+    const std::vector<sb_chunk_task> t = plan_fast_tasks(audio_len, *cfg);
+    *n_tasks = (int64_t)t.size();
+    if (!tasks) return SB_OK;
+    if (cap < (int64_t)t.size()) return fail(SB_BUFFER_TOO_SMALL, "task buffer too small");
+    std::copy(t.begin(), t.end(), tasks);
+    return SB_OK;
+}
+
+int64_t sb_parallel_worker_count(int64_t task_count, int64_t requested) {
+    return parallel_worker_count(task_count, requested);
+}
+
+int32_t sb_apply_time_offsets(uint32_t* tok, int64_t* frm, int64_t* dur, float* conf, int64_t n, int64_t frame_offset,
+                              int64_t context_frames, int64_t* n_out) {
+    if (n < 0 || !n_out || (n > 0 && (!tok || !frm || !dur || !conf))) return fail(SB_INVALID_ARGUMENT, "null argument");
+    RawTokens r = raw_from_arrays(tok, frm, dur, conf, 0, n);
+    apply_time_offsets(r, frame_offset, context_frames);
+    const size_t k = r.token_ids.size();
+    std::copy(r.token_ids.begin(), r.token_ids.end(), tok);
+    std::copy(r.frame_indices.begin(), r.frame_indices.end(), frm);
+    std::copy(r.durations.begin(), r.durations.end(), dur);
+    std::copy(r.confidences.begin(), r.confidences.end(), conf);
+    *n_out = (int64_t)k;
+    return SB_OK;
+}
+
+int32_t sb_merge_windows(const uint32_t* tok, const int64_t* frm, const int64_t* dur, const float* conf,
+                         const int64_t* win_off, int64_t n_windows, uint32_t* otok, int64_t* ofrm, int64_t* odur,
+                         float* oconf, int64_t out_cap, int64_t* n_out) {
+    if (!win_off || !n_out || n_windows < 0) return fail(SB_INVALID_ARGUMENT, "null argument");
+    OverlapMerger m;
+    for (int64_t w = 0; w < n_windows; ++w) m.push(raw_from_arrays(tok, frm, dur, conf, win_off[w], win_off[w + 1]));
+    const RawTokens& r = m.merged();
+    *n_out = (int64_t)r.token_ids.size();
+    if (*n_out > out_cap) return fail(SB_BUFFER_TOO_SMALL, "merge output buffer too small");
+    std::copy(r.token_ids.begin(), r.token_ids.end(), otok);
+    std::copy(r.frame_indices.begin(), r.frame_indices.end(), ofrm);
+    std::copy(r.durations.begin(), r.durations.end(), odur);
+    std::copy(r.confidences.begin(), r.confidences.end(), oconf);
+    return SB_OK;
+}
+
+// ------------------------------------------------------------------ vocabulary / text / results
+int32_t sb_vocab_load(const char* path, sb_vocab** out) {
+    if (!path || !out) return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_vocab* v = new sb_vocab();
+    bool io = false;
+    const std::string err = vocabulary_from_file(path, &v->v, &io);
+    if (!err.empty()) {
+        delete v;
+        return fail(io ? SB_IO : SB_INVALID_VOCABULARY, err);
+    }
+    *out = v;
+    return SB_OK;
+}
+
+int32_t sb_vocab_from_text(const char* text, int64_t len, sb_vocab** out) {
+    if (!text || !out || len < 0) return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_vocab* v = new sb_vocab();
+    const std::string err = vocabulary_from_text(std::string(text, (size_t)len), &v->v);
+    if (!err.empty()) {
+        delete v;
+        return fail(SB_INVALID_VOCABULARY, err);
+    }
+    *out = v;
+    return SB_OK;
+}
+
+void sb_vocab_free(sb_vocab* v) { delete v; }
+int64_t sb_vocab_size(const sb_vocab* v) { return v ? (int64_t)v->v.id_to_token.size() : 0; }
+int64_t sb_vocab_blank_id(const sb_vocab* v) { return v ? v->v.blank_id : -1; }
+
+int32_t sb_text_decode(const sb_vocab* vocab, const uint32_t* tok, const int64_t* frm, const float* conf, int64_t n,
+                       int64_t n_conf, double duration_seconds, sb_result** out) {
+    if (!vocab || !out || n < 0 || (n > 0 && (!tok || !frm))) return fail(SB_INVALID_ARGUMENT, "null argument");
+    RawTokens r;
+    r.token_ids.assign(tok, tok + n);
+    r.frame_indices.assign(frm, frm + n);
+    r.durations.assign((size_t)n, 0);
+    if (conf && n_conf > 0) r.confidences.assign(conf, conf + n_conf);
+    sb_result* res = new sb_result();
+    res->r = decode_tokens(vocab->v, r, duration_seconds);
+    *out = res;
+    return SB_OK;
+}
+
+const char* sb_result_text(const sb_result* r) { return r ? r->r.text.c_str() : ""; }
+double sb_result_duration(const sb_result* r) { return r ? r->r.duration_seconds : 0.0; }
+int64_t sb_result_num_tokens(const sb_result* r) { return r ? (int64_t)r->r.tokens.size() : 0; }
+int64_t sb_result_num_chunks(const sb_result* r) { return r ? (int64_t)r->r.chunks.size() : 0; }
+
+int32_t sb_result_token(const sb_result* r, int64_t i, uint32_t* token_id, const char** text, double* start,
+                        double* end, float* confidence) {
+    if (!r || i < 0 || i >= (int64_t)r->r.tokens.size()) return fail(SB_INVALID_ARGUMENT, "token index out of range");
+    const TimedToken& t = r->r.tokens[(size_t)i];
+    if (token_id) *token_id = t.token_id;
+    if (text) *text = t.text.c_str();
+    if (start) *start = t.start;
+    if (end) *end = t.end;
+    if (confidence) *confidence = t.confidence;
+    return SB_OK;
+}
+
+int32_t sb_result_chunk(const sb_result* r, int64_t i, double* start, double* end, const char** text) {
+    if (!r || i < 0 || i >= (int64_t)r->r.chunks.size()) return fail(SB_INVALID_ARGUMENT, "chunk index out of range");
+    const TranscriptChunk& c = r->r.chunks[(size_t)i];
+    if (start) *start = c.start;
+    if (end) *end = c.end;
+    if (text) *text = c.text.c_str();
+    return SB_OK;
+}
+
+void sb_result_free(sb_result* r) { delete r; }
+
+int64_t sb_raw_batch_size(const sb_raw_batch* b) { return b ? (int64_t)b->items.size() : 0; }
+
+int32_t sb_raw_batch_get(const sb_raw_batch* b, int64_t i, int64_t* n, const uint32_t** tok, const int64_t** frm,
+                         const int64_t** dur, const float** conf) {
+    if (!b || i < 0 || i >= (int64_t)b->items.size()) return fail(SB_INVALID_ARGUMENT, "batch index out of range");
+    const RawTokens& r = b->items[(size_t)i];
+    if (n) *n = (int64_t)r.token_ids.size();
+    if (tok) *tok = r.token_ids.data();
+    if (frm) *frm = r.frame_indices.data();
+    if (dur) *dur = r.durations.data();
+    if (conf) *conf = r.confidences.data();
+    return SB_OK;
+}
+
+void sb_raw_batch_free(sb_raw_batch* b) { delete b; }
+
+// ------------------------------------------------------------------ pipelines
+int32_t sb_transcribe_chunks(sb_ctx* c, const float* pcm, int64_t n_samples, const sb_chunk_task* tasks,
+                             int64_t n_tasks, const sb_transcription_config* cfg, sb_raw_batch** out) {
+    if (!c || !pcm || !out || (n_tasks > 0 && !tasks) || n_tasks < 0) return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_transcription_config t;
+    if (cfg) t = *cfg; else sb_default_transcription_config(&t);
+    int32_t s = check_config(t);
+    if (s != SB_OK) return s;
+    sb_raw_batch* b = new sb_raw_batch();
+    s = transcribe_tasks(c, pcm, n_samples, tasks, n_tasks, t, &b->items);
+    if (s != SB_OK) {
+        delete b;
+        return s;
+    }
+    *out = b;
+    return SB_OK;
+}
+
+int32_t sb_pipeline_run(sb_ctx* c, const sb_vocab* vocab, const float* audio, int64_t n_samples,
+                        const sb_transcription_config* cfg, sb_result** out) {
+    if (!c || !vocab || !out) return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_transcription_config t;
+    if (cfg) t = *cfg; else sb_default_transcription_config(&t);
+    int32_t s = check_config(t);
+    if (s != SB_OK) return s;
+    if (n_samples <= 0 || !audio) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // pipeline.rs:150
+    const sb_chunk_task task{0, n_samples, 0, 0};
+    std::vector<RawTokens> raw;
+    s = transcribe_tasks(c, audio, n_samples, &task, 1, t, &raw);  // AudioTooLong is raised inside
+    if (s != SB_OK) return s;
+    sb_result* res = new sb_result();
+    res->r = decode_tokens(vocab->v, raw[0], (double)n_samples / (double)t.sample_rate);
+    *out = res;
+    return SB_OK;
+}
+
+int32_t sb_longform_finish(const sb_vocab* vocab, int64_t audio_len, const uint32_t* tok, const int64_t* frm,
+                           const int64_t* dur, const float* conf, const int64_t* win_off, int64_t n_windows,
+                           sb_result** out) {
+    if (!vocab || !out || !win_off || n_windows < 0) return fail(SB_INVALID_ARGUMENT, "null argument");
+    OverlapMerger m;
+    for (int64_t w = 0; w < n_windows; ++w) m.push(raw_from_arrays(tok, frm, dur, conf, win_off[w], win_off[w + 1]));
+    // long_form.rs:404-419: decode the merged stream against the whole recording's duration
+    TranscriptionResult merged = decode_tokens(vocab->v, m.merged(), (double)audio_len / 16000.0);
+    sb_result* res = new sb_result();
+    res->r = long_form_result(std::move(merged.tokens), audio_len);
+    *out = res;
+    return SB_OK;
+}
+
+int32_t sb_longform_run_multi(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio,
+                              int64_t n_samples, const sb_longform_config* cfg, sb_result** out) {
+    if (!ctxs || n_ctx <= 0 || !vocab || !out) return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_longform_config lc;
+    if (cfg) lc = *cfg; else sb_default_longform_config(&lc);
+    if (lc.mode != 0) return fail(SB_INVALID_ARGUMENT, "only the Fast long-form mode is available");
+    int32_t s = check_config(lc.transcription);
+    if (s != SB_OK) return s;
+    if (n_samples <= 0 || !audio) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // long_form.rs:158
+    if (n_samples <= lc.transcription.max_audio_samples)                                 // long_form.rs:161-163
+        return sb_pipeline_run(ctxs[0], vocab, audio, n_samples, &lc.transcription, out);
+    const std::vector<sb_chunk_task> tasks = plan_fast_tasks(n_samples, lc.overlap);
+    const int64_t n_tasks = (int64_t)tasks.size();
+    // long_form.rs:594-600, a worker being a GPU shard here
+    const int64_t shards = parallel_worker_count(n_tasks, std::min<int64_t>(lc.worker_count, n_ctx));
+    std::vector<std::vector<RawTokens>> parts((size_t)shards);
+    std::vector<int32_t> status((size_t)shards, SB_OK);
+    std::vector<std::string> errors((size_t)shards);
+    auto work = [&](int64_t k) {
+        const int64_t a = n_tasks * k / shards, b = n_tasks * (k + 1) / shards;
+        status[k] = transcribe_tasks(ctxs[k], audio, n_samples, tasks.data() + a, b - a, lc.transcription, &parts[k]);
+        if (status[k] != SB_OK) errors[k] = sb_last_error();
+    };
+    if (shards == 1) {
+        work(0);
+    } else {
+        std::vector<std::thread> th;
+        for (int64_t k = 0; k < shards; ++k) th.emplace_back(work, k);
+        for (auto& t : th) t.join();
+    }
+    for (int64_t k = 0; k < shards; ++k)  // the first failing shard aborts the call (long_form.rs:328-332)
+        if (status[k] != SB_OK) return fail((sb_status)status[k], errors[k]);
+    OverlapMerger m;
+    for (auto& p : parts)
+        for (auto& r : p) m.push(r);
+    TranscriptionResult merged = decode_tokens(vocab->v, m.merged(), (double)n_samples / 16000.0);
+    sb_result* res = new sb_result();
+    res->r = long_form_result(std::move(merged.tokens), n_samples);
+    *out = res;
+    return SB_OK;
+}
+
+int32_t sb_longform_run(sb_ctx* c, const sb_vocab* vocab, const float* audio, int64_t n_samples,
+                        const sb_longform_config* cfg, sb_result** out) {
+    if (!c) return fail(SB_INVALID_ARGUMENT, "ctx is null");
+    sb_ctx* one[1] = {c};
+    return sb_longform_run_multi(one, 1, vocab, audio, n_samples, cfg, out);
+}
+
+}  // extern "C"

@@ -83,15 +83,15 @@ __device__ __forceinline__ float2 twiddle(int num, int den) {
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
-logmel_kernel(const float* __restrict__ pcm, const int64_t* __restrict__ clip_off,
-              const int64_t* __restrict__ frame_off, float* __restrict__ out, float preemph,
+logmel_kernel(const float* __restrict__ pcm, const int64_t* __restrict__ clip_start,
+              const int64_t* __restrict__ clip_len, const int64_t* __restrict__ frame_off, float* __restrict__ out, float preemph,
               const FrontendTables* __restrict__ tables) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     SmemLayout& sm = *reinterpret_cast<SmemLayout*>(smem_raw);
 
     const int clip = blockIdx.y;
-    const int64_t c0 = clip_off[clip];
-    const int64_t n = clip_off[clip + 1] - c0;
+    const int64_t c0 = clip_start[clip];
+    const int64_t n = clip_len[clip];
     const int64_t fo = frame_off[clip];
     const int T = (int)(frame_off[clip + 1] - fo);
     const int f0 = blockIdx.x * kFramesPerTile;
@@ -299,14 +299,15 @@ cudaError_t frontend_configure() {
                                 (int)sizeof(SmemLayout));
 }
 
-cudaError_t frontend_launch(const float* pcm, const int64_t* d_clip_off, const int64_t* d_frame_off, int n_clips,
+cudaError_t frontend_launch(const float* pcm, const int64_t* d_clip_start, const int64_t* d_clip_len,
+                            const int64_t* d_frame_off, int n_clips,
                             int max_frames, float preemph, const FrontendTables* d_tables, float* feats,
                             float* d_mean, float* d_std, bool normalize, cudaStream_t stream) {
     if (n_clips <= 0) return cudaSuccess;
     const int tiles = (max_frames + kFramesPerTile - 1) / kFramesPerTile;
     dim3 grid(tiles, n_clips);
-    logmel_kernel<<<grid, kThreads, sizeof(SmemLayout), stream>>>(pcm, d_clip_off, d_frame_off, feats, preemph,
-                                                                 d_tables);
+    logmel_kernel<<<grid, kThreads, sizeof(SmemLayout), stream>>>(pcm, d_clip_start, d_clip_len, d_frame_off, feats,
+                                                                 preemph, d_tables);
     if (normalize) {
         colstats_kernel<<<n_clips, kMels, 0, stream>>>(feats, d_frame_off, d_mean, d_std);
         const int rows_per_cta = 64;

@@ -35,7 +35,10 @@ inline int64_t frames_for_samples(int64_t n) { return (n + 2 * kPad - kNfft) / k
 
 size_t frontend_smem_bytes();
 cudaError_t frontend_configure();
-cudaError_t frontend_launch(const float* pcm, const int64_t* d_clip_off, const int64_t* d_frame_off, int n_clips,
+// Clip i is pcm[d_clip_start[i] .. + d_clip_len[i]) (clips may overlap in the PCM buffer); its features are
+// written at row d_frame_off[i] of feats.
+cudaError_t frontend_launch(const float* pcm, const int64_t* d_clip_start, const int64_t* d_clip_len,
+                            const int64_t* d_frame_off, int n_clips,
                             int max_frames, float preemph, const FrontendTables* d_tables, float* feats,
                             float* d_mean, float* d_std, bool normalize, cudaStream_t stream);
 

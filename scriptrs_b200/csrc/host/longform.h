@@ -1,0 +1,71 @@
+// Host-side long-form logic (longform.cpp) and text decoding (text.cpp).
+#pragma once
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../../include/scriptrs_b200.h"
+#include "../pipeline.h"
+
+namespace sb {
+
+int64_t overlap_chunk_samples(const sb_overlap_config& c);
+int64_t overlap_overlap_samples(const sb_overlap_config& c);
+int64_t overlap_stride_samples(const sb_overlap_config& c);
+std::vector<sb_chunk_task> plan_fast_tasks(int64_t audio_len, const sb_overlap_config& c);
+int64_t parallel_worker_count(int64_t task_count, int64_t requested);
+void apply_time_offsets(RawTokens& raw, int64_t frame_offset, int64_t context_frames);
+
+// Left fold of the reference's overlap merge, one window at a time, in cost proportional to the
+// overlap rather than to the transcript so far.
+class OverlapMerger {
+  public:
+    void push(const RawTokens& window);
+    RawTokens take() { prefix_max_.clear(); return std::move(m_); }
+    const RawTokens& merged() const { return m_; }
+
+  private:
+    void append(const RawTokens& src, size_t from, size_t to);
+    void truncate(size_t n);
+    RawTokens m_;
+    std::vector<int64_t> prefix_max_;  // running maximum of m_.frame_indices
+};
+
+RawTokens merge_overlapping_windows(const std::vector<RawTokens>& windows);
+
+// ------------------------------------------------------------------ text
+struct Vocabulary {
+    std::vector<std::string> id_to_token;
+    int64_t blank_id = 0;
+};
+
+struct TimedToken {
+    uint32_t token_id;
+    std::string text;
+    double start, end;
+    float confidence;
+};
+
+struct TranscriptChunk {
+    double start, end;
+    std::string text;
+};
+
+struct TranscriptionResult {
+    std::string text;
+    std::vector<TranscriptChunk> chunks;
+    std::vector<TimedToken> tokens;
+    double duration_seconds = 0.0;
+};
+
+// vocab.rs:15-52.  Returns an empty string on success, else the error text; *io_error is set when the
+// file could not be read.
+std::string vocabulary_from_file(const std::string& path, Vocabulary* out, bool* io_error);
+std::string vocabulary_from_text(const std::string& text, Vocabulary* out);
+// decode.rs:39-104
+TranscriptionResult decode_tokens(const Vocabulary& vocab, const RawTokens& raw, double duration_seconds);
+// long_form.rs:344-374,602-647 for the single Overlap region of the Fast mode
+TranscriptionResult long_form_result(std::vector<TimedToken> tokens, int64_t audio_len);
+
+}  // namespace sb

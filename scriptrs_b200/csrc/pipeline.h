@@ -18,6 +18,9 @@ struct RawTokens {
 
 void decode_workspace_free(sb_ctx* c);
 
+int32_t frontend_run(sb_ctx* c, const float* d_pcm, const int64_t* clip_start, const int64_t* clip_len,
+                     int64_t n_clips, float preemphasis, bool normalize, float* d_feats, int64_t* frame_offsets);
+
 // Runs the TDT decoder over packed encoder output already on the device.  Blocking.
 int32_t tdt_decode(sb_ctx* c, const float* d_enc, const int64_t* enc_offsets, int64_t n_clips, int64_t max_tokens,
                    uint32_t* token_ids, int64_t* frame_indices, int64_t* durations, float* confidences,

@@ -1,0 +1,313 @@
+"""TranscriptionPipeline / LongFormTranscriptionPipeline: the reference's public API
+(src/pipeline.rs:30-99, src/long_form.rs:100-174) over the C ABI.  No CPU fallback: every call
+ends in libscriptrs_b200.so."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import _lib
+from ._lib import ScriptrsError, check
+from .api import Context, TranscriptionConfig, _ptr, load_model
+
+
+@dataclass
+class TimedToken:
+    """src/types.rs:1-14"""
+    token_id: int
+    text: str
+    start: float
+    end: float
+    confidence: float
+
+
+@dataclass
+class TranscriptChunk:
+    """src/types.rs:16-26"""
+    start: float
+    end: float
+    text: str
+
+
+@dataclass
+class TranscriptionResult:
+    """src/types.rs:28-49"""
+    text: str
+    chunks: list
+    tokens: list
+    duration_seconds: float
+
+
+@dataclass
+class RawTranscription:
+    """src/decode.rs:6-11"""
+    token_ids: np.ndarray
+    frame_indices: np.ndarray
+    durations: np.ndarray
+    confidences: np.ndarray
+
+
+@dataclass
+class OverlapChunkConfig:
+    """src/long_form/planner.rs:84-102"""
+    overlap_seconds: float = 2.0
+    context_samples: int = 1280
+    max_model_samples: int = 240_000
+
+    def to_c(self):
+        return _lib.OverlapConfigC(self.overlap_seconds, self.context_samples, self.max_model_samples)
+
+    def chunk_samples(self) -> int:
+        return int(_lib.lib().sb_overlap_chunk_samples(C.byref(self.to_c())))
+
+    def overlap_samples(self) -> int:
+        return int(_lib.lib().sb_overlap_overlap_samples(C.byref(self.to_c())))
+
+    def stride_samples(self) -> int:
+        return int(_lib.lib().sb_overlap_stride_samples(C.byref(self.to_c())))
+
+
+class LongFormMode:
+    Fast = 0
+
+
+@dataclass
+class LongFormConfig:
+    """src/long_form.rs:56-87.  worker_count: parallel chunk workers; a worker is a GPU shard here."""
+    mode: int = LongFormMode.Fast
+    worker_count: int = 4
+    transcription: TranscriptionConfig = field(default_factory=TranscriptionConfig)
+    overlap: OverlapChunkConfig = field(default_factory=OverlapChunkConfig)
+
+    def to_c(self):
+        return _lib.LongFormConfigC(self.mode, self.worker_count, self.transcription.to_c(), self.overlap.to_c())
+
+
+def plan_fast(audio_len: int, overlap: OverlapChunkConfig | None = None):
+    """build_fast_execution_plan: list of (audio_start, audio_end, global_sample_offset, context_samples)."""
+    oc = (overlap or OverlapChunkConfig()).to_c()
+    n = C.c_int64()
+    check(_lib.lib().sb_plan_fast(C.byref(oc), audio_len, None, 0, C.byref(n)))
+    arr = (_lib.ChunkTaskC * max(n.value, 1))()
+    check(_lib.lib().sb_plan_fast(C.byref(oc), audio_len, arr, n.value, C.byref(n)))
+    return [(t.audio_start, t.audio_end, t.global_sample_offset, t.context_samples) for t in arr[: n.value]]
+
+
+def parallel_worker_count(task_count: int, requested: int) -> int:
+    return int(_lib.lib().sb_parallel_worker_count(task_count, requested))
+
+
+def apply_time_offsets(raw: RawTranscription, frame_offset: int, context_frames: int) -> RawTranscription:
+    tok = np.array(raw.token_ids, np.uint32)
+    frm = np.array(raw.frame_indices, np.int64)
+    dur = np.array(raw.durations, np.int64)
+    conf = np.array(raw.confidences, np.float32)
+    n = C.c_int64()
+    check(_lib.lib().sb_apply_time_offsets(_ptr(tok), _ptr(frm), _ptr(dur), _ptr(conf), tok.size, frame_offset,
+                                           context_frames, C.byref(n)))
+    k = n.value
+    return RawTranscription(tok[:k], frm[:k], dur[:k], conf[:k])
+
+
+def _concat(windows):
+    offs = np.zeros(len(windows) + 1, np.int64)
+    for i, w in enumerate(windows):
+        offs[i + 1] = offs[i] + len(w.token_ids)
+    total = int(offs[-1])
+
+    def cat(attr, dt):
+        return (np.concatenate([np.asarray(getattr(w, attr), dt) for w in windows]) if total else np.zeros(0, dt))
+
+    return (cat("token_ids", np.uint32), cat("frame_indices", np.int64), cat("durations", np.int64),
+            cat("confidences", np.float32), offs, total)
+
+
+def merge_overlapping_windows(windows) -> RawTranscription:
+    """src/long_form/merge.rs:3-13"""
+    tok, frm, dur, conf, offs, total = _concat(windows)
+    cap = max(total, 1)
+    o = (np.zeros(cap, np.uint32), np.zeros(cap, np.int64), np.zeros(cap, np.int64), np.zeros(cap, np.float32))
+    n = C.c_int64()
+    check(_lib.lib().sb_merge_windows(_ptr(tok), _ptr(frm), _ptr(dur), _ptr(conf), _ptr(offs), len(windows),
+                                      _ptr(o[0]), _ptr(o[1]), _ptr(o[2]), _ptr(o[3]), cap, C.byref(n)))
+    k = n.value
+    return RawTranscription(o[0][:k], o[1][:k], o[2][:k], o[3][:k])
+
+
+class Vocabulary:
+    """src/vocab.rs:9-61"""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    @classmethod
+    def from_file(cls, path: str) -> "Vocabulary":
+        h = C.c_void_p()
+        check(_lib.lib().sb_vocab_load(os.fsencode(path), C.byref(h)))
+        return cls(h)
+
+    @classmethod
+    def from_text(cls, text: str) -> "Vocabulary":
+        b = text.encode("utf-8")
+        h = C.c_void_p()
+        check(_lib.lib().sb_vocab_from_text(b, len(b), C.byref(h)))
+        return cls(h)
+
+    @classmethod
+    def from_tokens(cls, tokens) -> "Vocabulary":
+        return cls.from_text("".join(f"{t} {i}\n" for i, t in enumerate(tokens)))
+
+    def blank_id(self) -> int:
+        return int(_lib.lib().sb_vocab_blank_id(self._h))
+
+    def __len__(self):
+        return int(_lib.lib().sb_vocab_size(self._h))
+
+    def __del__(self):
+        try:
+            if self._h:
+                _lib.lib().sb_vocab_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+def _take_result(h) -> TranscriptionResult:
+    L = _lib.lib()
+    try:
+        tokens = []
+        for i in range(L.sb_result_num_tokens(h)):
+            tid, txt, a, b, cf = C.c_uint32(), C.c_char_p(), C.c_double(), C.c_double(), C.c_float()
+            check(L.sb_result_token(h, i, C.byref(tid), C.byref(txt), C.byref(a), C.byref(b), C.byref(cf)))
+            tokens.append(TimedToken(tid.value, txt.value.decode("utf-8"), a.value, b.value, cf.value))
+        chunks = []
+        for i in range(L.sb_result_num_chunks(h)):
+            txt, a, b = C.c_char_p(), C.c_double(), C.c_double()
+            check(L.sb_result_chunk(h, i, C.byref(a), C.byref(b), C.byref(txt)))
+            chunks.append(TranscriptChunk(a.value, b.value, txt.value.decode("utf-8")))
+        return TranscriptionResult(L.sb_result_text(h).decode("utf-8"), chunks, tokens, L.sb_result_duration(h))
+    finally:
+        L.sb_result_free(h)
+
+
+class ParakeetTdtDecoder:
+    """src/decode.rs:29-104"""
+
+    def __init__(self, vocab: Vocabulary):
+        self.vocab = vocab
+
+    def decode(self, raw: RawTranscription, duration_seconds: float) -> TranscriptionResult:
+        tok = np.ascontiguousarray(raw.token_ids, np.uint32)
+        frm = np.ascontiguousarray(raw.frame_indices, np.int64)
+        conf = np.ascontiguousarray(raw.confidences, np.float32)
+        h = C.c_void_p()
+        check(_lib.lib().sb_text_decode(self.vocab._h, _ptr(tok), _ptr(frm), _ptr(conf), tok.size, conf.size,
+                                        float(duration_seconds), C.byref(h)))
+        return _take_result(h)
+
+
+def _audio(a) -> np.ndarray:
+    return np.ascontiguousarray(a, np.float32).reshape(-1)
+
+
+def transcribe_chunks(ctx: Context, audio: np.ndarray, tasks, config: TranscriptionConfig | None = None,
+                      audio_ptr: int | None = None, n_samples: int | None = None):
+    """Batched transcribe_task for a list of (audio_start, audio_end, global_sample_offset, context_samples).
+    Returns a list of RawTranscription.  `audio_ptr`/`n_samples` let a caller pass pinned host memory."""
+    if audio_ptr is None:
+        audio = _audio(audio)
+        audio_ptr, n_samples = audio.ctypes.data, audio.size
+    arr = (_lib.ChunkTaskC * max(len(tasks), 1))()
+    for i, t in enumerate(tasks):
+        arr[i] = _lib.ChunkTaskC(*[int(x) for x in t])
+    cfg = (config or TranscriptionConfig()).to_c()
+    h = C.c_void_p()
+    check(_lib.lib().sb_transcribe_chunks(ctx.handle, C.c_void_p(audio_ptr), n_samples, arr, len(tasks),
+                                          C.byref(cfg), C.byref(h)))
+    L = _lib.lib()
+    out = []
+    try:
+        for i in range(L.sb_raw_batch_size(h)):
+            n = C.c_int64()
+            p = [C.c_void_p() for _ in range(4)]
+            check(L.sb_raw_batch_get(h, i, C.byref(n), *[C.byref(x) for x in p]))
+            k = n.value
+
+            def arr_of(ptr, ctype, dt):
+                if k == 0:
+                    return np.zeros(0, dt)
+                return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(ctype)), shape=(k,)).astype(dt, copy=True)
+
+            out.append(RawTranscription(arr_of(p[0], C.c_uint32, np.uint32), arr_of(p[1], C.c_int64, np.int64),
+                                        arr_of(p[2], C.c_int64, np.int64), arr_of(p[3], C.c_float, np.float32)))
+    finally:
+        L.sb_raw_batch_free(h)
+    return out
+
+
+def longform_finish(vocab: Vocabulary, audio_len: int, windows) -> TranscriptionResult:
+    """Merge per-task token streams (task order), decode, build the long-form result."""
+    tok, frm, dur, conf, offs, _ = _concat(windows)
+    h = C.c_void_p()
+    check(_lib.lib().sb_longform_finish(vocab._h, audio_len, _ptr(tok), _ptr(frm), _ptr(dur), _ptr(conf), _ptr(offs),
+                                        len(windows), C.byref(h)))
+    return _take_result(h)
+
+
+class TranscriptionPipeline:
+    """Single-chunk pipeline (src/pipeline.rs:21-99).  Audio: mono 16 kHz float32."""
+
+    def __init__(self, ctx: Context, vocab: Vocabulary):
+        self.ctx = ctx
+        self.vocab = vocab
+        self._config = TranscriptionConfig()
+
+    @classmethod
+    def from_weights(cls, weights: dict, vocab: Vocabulary, encoder_layers: int = 24, scale_input: bool = False,
+                     device: int = 0, ctx: Context | None = None) -> "TranscriptionPipeline":
+        """Stands where the reference has from_dir / from_bundle (src/pipeline.rs:35-54): the caller hands
+        over named float32 tensors instead of a CoreML bundle directory."""
+        ctx = ctx or Context(device)
+        load_model(ctx, weights, encoder_layers, scale_input, has_encoder=True, has_decoder=True)
+        return cls(ctx, vocab)
+
+    def config(self) -> TranscriptionConfig:
+        return self._config
+
+    def run(self, audio) -> TranscriptionResult:
+        return self.run_with_config(audio, self._config)
+
+    def run_with_config(self, audio, config: TranscriptionConfig) -> TranscriptionResult:
+        a = _audio(audio)
+        cfg = config.to_c()
+        h = C.c_void_p()
+        check(_lib.lib().sb_pipeline_run(self.ctx.handle, self.vocab._h, _ptr(a) if a.size else None, a.size,
+                                         C.byref(cfg), C.byref(h)))
+        return _take_result(h)
+
+
+class LongFormTranscriptionPipeline:
+    """Long-form pipeline with overlap chunking (src/long_form.rs:44-174), Fast mode."""
+
+    def __init__(self, inner: TranscriptionPipeline, extra_contexts=()):
+        self.inner = inner
+        self.contexts = [inner.ctx, *extra_contexts]
+        self.default_config = LongFormConfig()
+
+    def run(self, audio) -> TranscriptionResult:
+        return self.run_with_config(audio, self.default_config)
+
+    def run_chunk(self, audio) -> TranscriptionResult:
+        return self.inner.run(audio)
+
+    def run_with_config(self, audio, config: LongFormConfig) -> TranscriptionResult:
+        a = _audio(audio)
+        cfg = config.to_c()
+        h = C.c_void_p()
+        hs = (C.c_void_p * len(self.contexts))(*[c.handle for c in self.contexts])
+        check(_lib.lib().sb_longform_run_multi(hs, len(self.contexts), self.inner.vocab._h,
+                                               _ptr(a) if a.size else None, a.size, C.byref(cfg), C.byref(h)))
+        return _take_result(h)
