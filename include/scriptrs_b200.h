@@ -277,6 +277,10 @@ void sb_raw_batch_free(sb_raw_batch* b);
 int32_t sb_transcribe_chunks(sb_ctx* ctx, const float* audio, int64_t n_samples, const sb_chunk_task* tasks,
                              int64_t n_tasks, const sb_transcription_config* cfg, sb_raw_batch** out);
 
+/* The same with the recording already in device memory (d_audio is a device pointer). */
+int32_t sb_transcribe_chunks_device(sb_ctx* ctx, const float* d_audio, int64_t n_samples, const sb_chunk_task* tasks,
+                                    int64_t n_tasks, const sb_transcription_config* cfg, sb_raw_batch** out);
+
 /* TranscriptionPipeline::run_with_config (src/pipeline.rs:81-89): one chunk of at most
  * cfg->max_audio_samples samples (SB_AUDIO_TOO_LONG beyond, SB_EMPTY_AUDIO if empty). */
 int32_t sb_pipeline_run(sb_ctx* ctx, const sb_vocab* vocab, const float* audio, int64_t n_samples,

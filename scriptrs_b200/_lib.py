@@ -100,6 +100,7 @@ SIGNATURES = {
                                 C.POINTER(_VP)]),
     "sb_raw_batch_free": (None, [_VP]),
     "sb_transcribe_chunks": (_I32, [_VP, _VP, _I64, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),
+    "sb_transcribe_chunks_device": (_I32, [_VP, _VP, _I64, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),
     "sb_pipeline_run": (_I32, [_VP, _VP, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),
     "sb_longform_run": (_I32, [_VP, _VP, _VP, _I64, C.POINTER(LongFormConfigC), C.POINTER(_VP)]),
     "sb_longform_run_multi": (_I32, [C.POINTER(_VP), _I64, _VP, _VP, _I64, C.POINTER(LongFormConfigC), C.POINTER(_VP)]),

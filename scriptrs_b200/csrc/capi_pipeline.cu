@@ -36,7 +36,7 @@ RawTokens raw_from_arrays(const uint32_t* tok, const int64_t* frm, const int64_t
 // Frontend -> encoder -> decoder for a set of tasks over one host PCM buffer; the reference's
 // transcribe_task (src/long_form.rs:584-592) for a whole batch at once.
 int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const sb_chunk_task* tasks, int64_t n_tasks,
-                         const sb_transcription_config& cfg, std::vector<RawTokens>* out) {
+                         const sb_transcription_config& cfg, std::vector<RawTokens>* out, bool pcm_on_device = false) {
     out->clear();
     if (n_tasks == 0) return SB_OK;
     if (!c->model || !c->model->has_encoder || !c->model->has_decoder)
@@ -60,8 +60,12 @@ int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const s
     SB_CUDA(cudaSetDevice(c->device));
     cudaStream_t st = c->stream;
     // PCM span of this batch -> device
-    SB_CUDA(c->pcm_stage.ensure(sizeof(float) * (size_t)(hi - lo)));
-    SB_CUDA(cudaMemcpyAsync(c->pcm_stage.p, pcm + lo, sizeof(float) * (size_t)(hi - lo), cudaMemcpyHostToDevice, st));
+    const float* d_pcm = pcm + lo;
+    if (!pcm_on_device) {
+        SB_CUDA(c->pcm_stage.ensure(sizeof(float) * (size_t)(hi - lo)));
+        SB_CUDA(cudaMemcpyAsync(c->pcm_stage.p, pcm + lo, sizeof(float) * (size_t)(hi - lo), cudaMemcpyHostToDevice, st));
+        d_pcm = c->pcm_stage.as<float>();
+    }
     std::vector<int64_t> start(n_tasks), len(n_tasks), fo(n_tasks + 1), eo(n_tasks + 1);
     int64_t frames = 0, enc_rows = 0, max_enc = 0;
     for (int64_t i = 0; i < n_tasks; ++i) {
@@ -77,7 +81,7 @@ int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const s
     SB_CUDA(c->enc_stage.ensure(sizeof(float) * kDModel * (size_t)enc_rows));
     if (n_tasks > 65535) return fail(SB_INVALID_ARGUMENT, "more than 65535 tasks in one batch");
     {
-        int32_t s = frontend_run(c, c->pcm_stage.as<float>(), start.data(), len.data(), n_tasks, cfg.preemphasis, true,
+        int32_t s = frontend_run(c, d_pcm, start.data(), len.data(), n_tasks, cfg.preemphasis, true,
                                  c->feat_stage.as<float>(), fo.data());
         if (s != SB_OK) return s;
     }
@@ -269,6 +273,23 @@ int32_t sb_transcribe_chunks(sb_ctx* c, const float* pcm, int64_t n_samples, con
     if (s != SB_OK) return s;
     sb_raw_batch* b = new sb_raw_batch();
     s = transcribe_tasks(c, pcm, n_samples, tasks, n_tasks, t, &b->items);
+    if (s != SB_OK) {
+        delete b;
+        return s;
+    }
+    *out = b;
+    return SB_OK;
+}
+
+int32_t sb_transcribe_chunks_device(sb_ctx* c, const float* d_audio, int64_t n_samples, const sb_chunk_task* tasks,
+                                    int64_t n_tasks, const sb_transcription_config* cfg, sb_raw_batch** out) {
+    if (!c || !d_audio || !out || (n_tasks > 0 && !tasks) || n_tasks < 0) return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_transcription_config t;
+    if (cfg) t = *cfg; else sb_default_transcription_config(&t);
+    int32_t s = check_config(t);
+    if (s != SB_OK) return s;
+    sb_raw_batch* b = new sb_raw_batch();
+    s = transcribe_tasks(c, d_audio, n_samples, tasks, n_tasks, t, &b->items, true);
     if (s != SB_OK) {
         delete b;
         return s;

@@ -214,9 +214,10 @@ def _audio(a) -> np.ndarray:
 
 
 def transcribe_chunks(ctx: Context, audio: np.ndarray, tasks, config: TranscriptionConfig | None = None,
-                      audio_ptr: int | None = None, n_samples: int | None = None):
+                      audio_ptr: int | None = None, n_samples: int | None = None, on_device: bool = False):
     """Batched transcribe_task for a list of (audio_start, audio_end, global_sample_offset, context_samples).
-    Returns a list of RawTranscription.  `audio_ptr`/`n_samples` let a caller pass pinned host memory."""
+    Returns a list of RawTranscription.  `audio_ptr`/`n_samples` let a caller pass pinned host memory, or,
+    with on_device=True, a device pointer."""
     if audio_ptr is None:
         audio = _audio(audio)
         audio_ptr, n_samples = audio.ctypes.data, audio.size
@@ -225,8 +226,8 @@ def transcribe_chunks(ctx: Context, audio: np.ndarray, tasks, config: Transcript
         arr[i] = _lib.ChunkTaskC(*[int(x) for x in t])
     cfg = (config or TranscriptionConfig()).to_c()
     h = C.c_void_p()
-    check(_lib.lib().sb_transcribe_chunks(ctx.handle, C.c_void_p(audio_ptr), n_samples, arr, len(tasks),
-                                          C.byref(cfg), C.byref(h)))
+    fn = _lib.lib().sb_transcribe_chunks_device if on_device else _lib.lib().sb_transcribe_chunks
+    check(fn(ctx.handle, C.c_void_p(audio_ptr), n_samples, arr, len(tasks), C.byref(cfg), C.byref(h)))
     L = _lib.lib()
     out = []
     try:
