@@ -5,16 +5,18 @@
 // joint network's encoder projection.  Operands are K-major bf16 (or e4m3), accumulation
 // is fp32 in tensor memory.
 //
-// One CTA per SM, 192 threads, warp-specialised:
+// One CTA per SM, 320 threads, warp-specialised:
 //   warp 0      TMA producer: 128-byte-swizzled [128 x 64] A tiles and [BN x 64] W tiles
 //               through a multi-stage shared-memory ring (full / empty mbarriers)
 //   warp 1      allocates tensor memory, issues tcgen05.mma (M = 128, N = BN, K = 16 per
 //               instruction, four per stage) from one lane; tcgen05.commit releases ring
 //               slots and publishes finished accumulators
-//   warps 2..5  epilogue: tcgen05.ld of the 128 x BN fp32 accumulator (one row per thread),
-//               scales / bias / activation / residual, vectorised stores.  Two accumulator
-//               buffers (2 x BN columns of tensor memory) let the epilogue of tile i overlap
-//               the main loop of tile i + 1.
+//   warps 2..9  epilogue: each warp owns one 32-lane quadrant of tensor memory and one half of
+//               the tile's columns; tcgen05.ld (one row per thread), scales / bias / activation,
+//               128-byte-swizzled staging slab in shared memory, TMA store of [32 rows x 128 B]
+//               boxes (TMA reduce-add for the residual mode, so the residual stream is never read;
+//               rows beyond M are clipped by the tensor map).  Two accumulator buffers (2 x BN
+//               columns of tensor memory) let the epilogue of tile i overlap the main loop of i + 1.
 // Every wait on an mbarrier is bounded by a cycle budget; when it runs out the kernel sets
 // *error, drains, frees its tensor memory and returns.
 #include <cuda.h>
@@ -30,7 +32,9 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kBKBytes = 128;  // one 128-byte swizzle row per operand row and stage
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;
+constexpr int kEpiWarps = 8;
+constexpr int kSlabBytes = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 1.9 GHz
 
 template <int BN>
@@ -40,7 +44,7 @@ struct Cfg {
     static constexpr int kBBytes = BN * kBKBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarBytes = 256;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiWarps * kSlabBytes + kBarBytes + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -86,6 +90,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
@@ -165,8 +184,8 @@ struct EpiParams {
 
 template <int BN, bool FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, EpiParams ep,
-            int* __restrict__ error) {
+gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+            const __grid_constant__ CUtensorMap tma_out, EpiParams ep, int* __restrict__ error) {
     using C = Cfg<BN>;
     constexpr int S = C::kStages;
     extern __shared__ unsigned char smem_dyn[];
@@ -174,13 +193,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     unsigned char* base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
     const uint32_t a_base = base;
     const uint32_t b_base = base + S * C::kABytes;
-    const uint32_t bar_base = base + S * C::kStageBytes;
+    const uint32_t slab_base = base + S * C::kStageBytes;
+    const uint32_t bar_base = slab_base + kEpiWarps * kSlabBytes;
     // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2], then tmem pointer and abort flag
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * S + a); };
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * S + 2 + a); };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + S * C::kStageBytes + 8 * (2 * S + 4));
+    uint32_t* tmem_slot =
+        reinterpret_cast<uint32_t*>(base_ptr + S * C::kStageBytes + kEpiWarps * kSlabBytes + 8 * (2 * S + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -196,7 +217,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);
+            mbar_init(tempty_bar(a), kEpiWarps);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -264,7 +285,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+        const int ew = warp - 2;
+        const int quad = warp & 3;   // tensor-memory lane quadrant this warp may read
+        const int half = ew >> 2;    // which half of the tile's columns
+        const uint32_t slab = slab_base + ew * kSlabBytes;
+        unsigned char* slab_ptr = base_ptr + S * C::kStageBytes + ew * kSlabBytes;
+        const bool out_bf16 = ep.out_mode == kOutBf16;
+        const int slab_cols = out_bf16 ? 64 : 32;  // 128 bytes per row either way
+        const int sw = lane & 7;
         uint32_t lt = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
@@ -274,65 +302,80 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             if (!mbar_wait(tfull_bar(acc), acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + quad * 32 + lane;
-            const bool row_ok = row < ep.M;
-            const float rs = (FP8 && ep.row_scale && row_ok) ? ep.row_scale[row] : 1.0f;
+            const float rs = (FP8 && ep.row_scale && row < ep.M) ? ep.row_scale[row] : 1.0f;
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+            const int cbeg = half * (BN / 2), cend = cbeg + BN / 2;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(taddr + c, v);
-                tmem_wait_ld();
-                if (c + 32 >= BN) {
-                    // accumulator fully read: hand the buffer back to the MMA warp
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(acc));
-                }
-                if (!row_ok) continue;
-                const int col0 = n0 + c;
-                float x[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float f = __uint_as_float(v[j]);
-                    if (FP8) f *= rs * (ep.col_scale ? __ldg(ep.col_scale + col0 + j) : 1.0f);
-                    if (ep.bias) f += __ldg(ep.bias + col0 + j);
-                    x[j] = apply_act(f, ep.act);
-                }
-                if (ep.out_mode == kOutBf16) {
-                    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out) + (size_t)row * ep.ldo + col0;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        uint4 pk;
-                        __nv_bfloat162 p0 = __floats2bfloat162_rn(x[j], x[j + 1]);
-                        __nv_bfloat162 p1 = __floats2bfloat162_rn(x[j + 2], x[j + 3]);
-                        __nv_bfloat162 p2 = __floats2bfloat162_rn(x[j + 4], x[j + 5]);
-                        __nv_bfloat162 p3 = __floats2bfloat162_rn(x[j + 6], x[j + 7]);
-                        pk.x = *reinterpret_cast<uint32_t*>(&p0);
-                        pk.y = *reinterpret_cast<uint32_t*>(&p1);
-                        pk.z = *reinterpret_cast<uint32_t*>(&p2);
-                        pk.w = *reinterpret_cast<uint32_t*>(&p3);
-                        *reinterpret_cast<uint4*>(o + j) = pk;
+            for (int c = cbeg; c < cend; c += slab_cols) {
+                // the slab is free again once the previous TMA store has read it
+                if (lane == 0) bulk_wait_read0();
+                __syncwarp();
+#pragma unroll 1
+                for (int sub = 0; sub * 32 < slab_cols; ++sub) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + c + 32 * sub, v);
+                    tmem_wait_ld();
+                    if (c + 32 * (sub + 1) >= cend) {
+                        // this warp has read its part of the accumulator: hand it back to the MMA warp
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar(acc));
                     }
-                } else {
-                    float* o = reinterpret_cast<float*>(ep.out) + (size_t)row * ep.ldo + col0;
+                    const int col0 = n0 + c + 32 * sub;
+                    float x[32];
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
-                        float4 r;
-                        if (ep.out_mode == kOutResidual) {
-                            r = *reinterpret_cast<const float4*>(o + j);
-                            r.x = fmaf(ep.alpha, x[j], r.x);
-                            r.y = fmaf(ep.alpha, x[j + 1], r.y);
-                            r.z = fmaf(ep.alpha, x[j + 2], r.z);
-                            r.w = fmaf(ep.alpha, x[j + 3], r.w);
-                        } else {
-                            r = make_float4(ep.alpha * x[j], ep.alpha * x[j + 1], ep.alpha * x[j + 2],
-                                            ep.alpha * x[j + 3]);
-                        }
-                        *reinterpret_cast<float4*>(o + j) = r;
+                        float4 bb = make_float4(0.f, 0.f, 0.f, 0.f), cs = make_float4(1.f, 1.f, 1.f, 1.f);
+                        if (ep.bias) bb = __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + j));
+                        if (FP8 && ep.col_scale) cs = __ldg(reinterpret_cast<const float4*>(ep.col_scale + col0 + j));
+                        float f0 = __uint_as_float(v[j]), f1 = __uint_as_float(v[j + 1]);
+                        float f2 = __uint_as_float(v[j + 2]), f3 = __uint_as_float(v[j + 3]);
+                        if (FP8) { f0 *= rs * cs.x; f1 *= rs * cs.y; f2 *= rs * cs.z; f3 *= rs * cs.w; }
+                        x[j] = f0 + bb.x; x[j + 1] = f1 + bb.y; x[j + 2] = f2 + bb.z; x[j + 3] = f3 + bb.w;
                     }
+                    if (ep.act == kActSilu) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j]));
+                    } else if (ep.act == kActRelu) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
+                    }
+                    if (out_bf16) {
+                        // 32 columns = 64 bytes = chunks 4*sub .. 4*sub + 3 of this row
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 pk;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(x[8 * q], x[8 * q + 1]);
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(x[8 * q + 2], x[8 * q + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(x[8 * q + 4], x[8 * q + 5]);
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(x[8 * q + 6], x[8 * q + 7]);
+                            pk.x = *reinterpret_cast<uint32_t*>(&p0);
+                            pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&p2);
+                            pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                            const int ch = 4 * sub + q;
+                            *reinterpret_cast<uint4*>(slab_ptr + lane * 128 + ((ch ^ sw) << 4)) = pk;
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const float4 r = make_float4(ep.alpha * x[4 * q], ep.alpha * x[4 * q + 1],
+                                                         ep.alpha * x[4 * q + 2], ep.alpha * x[4 * q + 3]);
+                            *reinterpret_cast<float4*>(slab_ptr + lane * 128 + ((q ^ sw) << 4)) = r;
+                        }
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (ep.out_mode == kOutResidual) tma_reduce_add_2d(&tma_out, slab, n0 + c, m0 + quad * 32);
+                    else tma_store_2d(&tma_out, slab, n0 + c, m0 + quad * 32);
+                    bulk_commit();
                 }
             }
         }
+        if (lane == 0) bulk_wait_all();
+        __syncwarp();
     }
 
     tc_fence_before();
@@ -349,12 +392,13 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 
-bool make_map(CUtensorMap* map, const void* ptr, int rows, int k_elems, int elem_bytes, int box_rows) {
-    const cuuint64_t dims[2] = {(cuuint64_t)k_elems, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)k_elems * elem_bytes};
+// 2-D row-major tensor [rows x cols] with a row pitch of `pitch_elems`; boxes of 128 bytes x box_rows, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int pitch_elems, CUtensorMapDataType dt,
+              int elem_bytes, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * elem_bytes};
     const cuuint32_t box[2] = {(cuuint32_t)(kBKBytes / elem_bytes), (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     CUresult r = g_encode(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -363,13 +407,18 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int k_elems, int elem
 
 template <int BN, bool FP8>
 cudaError_t launch_t(const GemmArgs& g, int sm_count, int* d_error, cudaStream_t stream) {
-    alignas(64) CUtensorMap ma, mb;
+    alignas(64) CUtensorMap ma, mb, mo;
     const int eb = FP8 ? 1 : 2;
-    if (!make_map(&ma, g.a, g.M, g.K, eb, kBM) || !make_map(&mb, g.w, g.N, g.K, eb, BN)) return cudaErrorInvalidValue;
+    const CUtensorMapDataType in_dt = FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const bool ob = g.out_mode == kOutBf16;
+    if (!make_map(&ma, g.a, g.M, g.K, g.K, in_dt, eb, kBM) || !make_map(&mb, g.w, g.N, g.K, g.K, in_dt, eb, BN) ||
+        !make_map(&mo, g.out, g.M, g.N, g.ldo, ob ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                  ob ? 2 : 4, 32))
+        return cudaErrorInvalidValue;
     EpiParams ep{g.bias, g.row_scale, g.col_scale, g.out, g.M, g.N, g.K, g.ldo, g.act, g.out_mode, g.alpha};
     const int tiles = ((g.M + kBM - 1) / kBM) * (g.N / BN);
     const int grid = tiles < sm_count ? tiles : sm_count;
-    gemm_kernel<BN, FP8><<<grid, kGemmThreads, Cfg<BN>::kSmemBytes, stream>>>(ma, mb, ep, d_error);
+    gemm_kernel<BN, FP8><<<grid, kGemmThreads, Cfg<BN>::kSmemBytes, stream>>>(ma, mb, mo, ep, d_error);
     return cudaGetLastError();
 }
 
@@ -405,7 +454,8 @@ cudaError_t gemm_launch(const GemmArgs& g, int sm_count, int* d_error, cudaStrea
     const int kq = g.fp8 ? 128 : 64;
     if (g.N % 128 != 0 || g.K % kq != 0 || g.K <= 0) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.w) & 15) ||
-        (reinterpret_cast<uintptr_t>(g.out) & 15) || (g.ldo & 7))
+        (reinterpret_cast<uintptr_t>(g.out) & 15) || (g.ldo & 7) || (reinterpret_cast<uintptr_t>(g.bias) & 15) ||
+        (reinterpret_cast<uintptr_t>(g.col_scale) & 15))
         return cudaErrorInvalidValue;
     // BN = 256 when it divides N and still leaves at least one tile per SM; else 128.
     const int m_tiles = (g.M + kBM - 1) / kBM;
