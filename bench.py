@@ -450,7 +450,15 @@ def run_longform(args, rank, world, local):
     peak = float(peaks["bf16_tflops"])
 
     # stage breakdown on this rank's shard (one extra untimed pass through the stage entry points)
-    stage_ms = stage_breakdown(ctx, sb, torch, stream, d_audio, mine)
+    stage_ms = stage_breakdown(ctx, sb, torch, stream, d_audio, mine) if args.stage_breakdown else None
+    # per-kernel device time of one more step (CUDA events around every launch, inside the library)
+    ctx.set_profiling(True)
+    t0 = time.perf_counter()
+    device_step()
+    prof_wall_ms = (time.perf_counter() - t0) * 1e3
+    kernel_ms = {k: {"ms": round(v[0], 3), "launches": v[1]} for k, v in ctx.profile_report().items()}
+    kernel_ms["_step_wall_ms"] = round(prof_wall_ms, 3)
+    ctx.set_profiling(False)
     clocks = sampler.stop()
 
     enc_flops = sum(ENC_GFLOP_PER_15S_CHUNK * 1e9 * (layers / 24.0) * ((t[1] - t[0]) / 240000.0) for t in tasks)
@@ -476,6 +484,7 @@ def run_longform(args, rank, world, local):
                 "transcript_tokens": (len(res.tokens) if res is not None else None)},
         "gpu_launches": int(launches),
         "stage_ms_rank0": stage_ms,
+        "kernel_ms_rank0": kernel_ms,
         "clocks": clocks,
     }
     if rank == 0 and not args.skip_cpu_baseline:
@@ -575,6 +584,7 @@ def main():
     ap.add_argument("--hours", type=float, default=8.0, help="longform workload: hours of audio (default 8)")
     ap.add_argument("--layers", type=int, default=24, help="longform workload: Conformer blocks (default 24)")
     ap.add_argument("--clips", type=int, default=0, help="frontend workload: clips per GPU (default 1024)")
+    ap.add_argument("--stage-breakdown", action="store_true", help="longform: also time the three stage entry points")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="profiling runs: leave the CPU leg out")
     args = ap.parse_args()
     rank, world, local = dist_env()

@@ -102,6 +102,17 @@ int32_t sb_ctx_synchronize(sb_ctx* ctx);
 /* Number of kernels this context has launched since creation. */
 int64_t sb_ctx_kernel_launches(const sb_ctx* ctx);
 
+/* Tuning and test switches.  "simt_attention" (0/1): run the relative-position attention on CUDA cores
+ * instead of the tensor-core kernel; "workspace_budget_mb": bytes of encoder intermediates per group
+ * of clips (default 12288). */
+int32_t sb_ctx_set_option(sb_ctx* ctx, const char* name, int64_t value);
+
+/* In-situ timing (off by default): CUDA events around every kernel launch, summed per kernel label.
+ * sb_ctx_profile_report synchronises, writes lines "label milliseconds launches" into buf (NUL
+ * terminated, truncated to cap) and resets the counters; it returns the full length. */
+int32_t sb_ctx_set_profiling(sb_ctx* ctx, int32_t on);
+int64_t sb_ctx_profile_report(sb_ctx* ctx, char* buf, int64_t cap);
+
 /* --------------------------------------------------------------- frontend */
 
 /* Host copies of the frontend's constant tables: hann_window (src/frontend.rs:161-165)

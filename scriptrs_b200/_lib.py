@@ -66,6 +66,9 @@ SIGNATURES = {
     "sb_ctx_set_stream": (_I32, [_VP, _VP]),
     "sb_ctx_synchronize": (_I32, [_VP]),
     "sb_ctx_kernel_launches": (_I64, [_VP]),
+    "sb_ctx_set_option": (_I32, [_VP, C.c_char_p, _I64]),
+    "sb_ctx_set_profiling": (_I32, [_VP, _I32]),
+    "sb_ctx_profile_report": (_I64, [_VP, C.c_char_p, _I64]),
     "sb_frontend_tables": (_I32, [_VP, _VP]),
     "sb_frontend_num_frames": (_I64, [_I64]),
     "sb_frontend_device": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),

@@ -75,6 +75,22 @@ class Context:
     def kernel_launches(self) -> int:
         return int(_lib.lib().sb_ctx_kernel_launches(self._h))
 
+    def set_option(self, name: str, value: int):
+        check(_lib.lib().sb_ctx_set_option(self._h, name.encode(), int(value)))
+
+    def set_profiling(self, on: bool):
+        check(_lib.lib().sb_ctx_set_profiling(self._h, int(on)))
+
+    def profile_report(self) -> dict:
+        """{label: (milliseconds, launches)} since the last report (synchronises)."""
+        buf = C.create_string_buffer(1 << 16)
+        _lib.lib().sb_ctx_profile_report(self._h, buf, len(buf))
+        out = {}
+        for line in buf.value.decode().splitlines():
+            name, ms, n = line.rsplit(" ", 2)
+            out[name] = (float(ms), int(n))
+        return out
+
     def close(self):
         if self._h:
             _lib.lib().sb_ctx_destroy(self._h)

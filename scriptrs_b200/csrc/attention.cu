@@ -1,0 +1,376 @@
+// Relative-position multi-head attention on tcgen05 tensor cores (sm_100a), one CTA per (clip, head).
+//
+//   scores(i, j) = ((q_i + u) . k_j + (q_i + v) . p_{i-j}) / sqrt(128),  softmax over j,  out_i = sum_j P(i, j) v_j
+// with p_r the projected sinusoidal embedding of relative position r (model.h: row (187 - r) of the
+// per-layer table).  Part of the encoder that the reference runs as a CoreML blob
+// (src/model.rs:327-342); T' <= 188 frames per clip, 8 heads of 128.
+//
+// For each block of 128 query rows:
+//   TMA      Q [128 x 128], K [192 x 128] and the 320 table rows this block can reach, 128-byte swizzled
+//   MMA 1    S_ac = Q K^T            (128 x 192, fp32, tensor memory columns 0..191)
+//   MMA 2    S_bd = Q Pseg^T         (128 x 320, columns 192..511): column q of row i is relative
+//            position i - j for j = q - ((T'-1) - i - first_row); the "relative shift" is therefore a
+//            per-row offset, applied when each thread copies its own row out of tensor memory
+//   softmax  one thread per query row: scores = (S_ac + u.k_j + S_bd + v.p) / sqrt(128) in a private
+//            fp32 row of shared memory, max, exp, sum; probabilities written as the bf16 A operand
+//   MMA 3    O = P V                  (128 x 128, V supplied transposed so that it is K-major)
+//   store    O / sum -> bf16, staged through shared memory, coalesced rows
+// The u and v biases enter as per-key (u.k_j, computed here) and per-position (v.p, computed at model
+// load) scalars, so Q goes to the tensor cores untouched.  All mbarrier waits are bounded, and every
+// wait is followed by a block-wide vote so that all threads leave the loop together.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "attention.h"
+#include "tc_ptx.cuh"
+
+namespace sb {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kAT = 128;             // threads per CTA = query rows per block
+constexpr int kNK = 192;             // key columns of S_ac (T' padded)
+constexpr int kNP = 320;             // table rows per query block (256 + 64)
+constexpr int kSStride = 189;        // floats per private score row (odd: conflict-free reads)
+constexpr int kR1 = 97280;           // table rows (2 x 40 KB) / score rows (128 x 189 x 4) / output staging
+constexpr int kR2 = 49152;           // K (2 x 24 KB) / probabilities (3 x 16 KB)
+constexpr int kR3 = 32768;           // Q (2 x 16 KB)
+constexpr int kR4 = 49152;           // V^T (3 x 16 KB)
+constexpr int kSmall = 192 * 4 + 320 * 4 + 128 * 4 + 64;
+constexpr int kAttSmem = kR1 + kR2 + kR3 + kR4 + kSmall + 1024;
+constexpr int kOStride = 272;        // bytes per staged output row (256 + 16)
+constexpr uint32_t kBoxBytes = 64 * 128;  // one TMA box: 64 rows x 128 bytes
+
+__device__ __forceinline__ uint32_t idesc_bf16(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(kAT, 1)
+relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_pos,
+                           const __grid_constant__ CUtensorMap map_vt, const int* __restrict__ t3_off,
+                           const float* __restrict__ bias_u, const float* __restrict__ pos_vp,
+                           bf16* __restrict__ out, int* __restrict__ error) {
+    extern __shared__ unsigned char att_dyn[];
+    const uint32_t base = (smem_u32(att_dyn) + 1023u) & ~1023u;
+    unsigned char* bp = att_dyn + (base - smem_u32(att_dyn));
+    const uint32_t r1 = base, r2 = r1 + kR1, r3 = r2 + kR2, r4 = r3 + kR3;
+    unsigned char* p1 = bp;
+    unsigned char* p2 = bp + kR1;
+    float* uk = reinterpret_cast<float*>(bp + kR1 + kR2 + kR3 + kR4);
+    float* vp = uk + 192;
+    float* us = vp + 320;
+    const uint32_t bar0 = r4 + kR4 + 192 * 4 + 320 * 4 + 128 * 4;  // bar_in, bar_v, bar_mma, then tmem slot, abort flag
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(us + 128) + 6;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t bar_in = bar0, bar_v = bar0 + 8, bar_mma = bar0 + 16;
+
+    const int head = blockIdx.x, clip = blockIdx.y;
+    const int row0 = t3_off[clip];
+    const int t = t3_off[clip + 1] - row0;
+    if (t <= 0) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        mbar_init(bar_in, 1);
+        mbar_init(bar_v, 1);
+        mbar_init(bar_mma, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    us[tid] = bias_u[head * kHeadDim + tid];
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // V^T of this (clip, head): [128 d x 192 j], three K-blocks of 64 j
+    if (tid == 0) {
+        mbar_expect_tx(bar_v, 6 * kBoxBytes);
+        const int vrow = (clip * kHeads + head) * kHeadDim;
+        for (int kb = 0; kb < 3; ++kb)
+            for (int h = 0; h < 2; ++h)
+                tma_load_2d(r4 + kb * 16384 + h * kBoxBytes, &map_vt, bar_v, kb * 64, vrow + h * 64);
+    }
+
+    const float scale = 0.08838834764831845f;  // 1 / sqrt(128)
+    const int p_first = (kMaxEncFrames - 1) - (t - 1);  // table row of relative position t - 1
+    const int n_blocks = (t + kAT - 1) / kAT;
+    uint32_t mma_phase = 0;
+    bool ok = true;
+
+    for (int qb = 0; qb < n_blocks && ok; ++qb) {
+        const int i0 = qb * kAT;
+        const int plo = max(0, (t - 1) - (i0 + kAT - 1));  // first local table row this block can reach
+        if (tid == 0) {
+            mbar_expect_tx(bar_in, 20 * kBoxBytes);
+            for (int kb = 0; kb < 2; ++kb) {
+                const int col = head * kHeadDim + kb * 64;
+                for (int h = 0; h < 2; ++h)   // Q rows i0 .. i0 + 127
+                    tma_load_2d(r3 + kb * 16384 + h * kBoxBytes, &map_qkv, bar_in, col, row0 + i0 + h * 64);
+                for (int h = 0; h < 3; ++h)   // K rows 0 .. 191
+                    tma_load_2d(r2 + kb * 24576 + h * kBoxBytes, &map_qkv, bar_in, kDModel + col, row0 + h * 64);
+                for (int h = 0; h < 5; ++h)   // table rows plo .. plo + 319
+                    tma_load_2d(r1 + kb * 40960 + h * kBoxBytes, &map_pos, bar_in, col, p_first + plo + h * 64);
+            }
+        }
+        // v . p for the table rows of this block
+        for (int q = tid; q < kNP; q += kAT) {
+            const int p = p_first + plo + q;
+            vp[q] = p < kPosRows ? pos_vp[p * kHeads + head] : 0.0f;
+        }
+        if (!__syncthreads_and(mbar_wait(bar_in, qb & 1, abort_flag))) { ok = false; break; }
+        // u . k_j from the swizzled K tile
+        for (int j = tid; j < kNK; j += kAT) {
+            float acc = 0.0f;
+            if (j < t) {
+#pragma unroll
+                for (int ch = 0; ch < 16; ++ch) {
+                    const int kb = ch >> 3, c8 = ch & 7;
+                    const uint4 raw = *reinterpret_cast<const uint4*>(p2 + kb * 24576 + j * 128 + ((c8 ^ (j & 7)) << 4));
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __bfloat1622float2(h2[e]);
+                        acc = fmaf(us[ch * 8 + 2 * e], f.x, acc);
+                        acc = fmaf(us[ch * 8 + 2 * e + 1], f.y, acc);
+                    }
+                }
+            }
+            uk[j] = acc;
+        }
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int kb = k >> 2, ko = (k & 3) * 2;
+                const uint64_t a = make_smem_desc(r3 + kb * 16384) + ko;
+                tc_mma<false>(tmem, a, make_smem_desc(r2 + kb * 24576) + ko, idesc_bf16(kNK), k ? 1u : 0u);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int kb = k >> 2, ko = (k & 3) * 2;
+                const uint64_t a = make_smem_desc(r3 + kb * 16384) + ko;
+                tc_mma<false>(tmem + kNK, a, make_smem_desc(r1 + kb * 40960) + ko, idesc_bf16(256), k ? 1u : 0u);
+                tc_mma<false>(tmem + kNK + 256, a, make_smem_desc(r1 + kb * 40960 + 256 * 128) + ko, idesc_bf16(64),
+                              k ? 1u : 0u);
+            }
+            tc_commit(bar_mma);
+        }
+        // (the vote also makes uk and vp visible to all threads)
+        if (!__syncthreads_and(mbar_wait(bar_mma, mma_phase, abort_flag))) { ok = false; break; }
+        mma_phase ^= 1;
+        tc_fence_after();
+
+        const int i = i0 + tid;
+        const bool row_ok = i < t;
+        float* srow = reinterpret_cast<float*>(p1) + tid * kSStride;
+        const uint32_t tq = tmem + ((uint32_t)(warp * 32) << 16);
+        // S_bd: relative shift while copying this thread's row out of tensor memory
+        const int shift = (t - 1) - i - plo;  // j = q - shift
+#pragma unroll 1
+        for (int c = 0; c < kNP / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tq + kNK + 32 * c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) {
+                const int q = 32 * c + jj;
+                const int j = q - shift;
+                if (row_ok && j >= 0 && j < t) srow[j] = __uint_as_float(v[jj]) + vp[q];
+            }
+        }
+        // scores and row maximum
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < kNK / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tq + 32 * c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) {
+                const int j = 32 * c + jj;
+                if (row_ok && j < t) {
+                    const float s = (__uint_as_float(v[jj]) + uk[j] + srow[j]) * scale;
+                    srow[j] = s;
+                    mx = fmaxf(mx, s);
+                }
+            }
+        }
+        // probabilities -> bf16 A operand (K-major, 128-byte swizzle, three blocks of 64 keys)
+        float sum = 0.0f;
+#pragma unroll 1
+        for (int j8 = 0; j8 < kNK; j8 += 8) {
+            float e[8];
+#pragma unroll
+            for (int u8 = 0; u8 < 8; ++u8) {
+                const int j = j8 + u8;
+                e[u8] = (row_ok && j < t) ? __expf(srow[j] - mx) : 0.0f;
+                sum += e[u8];
+            }
+            uint4 pk;
+            __nv_bfloat162 q0 = __floats2bfloat162_rn(e[0], e[1]), q1 = __floats2bfloat162_rn(e[2], e[3]);
+            __nv_bfloat162 q2 = __floats2bfloat162_rn(e[4], e[5]), q3 = __floats2bfloat162_rn(e[6], e[7]);
+            pk.x = *reinterpret_cast<uint32_t*>(&q0);
+            pk.y = *reinterpret_cast<uint32_t*>(&q1);
+            pk.z = *reinterpret_cast<uint32_t*>(&q2);
+            pk.w = *reinterpret_cast<uint32_t*>(&q3);
+            const int kb = j8 >> 6, ch = (j8 & 63) >> 3;
+            *reinterpret_cast<uint4*>(p2 + kb * 16384 + tid * 128 + ((ch ^ (tid & 7)) << 4)) = pk;
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        if (qb == 0 && !__syncthreads_and(mbar_wait(bar_v, 0, abort_flag))) { ok = false; break; }
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < kNK / 16; ++k) {
+                const int kb = k >> 2, ko = (k & 3) * 2;
+                tc_mma<false>(tmem, make_smem_desc(r2 + kb * 16384) + ko, make_smem_desc(r4 + kb * 16384) + ko,
+                              idesc_bf16(kHeadDim), k ? 1u : 0u);
+            }
+            tc_commit(bar_mma);
+        }
+        if (!__syncthreads_and(mbar_wait(bar_mma, mma_phase, abort_flag))) { ok = false; break; }
+        mma_phase ^= 1;
+        tc_fence_after();
+        // O / sum -> bf16 -> staging rows -> coalesced global rows
+        const float inv = row_ok ? 1.0f / sum : 0.0f;
+#pragma unroll 1
+        for (int c = 0; c < kHeadDim / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tq + 32 * c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 pk;
+                __nv_bfloat162 o0 = __floats2bfloat162_rn(__uint_as_float(v[8 * q]) * inv, __uint_as_float(v[8 * q + 1]) * inv);
+                __nv_bfloat162 o1 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv);
+                __nv_bfloat162 o2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv);
+                __nv_bfloat162 o3 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv);
+                pk.x = *reinterpret_cast<uint32_t*>(&o0);
+                pk.y = *reinterpret_cast<uint32_t*>(&o1);
+                pk.z = *reinterpret_cast<uint32_t*>(&o2);
+                pk.w = *reinterpret_cast<uint32_t*>(&o3);
+                *reinterpret_cast<uint4*>(p1 + tid * kOStride + c * 64 + q * 16) = pk;
+            }
+        }
+        tc_fence_before();
+        __syncthreads();
+        const int valid = min(kAT, t - i0);
+        for (int r = warp; r < valid; r += kAT / 32) {
+            const uint2 val = *reinterpret_cast<const uint2*>(p1 + r * kOStride + lane * 8);
+            *reinterpret_cast<uint2*>(out + (size_t)(row0 + i0 + r) * kDModel + head * kHeadDim + lane * 4) = val;
+        }
+        fence_proxy_async();  // generic accesses to the operand regions are ordered before the next block's TMA writes
+        __syncthreads();      // staging and operand regions are reused by the next block
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (!ok || *abort_flag) {
+        // give copies that may still be in flight time to land before the shared memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {}
+    }
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+    if (tid == 0 && *abort_flag) atomicExch(error, 1);
+}
+
+// qkv [rows x 3072] -> vt [(clip * 8 + head) * 128 + d][192] (keys beyond T' are zero).  grid (8, clips).
+__global__ void __launch_bounds__(256)
+transpose_v_kernel(const bf16* __restrict__ qkv, const int* __restrict__ t3_off, bf16* __restrict__ vt) {
+    __shared__ bf16 tile[32][kHeadDim + 2];
+    const int head = blockIdx.x, clip = blockIdx.y;
+    const int row0 = t3_off[clip];
+    const int t = t3_off[clip + 1] - row0;
+    bf16* dst = vt + (size_t)(clip * kHeads + head) * kHeadDim * kNK;
+    for (int j0 = 0; j0 < kNK; j0 += 32) {
+        for (int idx = threadIdx.x; idx < 32 * kHeadDim; idx += 256) {
+            const int jl = idx >> 7, d = idx & 127;
+            const int j = j0 + jl;
+            tile[jl][d] = j < t ? qkv[(size_t)(row0 + j) * (3 * kDModel) + 2 * kDModel + head * kHeadDim + d]
+                                : __float2bfloat16(0.0f);
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 32 * kHeadDim; idx += 256) {
+            const int d = idx >> 5, jl = idx & 31;
+            dst[(size_t)d * kNK + j0 + jl] = tile[jl][d];
+        }
+        __syncthreads();
+    }
+}
+
+// vp[p][h] = sum_d v[h][d] * pos[p][h * 128 + d].  grid kPosRows, 256 threads (8 warps = 8 heads).
+__global__ void __launch_bounds__(256)
+pos_bias_kernel(const bf16* __restrict__ pos, const float* __restrict__ bias_v, float* __restrict__ vp) {
+    const int p = blockIdx.x, head = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float acc = 0.0f;
+    for (int d = lane; d < kHeadDim; d += 32)
+        acc = fmaf(bias_v[head * kHeadDim + d], __bfloat162float(pos[(size_t)p * kDModel + head * kHeadDim + d]), acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) vp[p * kHeads + head] = acc;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_enc = nullptr;
+
+bool map_bf16(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {64, 64};
+    const cuuint32_t estr[2] = {1, 1};
+    return g_enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+cudaError_t attention_configure() {
+    if (!g_enc) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) return e != cudaSuccess ? e : cudaErrorNotSupported;
+        g_enc = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    return cudaFuncSetAttribute(relpos_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttSmem);
+}
+
+size_t attention_vt_bytes(int n_clips) { return (size_t)n_clips * kHeads * kHeadDim * kNK * sizeof(bf16); }
+
+cudaError_t pos_bias_launch(const bf16* pos_proj, const float* bias_v, float* vp, cudaStream_t st) {
+    pos_bias_kernel<<<kPosRows, 256, 0, st>>>(pos_proj, bias_v, vp);
+    return cudaGetLastError();
+}
+
+cudaError_t attention_launch(const bf16* qkv, int rows, const int* d_t3_off, int n_clips, const bf16* pos_proj,
+                             const float* bias_u, const float* pos_vp, bf16* vt, bf16* out, int* d_error,
+                             cudaStream_t st) {
+    if (n_clips <= 0 || rows <= 0) return cudaSuccess;
+    alignas(64) CUtensorMap mq, mp, mv;
+    if (!map_bf16(&mq, qkv, rows, 3 * kDModel) || !map_bf16(&mp, pos_proj, kPosRows, kDModel) ||
+        !map_bf16(&mv, vt, (int64_t)n_clips * kHeads * kHeadDim, kNK))
+        return cudaErrorInvalidValue;
+    transpose_v_kernel<<<dim3(kHeads, n_clips), 256, 0, st>>>(qkv, d_t3_off, vt);
+    relpos_attention_tc_kernel<<<dim3(kHeads, n_clips), kAT, kAttSmem, st>>>(mq, mp, mv, d_t3_off, bias_u, pos_vp, out,
+                                                                            d_error);
+    return cudaGetLastError();
+}
+
+}  // namespace sb

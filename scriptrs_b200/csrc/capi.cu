@@ -1,8 +1,11 @@
 // extern "C" layer: context management and the frontend entry points.
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <cstring>
+#include <map>
 #include <string>
+#include <algorithm>
 #include <vector>
 
 #include "context.h"
@@ -50,6 +53,51 @@ void Buffer::release() {
     cap = 0;
 }
 
+cudaEvent_t Profiler::take() {
+    if (used == pool.size()) {
+        cudaEvent_t e;
+        cudaEventCreate(&e);
+        pool.push_back(e);
+    }
+    return pool[used++];
+}
+void Profiler::begin(const char* name, cudaStream_t st) {
+    if (!on) return;
+    Rec r{name, take(), take()};
+    cudaEventRecord(r.a, st);
+    recs.push_back(r);
+}
+void Profiler::end(cudaStream_t st) {
+    if (!on || recs.empty()) return;
+    cudaEventRecord(recs.back().b, st);
+}
+std::string Profiler::report() {
+    std::map<std::string, std::pair<double, long>> sum;
+    if (!recs.empty()) cudaEventSynchronize(recs.back().b);
+    for (const Rec& r : recs) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+            sum[r.name].first += ms;
+            sum[r.name].second += 1;
+        }
+    }
+    recs.clear();
+    used = 0;
+    std::string out;
+    char line[160];
+    for (auto& kv : sum) {
+        std::snprintf(line, sizeof line, "%s %.4f %ld\n", kv.first.c_str(), kv.second.first, kv.second.second);
+        out += line;
+    }
+    return out;
+}
+void Profiler::release() {
+    for (cudaEvent_t e : pool) cudaEventDestroy(e);
+    pool.clear();
+    recs.clear();
+    used = 0;
+}
+
 }  // namespace sb
 
 using namespace sb;
@@ -84,9 +132,11 @@ int32_t frontend_run(sb_ctx* c, const float* d_pcm, const int64_t* clip_start, c
     // pageable source: the copy is staged before the call returns, so the vector may go out of scope
     SB_CUDA(cudaMemcpyAsync(c->clip_off.p, meta.data(), sizeof(int64_t) * 3 * n1, cudaMemcpyHostToDevice, c->stream));
     const int64_t* d_meta = c->clip_off.as<int64_t>();
+    c->prof.begin("frontend(3 kernels)", c->stream);
     SB_CUDA(frontend_launch(d_pcm, d_meta, d_meta + n1, d_meta + 2 * n1, (int)n_clips, (int)max_frames, preemphasis,
                             c->d_tables, d_feats, c->col_mean.as<float>(), c->col_std.as<float>(), normalize,
                             c->stream));
+    c->prof.end(c->stream);
     c->launches += normalize ? 3 : 1;
     return SB_OK;
 }
@@ -191,6 +241,7 @@ void sb_ctx_destroy(sb_ctx* c) {
     c->enc_stage.release();
     if (c->d_tables) cudaFree(c->d_tables);
     if (c->d_error) cudaFree(c->d_error);
+    c->prof.release();
     if (c->own_stream) cudaStreamDestroy(c->own_stream);
     delete c;
 }
@@ -215,6 +266,33 @@ int32_t sb_ctx_synchronize(sb_ctx* c) {
 }
 
 int64_t sb_ctx_kernel_launches(const sb_ctx* c) { return c ? c->launches : 0; }
+
+int32_t sb_ctx_set_option(sb_ctx* c, const char* name, int64_t value) {
+    if (!c || !name) return fail(SB_INVALID_ARGUMENT, "null argument");
+    const std::string n(name);
+    if (n == "simt_attention") c->simt_attention = value != 0;
+    else if (n == "workspace_budget_mb" && value > 0) c->workspace_budget = (size_t)value << 20;
+    else return fail(SB_INVALID_ARGUMENT, "unknown option: " + n);
+    return SB_OK;
+}
+
+int32_t sb_ctx_set_profiling(sb_ctx* c, int32_t on) {
+    if (!c) return fail(SB_INVALID_ARGUMENT, "ctx is null");
+    c->prof.on = on != 0;
+    return SB_OK;
+}
+
+int64_t sb_ctx_profile_report(sb_ctx* c, char* buf, int64_t cap) {
+    if (!c) return 0;
+    cudaSetDevice(c->device);
+    const std::string r = c->prof.report();
+    if (buf && cap > 0) {
+        const size_t n = std::min<size_t>(r.size(), (size_t)cap - 1);
+        std::memcpy(buf, r.data(), n);
+        buf[n] = 0;
+    }
+    return (int64_t)r.size();
+}
 
 int32_t sb_frontend_tables(float* window, float* filterbank) {
     if (window) hann_window_host(window, kWin);

@@ -4,6 +4,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <vector>
 
 #include "../../include/scriptrs_b200.h"
 #include "frontend.h"
@@ -32,6 +33,20 @@ struct Buffer {
     T* as() const { return static_cast<T*>(p); }
 };
 
+// Optional in-situ timing: CUDA events around kernel launches, summed per label.
+struct Profiler {
+    bool on = false;
+    std::vector<cudaEvent_t> pool;
+    size_t used = 0;
+    struct Rec { const char* name; cudaEvent_t a, b; };
+    std::vector<Rec> recs;
+    cudaEvent_t take();
+    void begin(const char* name, cudaStream_t st);
+    void end(cudaStream_t st);
+    std::string report();  // synchronises; "name ms launches" per line, then resets
+    void release();
+};
+
 struct Model;             // encoder + predictor + joint weights (model.h)
 struct EncoderWorkspace;  // encoder.h
 struct DecodeWorkspace;   // pipeline.cu
@@ -50,6 +65,8 @@ struct sb_ctx {
     // frontend workspaces
     sb::Buffer clip_off, frame_off, col_mean, col_std, pcm_stage, feat_stage, enc_stage;
     sb::Model* model = nullptr;
+    sb::Profiler prof;
+    bool simt_attention = false;  // reference implementation of the attention kernel on CUDA cores (tests)
     sb::EncoderWorkspace* enc_ws = nullptr;
     sb::DecodeWorkspace* dec_ws = nullptr;
     size_t workspace_budget = (size_t)12 << 30;  // bytes of encoder intermediates per group of clips

@@ -20,6 +20,7 @@
 #include <algorithm>
 #include <vector>
 
+#include "attention.h"
 #include "encoder.h"
 #include "gemm.h"
 
@@ -302,14 +303,24 @@ glu_dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, c
     }
 }
 
-cudaError_t run_gemm(sb_ctx* c, const void* a, const bf16* w, const float* bias, void* out, int M, int N, int K, int act,
-                     int mode, float alpha) {
+cudaError_t run_gemm(sb_ctx* c, const char* label, const void* a, const bf16* w, const float* bias, void* out, int M, int N,
+                     int K, int act, int mode, float alpha) {
     GemmArgs g{};
     g.a = a; g.w = w; g.bias = bias; g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = N; g.act = act; g.out_mode = mode;
     g.alpha = alpha; g.fp8 = false;
     c->launches += 1;
-    return gemm_launch(g, c->sm_count, c->d_error, c->stream);
+    c->prof.begin(label, c->stream);
+    cudaError_t e = gemm_launch(g, c->sm_count, c->d_error, c->stream);
+    c->prof.end(c->stream);
+    return e;
 }
+
+#define PROF(label, launch)              \
+    do {                                 \
+        c->prof.begin(label, st);        \
+        launch;                          \
+        c->prof.end(st);                 \
+    } while (0)
 
 #define ENC_CUDA(expr)                       \
     do {                                     \
@@ -320,6 +331,8 @@ cudaError_t run_gemm(sb_ctx* c, const void* a, const bf16* w, const float* bias,
 }  // namespace
 
 cudaError_t encoder_configure() {
+    cudaError_t e = attention_configure();
+    if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(relpos_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)kAttSmemBytes);
 }
@@ -373,17 +386,18 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     ENC_CUDA(ws.a.ensure((size_t)R3 * kDModel * sizeof(bf16)));
     ENC_CUDA(ws.h.ensure((size_t)R3 * kFF * sizeof(bf16)));
     ENC_CUDA(ws.att.ensure((size_t)R3 * kDModel * sizeof(bf16)));
+    ENC_CUDA(ws.vt.ensure(attention_vt_bytes(n)));
 
     // sub-sampling
-    sub_conv0_kernel<<<R1, 256, 0, st>>>(d_feats, d_t0, d_t1, n, m.sub0_w, m.sub0_b, ws.y0.as<bf16>());
-    sub_dw_kernel<<<R2, 128, 0, st>>>(ws.y0.as<bf16>(), d_t1, d_t2, n, 64, m.dw1_w, m.dw1_b, ws.y1.as<bf16>());
+    PROF("sub_conv0", (sub_conv0_kernel<<<R1, 256, 0, st>>>(d_feats, d_t0, d_t1, n, m.sub0_w, m.sub0_b, ws.y0.as<bf16>())));
+    PROF("sub_dw1", (sub_dw_kernel<<<R2, 128, 0, st>>>(ws.y0.as<bf16>(), d_t1, d_t2, n, 64, m.dw1_w, m.dw1_b, ws.y1.as<bf16>())));
     c->launches += 2;
-    ENC_CUDA(run_gemm(c, ws.y1.p, m.pw1_w, m.pw1_b, ws.y2.p, R2 * 32, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
-    sub_dw_kernel<<<R3, 128, 0, st>>>(ws.y2.as<bf16>(), d_t2, d_t3, n, 32, m.dw2_w, m.dw2_b, ws.y3.as<bf16>());
+    ENC_CUDA(run_gemm(c, "gemm_sub_pw", ws.y1.p, m.pw1_w, m.pw1_b, ws.y2.p, R2 * 32, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
+    PROF("sub_dw2", (sub_dw_kernel<<<R3, 128, 0, st>>>(ws.y2.as<bf16>(), d_t2, d_t3, n, 32, m.dw2_w, m.dw2_b, ws.y3.as<bf16>())));
     c->launches += 1;
-    ENC_CUDA(run_gemm(c, ws.y3.p, m.pw2_w, m.pw2_b, ws.y4.p, R3 * 16, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
+    ENC_CUDA(run_gemm(c, "gemm_sub_pw", ws.y3.p, m.pw2_w, m.pw2_b, ws.y4.p, R3 * 16, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
     float* x = ws.x.as<float>();
-    ENC_CUDA(run_gemm(c, ws.y4.p, m.lin_w, m.lin_b, x, R3, kDModel, 16 * kSubC, kActNone, kOutF32, m.xscale));
+    ENC_CUDA(run_gemm(c, "gemm_sub_linear", ws.y4.p, m.lin_w, m.lin_b, x, R3, kDModel, 16 * kSubC, kActNone, kOutF32, m.xscale));
 
     const int ln_grid = (R3 + 7) / 8;
     bf16* a = ws.a.as<bf16>();
@@ -392,28 +406,35 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     for (int l = 0; l < m.layers; ++l) {
         const LayerWeights& L = m.L[l];
         // x += 0.5 * FF1(LN x)
-        layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_ff1_g, L.ln_ff1_b, a, R3);
-        ENC_CUDA(run_gemm(c, a, L.ff1_w1, L.ff1_b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
-        ENC_CUDA(run_gemm(c, h, L.ff1_w2, L.ff1_b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
+        PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_ff1_g, L.ln_ff1_b, a, R3)));
+        ENC_CUDA(run_gemm(c, "gemm_ff_up", a, L.ff1_w1, L.ff1_b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
+        ENC_CUDA(run_gemm(c, "gemm_ff_down", h, L.ff1_w2, L.ff1_b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
         // x += MHA(LN x)
-        layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_att_g, L.ln_att_b, a, R3);
-        ENC_CUDA(run_gemm(c, a, L.qkv_w, L.qkv_b, h, R3, 3 * kDModel, kDModel, kActNone, kOutBf16, 1.0f));
-        relpos_attention_kernel<<<dim3(kHeads, n), kAttThreads, kAttSmemBytes, st>>>(h, d_t3, L.pos_proj, L.bias_u,
-                                                                                    L.bias_v, att);
-        ENC_CUDA(run_gemm(c, att, L.o_w, L.o_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
+        PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_att_g, L.ln_att_b, a, R3)));
+        ENC_CUDA(run_gemm(c, "gemm_qkv", a, L.qkv_w, L.qkv_b, h, R3, 3 * kDModel, kDModel, kActNone, kOutBf16, 1.0f));
+        if (c->simt_attention) {
+            PROF("relpos_attention_simt", (relpos_attention_kernel<<<dim3(kHeads, n), kAttThreads, kAttSmemBytes, st>>>(
+                                              h, d_t3, L.pos_proj, L.bias_u, L.bias_v, att)));
+        } else {
+            c->prof.begin("relpos_attention(transpose+tcgen05)", st);
+            ENC_CUDA(attention_launch(h, R3, d_t3, n, L.pos_proj, L.bias_u, L.pos_vp, ws.vt.as<bf16>(), att, c->d_error, st));
+            c->prof.end(st);
+            c->launches += 1;
+        }
+        ENC_CUDA(run_gemm(c, "gemm_attn_out", att, L.o_w, L.o_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
         // x += Conv(LN x)
-        layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_conv_g, L.ln_conv_b, a, R3);
-        ENC_CUDA(run_gemm(c, a, L.pw1_w, L.pw1_b, h, R3, 2 * kDModel, kDModel, kActNone, kOutBf16, 1.0f));
-        glu_dwconv_kernel<<<dim3((max_t3 + kDwRows - 1) / kDwRows, n, kDModel / 256), 256, 0, st>>>(h, d_t3, L.dw_w,
-                                                                                                   L.dw_b, att);
-        ENC_CUDA(run_gemm(c, att, L.pw2_w, L.pw2_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
+        PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_conv_g, L.ln_conv_b, a, R3)));
+        ENC_CUDA(run_gemm(c, "gemm_conv_pw1", a, L.pw1_w, L.pw1_b, h, R3, 2 * kDModel, kDModel, kActNone, kOutBf16, 1.0f));
+        PROF("glu_dwconv", (glu_dwconv_kernel<<<dim3((max_t3 + kDwRows - 1) / kDwRows, n, kDModel / 256), 256, 0, st>>>(
+                               h, d_t3, L.dw_w, L.dw_b, att)));
+        ENC_CUDA(run_gemm(c, "gemm_conv_pw2", att, L.pw2_w, L.pw2_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
         // x += 0.5 * FF2(LN x)
-        layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_ff2_g, L.ln_ff2_b, a, R3);
-        ENC_CUDA(run_gemm(c, a, L.ff2_w1, L.ff2_b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
-        ENC_CUDA(run_gemm(c, h, L.ff2_w2, L.ff2_b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
+        PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_ff2_g, L.ln_ff2_b, a, R3)));
+        ENC_CUDA(run_gemm(c, "gemm_ff_up", a, L.ff2_w1, L.ff2_b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
+        ENC_CUDA(run_gemm(c, "gemm_ff_down", h, L.ff2_w2, L.ff2_b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
         // x = LN_out(x); the last block writes straight into the caller's buffer
         float* dst = (l == m.layers - 1) ? d_out + (size_t)enc_off_all[c0] * kDModel : x;
-        layernorm_kernel<true><<<ln_grid, 256, 0, st>>>(x, L.ln_out_g, L.ln_out_b, dst, R3);
+        PROF("layernorm", (layernorm_kernel<true><<<ln_grid, 256, 0, st>>>(x, L.ln_out_g, L.ln_out_b, dst, R3)));
         c->launches += 7;
     }
     if (m.layers == 0)

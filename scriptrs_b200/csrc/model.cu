@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "context.h"
+#include "attention.h"
 #include "encoder.h"
 #include "gemm.h"
 #include "model.h"
@@ -192,6 +193,11 @@ int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensor
                 g.act = kActNone; g.out_mode = kOutBf16; g.alpha = 1.0f;
                 cudaError_t e = gemm_launch(g, c->sm_count, c->d_error, c->stream);
                 if (e != cudaSuccess && ld.err.empty()) ld.err = std::string("position projection failed: ") + cudaGetErrorString(e);
+                L.pos_vp = static_cast<float*>(ld.dalloc((size_t)kPosRows * kHeads * sizeof(float)));
+                if (L.pos_vp && L.bias_v) {
+                    e = pos_bias_launch(L.pos_proj, L.bias_v, L.pos_vp, c->stream);
+                    if (e != cudaSuccess && ld.err.empty()) ld.err = std::string("position bias failed: ") + cudaGetErrorString(e);
+                }
             }
             L.pw1_w = ld.b16(p + "conv.pointwise_conv1.weight", 2 * d * d);
             L.pw1_b = ld.f32(p + "conv.pointwise_conv1.bias", 2 * d);

@@ -40,6 +40,7 @@ struct LayerWeights {
     float* o_b;
     bf16* pos_proj;  // [kPosRows x 1024]: row p = W_r * pos(187 - p), computed once at load
     float *bias_u, *bias_v;  // [1024] (head-major)
+    float* pos_vp;           // [kPosRows x 8]: bias_v . pos_proj per table row and head
     bf16* pw1_w;  // [2048 x 1024]
     float* pw1_b;
     float* dw_w;  // [9 x 1024] tap-major, BatchNorm folded in

@@ -81,7 +81,9 @@ int32_t tdt_decode(sb_ctx* c, const float* d_enc, const int64_t* enc_offsets, in
         SB_CUDA(ws.out_conf.ensure((size_t)n * max_tokens * sizeof(float)));
         if (logits_trace) SB_CUDA(ws.trace.ensure((size_t)n * trace_cap * kJointOut * sizeof(float)));
 
+        c->prof.begin("decode_enc_projection", st);
         SB_CUDA(decode_enc_projection(d_enc + row0 * kDModel, m.w_enc, m.b_enc, ws.enc_proj.as<float>(), (int)rows, st));
+        c->prof.end(st);
         c->launches += rows > 0 ? 1 : 0;
 
         DecodeWeights w{m.embedding, m.w_ih, m.w_hh, m.b_gates, m.w_pred, m.b_pred, m.w_out, m.b_out};
@@ -112,7 +114,9 @@ int32_t tdt_decode(sb_ctx* c, const float* d_enc, const int64_t* enc_offsets, in
         s.trace = logits_trace ? ws.trace.as<float>() : nullptr;
         const int max_steps = (kMaxSymbols + 1) * max_len + 2;
         if (max_len > 0) {
+            c->prof.begin("tdt_decode", st);
             SB_CUDA(decode_launch(w, s, max_steps, c->sm_count, st));
+            c->prof.end(st);
             c->launches += 1;
         }
         // read back: counts first, then only the used columns of the output tables

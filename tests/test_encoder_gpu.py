@@ -28,15 +28,24 @@ def run_gpu(ctx, feats_list):
     return [out[offs[i]:offs[i + 1]] for i in range(len(feats_list))]
 
 
+@pytest.fixture(params=["tensor-core attention", "simt attention"])
+def attention_mode(ctx, request):
+    ctx.set_option("simt_attention", int(request.param.startswith("simt")))
+    yield request.param
+    ctx.set_option("simt_attention", 0)
+
+
 @pytest.mark.parametrize("layers", [0, 1, 2])
-def test_shallow_stacks_match_oracle(ctx, layers):
+def test_shallow_stacks_match_oracle(ctx, layers, attention_mode):
     import scriptrs_b200 as sb
 
+    if layers == 0 and attention_mode.startswith("simt"):
+        pytest.skip("no attention in a 0-block stack")
     cfg = eo.EncoderConfig(layers=layers)
     w = eo.seeded_weights(cfg, seed=11, std=0.02, plain_norms=False)
     sb.load_model(ctx, w, encoder_layers=layers)
     rng = np.random.default_rng(layers)
-    feats = [rng.standard_normal((t, 128)).astype(np.float32) for t in (203, 1001, 9, 64, 1497, 1)]
+    feats = [rng.standard_normal((t, 128)).astype(np.float32) for t in (203, 1001, 9, 64, 1497, 1, 1024, 1030, 1329)]
     got = run_gpu(ctx, feats)
     for f, g in zip(feats, got):
         r = eo.encoder_forward(w, f, cfg)
