@@ -350,11 +350,12 @@ def run_longform(args, rank, world, local):
     import torch
 
     import scriptrs_b200 as sb
+    from scriptrs_b200 import dist as sbd
     from scriptrs_b200 import synth
 
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    dist = init_dist(world, local)
+    init_dist(world, local)
     peaks, peak_kind = measured_peaks()
     ctx = sb.Context(local)
     stream = torch.cuda.Stream(device=device)
@@ -369,7 +370,7 @@ def run_longform(args, rank, world, local):
     h_audio.copy_(d_audio)
     torch.cuda.synchronize()
     tasks = sb.plan_fast(n)
-    lo, hi = len(tasks) * rank // world, len(tasks) * (rank + 1) // world
+    lo, hi = sbd.shard_bounds(len(tasks), rank, world)
     mine = tasks[lo:hi]
 
     def device_step():
@@ -377,14 +378,7 @@ def run_longform(args, rank, world, local):
 
     def gather_and_finish(raws):
         """Rank 0 collects the per-task token streams in task order, merges and decodes them."""
-        if world > 1:
-            payload = [(r.token_ids, r.frame_indices, r.durations, r.confidences) for r in raws]
-            parts = [None] * world if rank == 0 else None
-            dist.gather_object(payload, parts, dst=0)
-            if rank != 0:
-                return None
-            raws = [sb.RawTranscription(*t) for part in parts for t in part]
-        return sb.longform_finish(vocab, n, raws)
+        return sbd.gather_and_finish(vocab, n, raws, rank, world)
 
     def host_step():
         raws = sb.transcribe_chunks(ctx, None, mine, audio_ptr=h_audio.data_ptr(), n_samples=n)
