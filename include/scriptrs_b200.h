@@ -141,6 +141,26 @@ int32_t sb_frontend_device(sb_ctx* ctx, const float* d_pcm, const int64_t* clip_
 int32_t sb_frontend_host(sb_ctx* ctx, const float* pcm, const int64_t* clip_offsets, int64_t n_clips,
                          float preemphasis, int32_t normalize, float* feats, int64_t* frame_offsets);
 
+/* The batched frontend for callers that must not allocate.  It has no counterpart in the reference
+ * (whose extractor keeps its scratch in a RefCell workspace on the host, src/frontend.rs:16,40-57).
+ * sb_frontend_device grows work buffers inside the context with cudaMalloc when a batch is larger
+ * than any before, and cudaMalloc / cudaFree synchronise the whole device.  That is wrong for an
+ * ingest thread that extracts features while other streams of the same GPU encode and decode, and
+ * impossible for a host that has given all device memory to its own pool.  This variant needs no
+ * context and calls no cudaMalloc, cudaFree or allocating library routine: tables, clip metadata
+ * and the per-(clip, feature) statistics live in a device array of fixed size (about 1.1 MB) that
+ * every GPU loading the library holds until the process exits.
+ *   - at most 1024 clips per call; more fails with SB_INVALID_ARGUMENT;
+ *   - runs on the CURRENT device, on `stream` (a cudaStream_t; NULL = default stream); arguments and
+ *     results are those of sb_frontend_device, bit for bit;
+ *   - the first call on a device looks up the array's address and fills the tables: make it before
+ *     any stream capture;
+ *   - all calls on a device share the array, which keeps the last call's contents (nothing in it has
+ *     to be zero); calls whose kernels overlap on the GPU race on it, so serialise them. */
+int32_t sb_frontend_device_noalloc(const float* d_pcm, const int64_t* clip_offsets, int64_t n_clips,
+                                   float preemphasis, int32_t normalize, float* d_feats, int64_t* frame_offsets,
+                                   void* stream);
+
 /* ------------------------------------------------------------------ model */
 
 /* One named fp32 tensor in host memory. */

@@ -73,6 +73,7 @@ SIGNATURES = {
     "sb_frontend_num_frames": (_I64, [_I64]),
     "sb_frontend_device": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
     "sb_frontend_host": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
+    "sb_frontend_device_noalloc": (_I32, [_VP, _VP, _I64, C.c_float, _I32, _VP, _VP, _VP]),
     "sb_model_load": (_I32, [_VP, C.POINTER(ModelDescC), C.POINTER(TensorC), _I64]),
     "sb_encoder_num_frames": (_I64, [_I64]),
     "sb_encode_device": (_I32, [_VP, _VP, _VP, _I64, _VP, _VP]),

@@ -218,3 +218,16 @@ def tdt_decode_device(ctx: Context, d_enc: int, enc_offsets: np.ndarray, max_tok
             d["logits"] = trace[i, : int(steps[i])]
         out.append(d)
     return out
+
+
+def frontend_device_noalloc(d_pcm: int, clip_offsets: np.ndarray, d_feats: int, normalize: bool = True,
+                            preemphasis: float = 0.97, stream: int = 0) -> np.ndarray:
+    """Frontend for callers that must not allocate: no context, fixed scratch inside the library, at most
+    1024 clips, current device, asynchronous on `stream`.  Returns the frame offsets."""
+    clip_offsets = np.ascontiguousarray(clip_offsets, np.int64)
+    n = clip_offsets.size - 1
+    fo = np.zeros(n + 1, np.int64)
+    check(_lib.lib().sb_frontend_device_noalloc(C.c_void_p(d_pcm), _ptr(clip_offsets), n, float(preemphasis),
+                                                int(normalize), C.c_void_p(d_feats), _ptr(fo),
+                                                C.c_void_p(stream or None)))
+    return fo

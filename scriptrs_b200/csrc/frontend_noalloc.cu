@@ -1,0 +1,126 @@
+// sb_frontend_device_noalloc: the batched log-mel frontend for callers that must not allocate.
+//
+// The ordinary entry points (sb_frontend_device, sb_transcribe_chunks, ...) keep grow-only work
+// buffers inside an sb_ctx and enlarge them with cudaMalloc / cudaFree when a batch is bigger than
+// any before.  Two kinds of caller cannot live with that:
+//   * an ingest thread that extracts features while another stream of the same GPU is busy
+//     encoding or decoding: cudaMalloc and cudaFree synchronise the whole device, so one growing
+//     buffer stalls every stream at an unpredictable moment;
+//   * a host program that has handed all device memory to its own pool (an inference server, a
+//     framework allocator) and gives a library nothing but the input and output buffers it names.
+// For them this file holds everything the frontend needs besides its input and output in ONE
+// file-scope device array of fixed size: the constant tables (Hann window, mel taps, twiddles), the
+// per-clip metadata (start, length, first output row) and the per-(clip, feature) mean and standard
+// deviation that the normalisation pass reads.  Every GPU that loads the library carries this array
+// (about 1.1 MB) until the process exits.
+//
+// Consequences the caller has to know:
+//   * at most kNoAllocMaxClips clips per call; more is refused with SB_INVALID_ARGUMENT;
+//   * the first call on a device resolves the array's device address and fills the tables; make
+//     that first call outside any stream capture;
+//   * all calls on a device share the array, and it keeps what the last call left in it.  Nothing in
+//     it has to start at zero (each call rewrites the metadata and the statistics of the clips it
+//     processes before reading them), but two calls whose kernels overlap on the GPU, from
+//     different streams or threads, race on it: serialise them;
+//   * no cudaMalloc, cudaFree or allocating library routine is called, on the first call or later.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstring>
+#include <string>
+
+#include "context.h"
+#include "frontend.h"
+
+namespace sb {
+
+constexpr int kNoAllocMaxClips = 1024;
+
+namespace {
+
+// Layout of the scratch array (all offsets multiples of 256 bytes).
+constexpr size_t kTablesBytes = (sizeof(FrontendTables) + 255) / 256 * 256;
+constexpr size_t kMetaBytes = (3 * (size_t)(kNoAllocMaxClips + 1) * sizeof(int64_t) + 255) / 256 * 256;
+constexpr size_t kStatBytes = (size_t)kNoAllocMaxClips * kMels * sizeof(float);
+constexpr size_t kScratchBytes = kTablesBytes + kMetaBytes + 2 * kStatBytes;
+
+static __device__ __align__(256) unsigned char g_frontend_scratch[kScratchBytes];
+
+constexpr int kMaxDevices = 64;
+// Device address of g_frontend_scratch per device.  The symbol's name is only a host-side handle:
+// kernels must be given the address that cudaGetSymbolAddress returns for the current device.
+unsigned char* g_scratch_ptr[kMaxDevices] = {};
+bool g_ready[kMaxDevices] = {};
+
+int32_t setup_device(int device, cudaStream_t stream) {
+    if (g_ready[device]) return SB_OK;
+    unsigned char* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_frontend_scratch);
+    if (e != cudaSuccess || !ptr) return cuda_fail(e != cudaSuccess ? e : cudaErrorInvalidSymbol, "cudaGetSymbolAddress(frontend scratch)");
+    e = frontend_configure();  // shared-memory opt-in of the log-mel kernel; not an allocation
+    if (e != cudaSuccess) return cuda_fail(e, "frontend_configure");
+    static FrontendTables host_tables;  // static: the copy below may outlive this call
+    if (!build_frontend_tables(&host_tables, nullptr))
+        return fail(SB_INVALID_MODEL_OUTPUT, "mel filterbank rows exceed the tap budget");
+    e = cudaMemcpyAsync(ptr, &host_tables, sizeof(FrontendTables), cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "copy of the frontend tables");
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return cuda_fail(e, "frontend table set-up");
+    g_scratch_ptr[device] = ptr;
+    g_ready[device] = true;
+    return SB_OK;
+}
+
+}  // namespace
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" int32_t sb_frontend_device_noalloc(const float* d_pcm, const int64_t* clip_offsets, int64_t n_clips,
+                                              float preemphasis, int32_t normalize, float* d_feats,
+                                              int64_t* frame_offsets, void* stream) {
+    if (!d_pcm || !clip_offsets || !d_feats) return fail(SB_INVALID_ARGUMENT, "null argument");
+    if (n_clips <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");
+    if (n_clips > kNoAllocMaxClips)
+        return fail(SB_INVALID_ARGUMENT, "sb_frontend_device_noalloc takes at most " + std::to_string(kNoAllocMaxClips) +
+                                             " clips per call (its scratch memory has a fixed size); got " +
+                                             std::to_string(n_clips));
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (device < 0 || device >= kMaxDevices) return fail(SB_INVALID_ARGUMENT, "device index out of range");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t s = setup_device(device, st);
+    if (s != SB_OK) return s;
+
+    // metadata on the stack: starts | lengths | output-row prefix sums
+    const size_t n1 = (size_t)kNoAllocMaxClips + 1;
+    int64_t meta[3 * (kNoAllocMaxClips + 1)] = {};
+    int64_t* fo = meta + 2 * n1;
+    fo[0] = 0;
+    int64_t max_frames = 0;
+    for (int64_t i = 0; i < n_clips; ++i) {
+        const int64_t len = clip_offsets[i + 1] - clip_offsets[i];
+        if (len <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");
+        meta[i] = clip_offsets[i];
+        meta[n1 + i] = len;
+        const int64_t t = frames_for_samples(len);
+        fo[i + 1] = fo[i] + t;
+        if (t > max_frames) max_frames = t;
+    }
+    if (max_frames > (int64_t)65535 * 32) return fail(SB_INVALID_ARGUMENT, "clip too long for one launch");
+    if (frame_offsets) std::memcpy(frame_offsets, fo, sizeof(int64_t) * ((size_t)n_clips + 1));
+
+    unsigned char* base = g_scratch_ptr[device];
+    const FrontendTables* d_tables = reinterpret_cast<const FrontendTables*>(base);
+    int64_t* d_meta = reinterpret_cast<int64_t*>(base + kTablesBytes);
+    float* d_mean = reinterpret_cast<float*>(base + kTablesBytes + kMetaBytes);
+    float* d_std = reinterpret_cast<float*>(base + kTablesBytes + kMetaBytes + kStatBytes);
+    // pageable source: the runtime has staged the bytes by the time the call returns
+    e = cudaMemcpyAsync(d_meta, meta, sizeof(meta), cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return cuda_fail(e, "copy of the clip metadata");
+    e = frontend_launch(d_pcm, d_meta, d_meta + n1, d_meta + 2 * n1, (int)n_clips, (int)max_frames, preemphasis,
+                        d_tables, d_feats, d_mean, d_std, normalize != 0, st);
+    if (e != cudaSuccess) return cuda_fail(e, "frontend launch");
+    return SB_OK;
+}
