@@ -380,9 +380,16 @@ def run_longform(args, rank, world, local):
         """Rank 0 collects the per-task token streams in task order, merges and decodes them."""
         return sbd.gather_and_finish(vocab, n, raws, rank, world)
 
+    phases = {"transcribe_ms": 0.0, "gather_merge_text_ms": 0.0}
+
     def host_step():
+        t_a = time.perf_counter()
         raws = sb.transcribe_chunks(ctx, None, mine, audio_ptr=h_audio.data_ptr(), n_samples=n)
-        return gather_and_finish(raws)
+        t_b = time.perf_counter()
+        r = gather_and_finish(raws)
+        phases["transcribe_ms"] += (t_b - t_a) * 1e3
+        phases["gather_merge_text_ms"] += (time.perf_counter() - t_b) * 1e3
+        return r
 
     sampler = ClockSampler(local)
     sampler.start()
@@ -413,6 +420,7 @@ def run_longform(args, rank, world, local):
     e2e_steps = max(1, min(args.steps, 3))
     res = host_step()
     barrier_sync(world)
+    phases.update(transcribe_ms=0.0, gather_merge_text_ms=0.0)
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         res = host_step()
@@ -475,7 +483,8 @@ def run_longform(args, rank, world, local):
                      "whole_step_tflops_per_gpu": enc_flops / world / (ms_per_step * 1e-3) / 1e12},
         "e2e": {"value": audio_s / (e2e_ms * 1e-3), "unit": "audio-sec/sec", "h2d_bytes_per_step": int(span * 4),
                 "d2h_bytes_per_step": int(n_tokens * 16), "steps": e2e_steps, "ms_per_step": e2e_ms,
-                "transcript_tokens": (len(res.tokens) if res is not None else None)},
+                "transcript_tokens": (len(res) if res is not None else None),
+                "rank0_phases_ms": {k: v / e2e_steps for k, v in phases.items()}},
         "gpu_launches": int(launches),
         "stage_ms_rank0": stage_ms,
         "kernel_ms_rank0": kernel_ms,

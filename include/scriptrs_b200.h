@@ -290,11 +290,22 @@ int32_t sb_result_token(const sb_result* r, int64_t i, uint32_t* token_id, const
                         double* end, float* confidence); /* TimedToken (src/types.rs:1-14) */
 int32_t sb_result_chunk(const sb_result* r, int64_t i, double* start, double* end,
                         const char** text);               /* TranscriptChunk (src/types.rs:16-26) */
+/* All tokens at once: arrays of sb_result_num_tokens entries (any may be NULL); the token texts are
+ * written back to back (UTF-8, no terminators) into text_buf with text_offsets[i] .. text_offsets[i+1]
+ * delimiting token i (text_offsets has n + 1 entries).  *text_len receives the bytes needed. */
+int32_t sb_result_tokens_bulk(const sb_result* r, uint32_t* token_ids, double* starts, double* ends,
+                              float* confidences, int64_t* text_offsets, char* text_buf, int64_t text_cap,
+                              int64_t* text_len);
 void sb_result_free(sb_result* r);
 
 int64_t sb_raw_batch_size(const sb_raw_batch* b);
 int32_t sb_raw_batch_get(const sb_raw_batch* b, int64_t i, int64_t* n, const uint32_t** token_ids,
                          const int64_t** frame_indices, const int64_t** durations, const float** confidences);
+/* The whole batch as flat arrays: sb_raw_batch_total tokens; task i is [offsets[i], offsets[i+1])
+ * (offsets has size + 1 entries; the data arrays may be NULL). */
+int64_t sb_raw_batch_total(const sb_raw_batch* b);
+int32_t sb_raw_batch_flatten(const sb_raw_batch* b, int64_t* offsets, uint32_t* token_ids, int64_t* frame_indices,
+                             int64_t* durations, float* confidences);
 void sb_raw_batch_free(sb_raw_batch* b);
 
 /* ------------------------------------------------------------------ pipelines */

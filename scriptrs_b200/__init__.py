@@ -7,6 +7,6 @@ from ._lib import ScriptrsError, lib, LIB_PATH  # noqa: F401
 from .api import *  # noqa: F401,F403
 from .pipeline import *  # noqa: F401,F403
 from .pipeline import (LongFormConfig, LongFormMode, LongFormTranscriptionPipeline, OverlapChunkConfig,  # noqa: F401
-                       ParakeetTdtDecoder, RawTranscription, TimedToken, TranscriptChunk, TranscriptionPipeline,
+                       ParakeetTdtDecoder, RawBatch, RawTranscription, TimedToken, TranscriptChunk, TranscriptionPipeline,
                        TranscriptionResult, Vocabulary, apply_time_offsets, longform_finish,
                        merge_overlapping_windows, parallel_worker_count, plan_fast, transcribe_chunks)

@@ -98,10 +98,13 @@ SIGNATURES = {
     "sb_result_token": (_I32, [_VP, _I64, C.POINTER(C.c_uint32), C.POINTER(C.c_char_p), C.POINTER(C.c_double),
                                C.POINTER(C.c_double), C.POINTER(C.c_float)]),
     "sb_result_chunk": (_I32, [_VP, _I64, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_char_p)]),
+    "sb_result_tokens_bulk": (_I32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, C.POINTER(_I64)]),
     "sb_result_free": (None, [_VP]),
     "sb_raw_batch_size": (_I64, [_VP]),
     "sb_raw_batch_get": (_I32, [_VP, _I64, C.POINTER(_I64), C.POINTER(_VP), C.POINTER(_VP), C.POINTER(_VP),
                                 C.POINTER(_VP)]),
+    "sb_raw_batch_total": (_I64, [_VP]),
+    "sb_raw_batch_flatten": (_I32, [_VP, _VP, _VP, _VP, _VP, _VP]),
     "sb_raw_batch_free": (None, [_VP]),
     "sb_transcribe_chunks": (_I32, [_VP, _VP, _I64, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),
     "sb_transcribe_chunks_device": (_I32, [_VP, _VP, _I64, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),

@@ -245,6 +245,29 @@ int32_t sb_result_chunk(const sb_result* r, int64_t i, double* start, double* en
     return SB_OK;
 }
 
+int32_t sb_result_tokens_bulk(const sb_result* r, uint32_t* token_ids, double* starts, double* ends,
+                              float* confidences, int64_t* text_offsets, char* text_buf, int64_t text_cap,
+                              int64_t* text_len) {
+    if (!r) return fail(SB_INVALID_ARGUMENT, "result is null");
+    const auto& tk = r->r.tokens;
+    int64_t total = 0;
+    for (const auto& t : tk) total += (int64_t)t.text.size();
+    if (text_len) *text_len = total;
+    if (text_buf && text_cap < total) return fail(SB_BUFFER_TOO_SMALL, "token text buffer too small");
+    int64_t off = 0;
+    for (size_t i = 0; i < tk.size(); ++i) {
+        if (token_ids) token_ids[i] = tk[i].token_id;
+        if (starts) starts[i] = tk[i].start;
+        if (ends) ends[i] = tk[i].end;
+        if (confidences) confidences[i] = tk[i].confidence;
+        if (text_offsets) text_offsets[i] = off;
+        if (text_buf) std::memcpy(text_buf + off, tk[i].text.data(), tk[i].text.size());
+        off += (int64_t)tk[i].text.size();
+    }
+    if (text_offsets) text_offsets[tk.size()] = off;
+    return SB_OK;
+}
+
 void sb_result_free(sb_result* r) { delete r; }
 
 int64_t sb_raw_batch_size(const sb_raw_batch* b) { return b ? (int64_t)b->items.size() : 0; }
@@ -258,6 +281,33 @@ int32_t sb_raw_batch_get(const sb_raw_batch* b, int64_t i, int64_t* n, const uin
     if (frm) *frm = r.frame_indices.data();
     if (dur) *dur = r.durations.data();
     if (conf) *conf = r.confidences.data();
+    return SB_OK;
+}
+
+int64_t sb_raw_batch_total(const sb_raw_batch* b) {
+    int64_t n = 0;
+    if (b)
+        for (const auto& r : b->items) n += (int64_t)r.token_ids.size();
+    return n;
+}
+
+int32_t sb_raw_batch_flatten(const sb_raw_batch* b, int64_t* offsets, uint32_t* tok, int64_t* frm, int64_t* dur,
+                             float* conf) {
+    if (!b || !offsets) return fail(SB_INVALID_ARGUMENT, "null argument");
+    int64_t off = 0;
+    for (size_t i = 0; i < b->items.size(); ++i) {
+        const RawTokens& r = b->items[i];
+        const size_t k = r.token_ids.size();
+        offsets[i] = off;
+        if (k) {
+            if (tok) std::memcpy(tok + off, r.token_ids.data(), k * sizeof(uint32_t));
+            if (frm) std::memcpy(frm + off, r.frame_indices.data(), k * sizeof(int64_t));
+            if (dur) std::memcpy(dur + off, r.durations.data(), k * sizeof(int64_t));
+            if (conf) std::memcpy(conf + off, r.confidences.data(), k * sizeof(float));
+        }
+        off += (int64_t)k;
+    }
+    offsets[b->items.size()] = off;
     return SB_OK;
 }
 

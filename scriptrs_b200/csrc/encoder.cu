@@ -266,40 +266,70 @@ constexpr size_t kAttSmemBytes = ((size_t)(2 * kMaxEncFrames + kPosRows) * kRowS
                                  (size_t)(kAttThreads / 32) * (2 * kHeadDim + 192) * sizeof(float);
 
 // ---------------------------------------------------------------- GLU + depthwise conv + BN + SiLU
-// in bf16 [rows x 2048] -> out bf16 [rows x 1024].  grid (time blocks of 32, clips, 4 channel blocks).
+// in bf16 [rows x 2048] -> out bf16 [rows x 1024].  grid (time blocks of 32, clips, 4 channel blocks of 256).
+// Phase 1: 16-byte loads of the value and gate halves, GLU, fp32 tile [40 rows x 256 channels] in shared
+// memory (zero outside the clip).  Phase 2: each thread convolves two channels over 16 rows.
 constexpr int kDwRows = 32;
+constexpr int kDwHalo = (kConvK - 1) / 2;
+constexpr int kDwTileRows = kDwRows + kConvK - 1;
 __global__ void __launch_bounds__(256)
 glu_dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, const float* __restrict__ w,
                   const float* __restrict__ b, bf16* __restrict__ out) {
+    __shared__ __align__(16) float tile[kDwTileRows][256];
     const int clip = blockIdx.y;
     const int r0 = t3_off[clip];
     const int t = t3_off[clip + 1] - r0;
     const int tb = blockIdx.x * kDwRows;
     if (tb >= t) return;
-    const int c = blockIdx.z * 256 + threadIdx.x;
-    float wr[kConvK];
-#pragma unroll
-    for (int k = 0; k < kConvK; ++k) wr[k] = w[k * kDModel + c];
-    const float bias = b[c];
-    float g[kDwRows + kConvK - 1];
-#pragma unroll
-    for (int r = 0; r < kDwRows + kConvK - 1; ++r) {
-        const int tt = tb - (kConvK - 1) / 2 + r;
-        float v = 0.0f;
+    const int c0 = blockIdx.z * 256;
+    for (int idx = threadIdx.x; idx < kDwTileRows * 32; idx += 256) {
+        const int r = idx >> 5, v8 = (idx & 31) * 8;
+        const int tt = tb - kDwHalo + r;
+        float g[8];
         if (tt >= 0 && tt < t) {
-            const bf16* p = in + (size_t)(r0 + tt) * (2 * kDModel) + c;
-            const float a = __bfloat162float(p[0]), gate = __bfloat162float(p[kDModel]);
-            v = a / (1.0f + __expf(-gate));
+            const bf16* p = in + (size_t)(r0 + tt) * (2 * kDModel) + c0 + v8;
+            const uint4 av = *reinterpret_cast<const uint4*>(p);
+            const uint4 gv = *reinterpret_cast<const uint4*>(p + kDModel);
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 af = __bfloat1622float2(a2[e]), gf = __bfloat1622float2(g2[e]);
+                g[2 * e] = af.x / (1.0f + __expf(-gf.x));
+                g[2 * e + 1] = af.y / (1.0f + __expf(-gf.y));
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g[e] = 0.0f;
         }
-        g[r] = v;
+        *reinterpret_cast<float4*>(&tile[r][v8]) = make_float4(g[0], g[1], g[2], g[3]);
+        *reinterpret_cast<float4*>(&tile[r][v8 + 4]) = make_float4(g[4], g[5], g[6], g[7]);
     }
+    __syncthreads();
+    const int cp = (threadIdx.x & 127) * 2, rh = (threadIdx.x >> 7) * (kDwRows / 2);
+    float w0[kConvK], w1[kConvK];
 #pragma unroll
-    for (int r = 0; r < kDwRows; ++r) {
-        if (tb + r >= t) break;
-        float acc = bias;
+    for (int k = 0; k < kConvK; ++k) {
+        w0[k] = w[k * kDModel + c0 + cp];
+        w1[k] = w[k * kDModel + c0 + cp + 1];
+    }
+    const float b0 = b[c0 + cp], b1 = b[c0 + cp + 1];
+    float2 win[kDwRows / 2 + kConvK - 1];
 #pragma unroll
-        for (int k = 0; k < kConvK; ++k) acc = fmaf(wr[k], g[r + k], acc);
-        out[(size_t)(r0 + tb + r) * kDModel + c] = __float2bfloat16(acc / (1.0f + __expf(-acc)));
+    for (int r = 0; r < kDwRows / 2 + kConvK - 1; ++r) win[r] = *reinterpret_cast<const float2*>(&tile[rh + r][cp]);
+#pragma unroll
+    for (int r = 0; r < kDwRows / 2; ++r) {
+        if (tb + rh + r >= t) break;
+        float a0 = b0, a1 = b1;
+#pragma unroll
+        for (int k = 0; k < kConvK; ++k) {
+            a0 = fmaf(w0[k], win[r + k].x, a0);
+            a1 = fmaf(w1[k], win[r + k].y, a1);
+        }
+        a0 = a0 / (1.0f + __expf(-a0));
+        a1 = a1 / (1.0f + __expf(-a1));
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(r0 + tb + rh + r) * kDModel + c0 + cp) =
+            __floats2bfloat162_rn(a0, a1);
     }
 }
 

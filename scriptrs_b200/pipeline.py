@@ -32,13 +32,29 @@ class TranscriptChunk:
     text: str
 
 
-@dataclass
 class TranscriptionResult:
-    """src/types.rs:28-49"""
-    text: str
-    chunks: list
-    tokens: list
-    duration_seconds: float
+    """src/types.rs:28-49.  Token fields are kept as arrays (token_ids, starts, ends, confidences, token
+    texts); `.tokens` builds the list of TimedToken on first use."""
+
+    def __init__(self, text, chunks, duration_seconds, token_ids, starts, ends, confidences, token_texts):
+        self.text = text
+        self.chunks = chunks
+        self.duration_seconds = duration_seconds
+        self.token_ids, self.starts, self.ends, self.confidences = token_ids, starts, ends, confidences
+        self._token_texts = token_texts  # (utf-8 bytes, offsets)
+        self._tokens = None
+
+    def __len__(self):
+        return len(self.token_ids)
+
+    @property
+    def tokens(self):
+        if self._tokens is None:
+            buf, off = self._token_texts
+            self._tokens = [TimedToken(int(self.token_ids[i]), buf[off[i]:off[i + 1]].decode("utf-8"),
+                                       float(self.starts[i]), float(self.ends[i]), float(self.confidences[i]))
+                            for i in range(len(self.token_ids))]
+        return self._tokens
 
 
 @dataclass
@@ -112,7 +128,46 @@ def apply_time_offsets(raw: RawTranscription, frame_offset: int, context_frames:
     return RawTranscription(tok[:k], frm[:k], dur[:k], conf[:k])
 
 
+class RawBatch:
+    """Per-task token streams of one batch as flat arrays; behaves like a list of RawTranscription."""
+
+    def __init__(self, offsets, token_ids, frame_indices, durations, confidences):
+        self.offsets, self.token_ids, self.frame_indices = offsets, token_ids, frame_indices
+        self.durations, self.confidences = durations, confidences
+
+    def __len__(self):
+        return len(self.offsets) - 1
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return [self[k] for k in range(*i.indices(len(self)))]
+        if i < 0:
+            i += len(self)
+        a, b = int(self.offsets[i]), int(self.offsets[i + 1])
+        return RawTranscription(self.token_ids[a:b], self.frame_indices[a:b], self.durations[a:b], self.confidences[a:b])
+
+    def __iter__(self):
+        return (self[i] for i in range(len(self)))
+
+    def flat(self):
+        return self.token_ids, self.frame_indices, self.durations, self.confidences, self.offsets
+
+    @classmethod
+    def concat(cls, parts):
+        """Batches of consecutive task blocks -> one batch."""
+        offs = [np.zeros(1, np.int64)]
+        base = 0
+        for p in parts:
+            offs.append(p.offsets[1:] + base)
+            base += int(p.offsets[-1])
+        cat = lambda attr: np.concatenate([getattr(p, attr) for p in parts])
+        return cls(np.concatenate(offs), cat("token_ids"), cat("frame_indices"), cat("durations"), cat("confidences"))
+
+
 def _concat(windows):
+    if isinstance(windows, RawBatch):
+        t, f, d, c, o = windows.flat()
+        return t, f, d, c, np.ascontiguousarray(o, np.int64), int(o[-1])
     offs = np.zeros(len(windows) + 1, np.int64)
     for i, w in enumerate(windows):
         offs[i + 1] = offs[i] + len(w.token_ids)
@@ -178,17 +233,21 @@ class Vocabulary:
 def _take_result(h) -> TranscriptionResult:
     L = _lib.lib()
     try:
-        tokens = []
-        for i in range(L.sb_result_num_tokens(h)):
-            tid, txt, a, b, cf = C.c_uint32(), C.c_char_p(), C.c_double(), C.c_double(), C.c_float()
-            check(L.sb_result_token(h, i, C.byref(tid), C.byref(txt), C.byref(a), C.byref(b), C.byref(cf)))
-            tokens.append(TimedToken(tid.value, txt.value.decode("utf-8"), a.value, b.value, cf.value))
+        n = int(L.sb_result_num_tokens(h))
+        ids, starts, ends = np.zeros(n, np.uint32), np.zeros(n, np.float64), np.zeros(n, np.float64)
+        confs, offs = np.zeros(n, np.float32), np.zeros(n + 1, np.int64)
+        need = C.c_int64()
+        check(L.sb_result_tokens_bulk(h, None, None, None, None, None, None, 0, C.byref(need)))
+        buf = C.create_string_buffer(max(need.value, 1))
+        check(L.sb_result_tokens_bulk(h, _ptr(ids), _ptr(starts), _ptr(ends), _ptr(confs), _ptr(offs), buf,
+                                      need.value, C.byref(need)))
         chunks = []
         for i in range(L.sb_result_num_chunks(h)):
             txt, a, b = C.c_char_p(), C.c_double(), C.c_double()
             check(L.sb_result_chunk(h, i, C.byref(a), C.byref(b), C.byref(txt)))
             chunks.append(TranscriptChunk(a.value, b.value, txt.value.decode("utf-8")))
-        return TranscriptionResult(L.sb_result_text(h).decode("utf-8"), chunks, tokens, L.sb_result_duration(h))
+        return TranscriptionResult(L.sb_result_text(h).decode("utf-8"), chunks, L.sb_result_duration(h), ids, starts,
+                                   ends, confs, (buf.raw[: need.value], offs))
     finally:
         L.sb_result_free(h)
 
@@ -216,7 +275,7 @@ def _audio(a) -> np.ndarray:
 def transcribe_chunks(ctx: Context, audio: np.ndarray, tasks, config: TranscriptionConfig | None = None,
                       audio_ptr: int | None = None, n_samples: int | None = None, on_device: bool = False):
     """Batched transcribe_task for a list of (audio_start, audio_end, global_sample_offset, context_samples).
-    Returns a list of RawTranscription.  `audio_ptr`/`n_samples` let a caller pass pinned host memory, or,
+    Returns a RawBatch (a list-like of RawTranscription).  `audio_ptr`/`n_samples` let a caller pass pinned host memory, or,
     with on_device=True, a device pointer."""
     if audio_ptr is None:
         audio = _audio(audio)
@@ -229,24 +288,15 @@ def transcribe_chunks(ctx: Context, audio: np.ndarray, tasks, config: Transcript
     fn = _lib.lib().sb_transcribe_chunks_device if on_device else _lib.lib().sb_transcribe_chunks
     check(fn(ctx.handle, C.c_void_p(audio_ptr), n_samples, arr, len(tasks), C.byref(cfg), C.byref(h)))
     L = _lib.lib()
-    out = []
     try:
-        for i in range(L.sb_raw_batch_size(h)):
-            n = C.c_int64()
-            p = [C.c_void_p() for _ in range(4)]
-            check(L.sb_raw_batch_get(h, i, C.byref(n), *[C.byref(x) for x in p]))
-            k = n.value
-
-            def arr_of(ptr, ctype, dt):
-                if k == 0:
-                    return np.zeros(0, dt)
-                return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(ctype)), shape=(k,)).astype(dt, copy=True)
-
-            out.append(RawTranscription(arr_of(p[0], C.c_uint32, np.uint32), arr_of(p[1], C.c_int64, np.int64),
-                                        arr_of(p[2], C.c_int64, np.int64), arr_of(p[3], C.c_float, np.float32)))
+        n_items, total = int(L.sb_raw_batch_size(h)), int(L.sb_raw_batch_total(h))
+        offs = np.zeros(n_items + 1, np.int64)
+        tok, frm = np.zeros(total, np.uint32), np.zeros(total, np.int64)
+        dur, conf = np.zeros(total, np.int64), np.zeros(total, np.float32)
+        check(L.sb_raw_batch_flatten(h, _ptr(offs), _ptr(tok), _ptr(frm), _ptr(dur), _ptr(conf)))
     finally:
         L.sb_raw_batch_free(h)
-    return out
+    return RawBatch(offs, tok, frm, dur, conf)
 
 
 def longform_finish(vocab: Vocabulary, audio_len: int, windows) -> TranscriptionResult:
