@@ -361,7 +361,10 @@ def run_longform(args, rank, world, local):
     stream = torch.cuda.Stream(device=device)
     ctx.set_stream(stream.cuda_stream)
     layers = args.layers
-    sb.load_model(ctx, seeded_model(layers), encoder_layers=layers, has_encoder=True, has_decoder=True)
+    fp8 = args.precision == "fp8"
+    sb.load_model(ctx, seeded_model(layers), encoder_layers=layers, has_encoder=True, has_decoder=True, fp8_weights=fp8)
+    if fp8:
+        ctx.set_option("fp8", 1)
     vocab = sb.Vocabulary.from_tokens(bench_vocab_tokens())
 
     n = int(args.hours * 3600 * 16000)
@@ -468,7 +471,7 @@ def run_longform(args, rank, world, local):
         "metric": "audio-sec/sec (RTFx), Parakeet-TDT-0.6B long-form transcription", "value": value,
         "unit": "audio-sec/sec", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
+        "dtype": ("fp8_e4m3 (ff/qkv/pointwise GEMMs) + bf16" if fp8 else "bf16"), "data": "synthetic",
         "config": {"workload": f"config 4: {args.hours:g} h of 16 kHz audio, overlap chunks of 14.88 s + 2 s overlap "
                                f"({len(tasks)} tasks), frontend -> bf16 FastConformer ({layers} blocks) -> TDT greedy "
                                f"decode -> overlap merge", "tasks": len(tasks), "tasks_per_gpu": len(mine),
@@ -585,6 +588,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="longform", choices=["longform", "frontend"])
     ap.add_argument("--hours", type=float, default=8.0, help="longform workload: hours of audio (default 8)")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8"], help="longform: encoder GEMM precision")
     ap.add_argument("--layers", type=int, default=24, help="longform workload: Conformer blocks (default 24)")
     ap.add_argument("--clips", type=int, default=0, help="frontend workload: clips per GPU (default 1024)")
     ap.add_argument("--stage-breakdown", action="store_true", help="longform: also time the three stage entry points")

@@ -102,7 +102,9 @@ int32_t sb_ctx_synchronize(sb_ctx* ctx);
 /* Number of kernels this context has launched since creation. */
 int64_t sb_ctx_kernel_launches(const sb_ctx* ctx);
 
-/* Tuning and test switches.  "simt_attention" (0/1): run the relative-position attention on CUDA cores
+/* Tuning and test switches.  "fp8" (0/1): run the feed-forward, QKV and first pointwise GEMMs of every
+ * Conformer block in FP8 e4m3 (per-row activation scales, per-output-channel weight scales, fp32
+ * accumulation); needs a model loaded with fp8_weights.  "simt_attention" (0/1): run the relative-position attention on CUDA cores
  * instead of the tensor-core kernel; "workspace_budget_mb": bytes of encoder intermediates per group
  * of clips (default 12288). */
 int32_t sb_ctx_set_option(sb_ctx* ctx, const char* name, int64_t value);
@@ -179,6 +181,8 @@ typedef struct sb_model_desc {
     int32_t scale_input;    /* multiply the sub-sampling output by sqrt(d_model) */
     int32_t has_encoder;
     int32_t has_decoder;
+    int32_t fp8_weights;    /* also keep e4m3 copies (one scale per output channel) of the Conformer
+                               blocks' feed-forward, QKV and first pointwise weights, for the "fp8" option */
 } sb_model_desc;
 
 /* Uploads the weights to the context's GPU in the layouts the kernels use (bf16 GEMM operands,

@@ -40,7 +40,7 @@ class TensorC(C.Structure):
 
 class ModelDescC(C.Structure):
     _fields_ = [("encoder_layers", C.c_int32), ("scale_input", C.c_int32), ("has_encoder", C.c_int32),
-                ("has_decoder", C.c_int32)]
+                ("has_decoder", C.c_int32), ("fp8_weights", C.c_int32)]
 
 
 class ChunkTaskC(C.Structure):

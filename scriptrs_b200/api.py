@@ -166,13 +166,13 @@ def gemm(ctx: Context, d_a: int, d_w: int, d_out: int, M: int, N: int, K: int, d
 
 
 def load_model(ctx: Context, weights: dict, encoder_layers: int, scale_input: bool = False,
-               has_encoder: bool = True, has_decoder: bool = False):
+               has_encoder: bool = True, has_decoder: bool = False, fp8_weights: bool = False):
     """Uploads a dict of named float32 arrays (see sb_model_load for the names)."""
     keep = {k: np.ascontiguousarray(v, np.float32) for k, v in weights.items()}
     arr = (_lib.TensorC * max(len(keep), 1))()
     for i, (k, v) in enumerate(keep.items()):
         arr[i] = _lib.TensorC(k.encode(), v.ctypes.data, v.size)
-    desc = _lib.ModelDescC(encoder_layers, int(scale_input), int(has_encoder), int(has_decoder))
+    desc = _lib.ModelDescC(encoder_layers, int(scale_input), int(has_encoder), int(has_decoder), int(fp8_weights))
     check(_lib.lib().sb_model_load(ctx.handle, C.byref(desc), arr, len(keep)))
 
 

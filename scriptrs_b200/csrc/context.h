@@ -66,6 +66,8 @@ struct sb_ctx {
     sb::Buffer clip_off, frame_off, col_mean, col_std, pcm_stage, feat_stage, enc_stage;
     sb::Model* model = nullptr;
     sb::Profiler prof;
+    bool fp8 = false;             // FP8 e4m3 GEMMs in the Conformer blocks (needs fp8 weights)
+    int fp8_mask = 15;            // which GEMMs take the FP8 path: 1 ff up, 2 ff down, 4 QKV, 8 first pointwise
     bool simt_attention = false;  // reference implementation of the attention kernel on CUDA cores (tests)
     sb::EncoderWorkspace* enc_ws = nullptr;
     sb::DecodeWorkspace* dec_ws = nullptr;

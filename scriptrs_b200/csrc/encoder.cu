@@ -14,6 +14,7 @@
 //                        softmax, PV; the relative shift is index arithmetic, never materialised
 //   glu_dwconv_kernel    GLU + depthwise conv k = 9 ('same' within the clip) + folded BatchNorm + SiLU
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -161,6 +162,102 @@ layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gamma, c
             pk.y = *reinterpret_cast<uint32_t*>(&p1);
             reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + (size_t)row * kDModel)[lane + 32 * k] = pk;
         }
+    }
+}
+
+// LayerNorm with an e4m3 output row and its scale: q = y / scale, scale = max|y| / 448.
+__global__ void __launch_bounds__(256)
+layernorm_fp8_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                     uint8_t* __restrict__ out, float* __restrict__ row_scale, int rows) {
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * kDModel);
+    float4 v[8];
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        v[k] = xr[lane + 32 * k];
+        s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mean = s * (1.0f / kDModel);
+    float q = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
+        q += (a * a + b * b) + (c * c + d * d);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    const float rstd = rsqrtf(q * (1.0f / kDModel) + 1e-5f);
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(beta);
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float4 g = g4[lane + 32 * k], b = b4[lane + 32 * k];
+        v[k].x = (v[k].x - mean) * rstd * g.x + b.x;
+        v[k].y = (v[k].y - mean) * rstd * g.y + b.y;
+        v[k].z = (v[k].z - mean) * rstd * g.z + b.z;
+        v[k].w = (v[k].w - mean) * rstd * g.w + b.w;
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[k].x), fabsf(v[k].y)), fmaxf(fabsf(v[k].z), fabsf(v[k].w))));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax > 0.0f ? amax * (1.0f / 448.0f) : 1.0f;
+    const float inv = 1.0f / scale;
+    if (lane == 0) row_scale[row] = scale;
+    uint32_t* o32 = reinterpret_cast<uint32_t*>(out + (size_t)row * kDModel);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const uint32_t b0 = __nv_cvt_float_to_fp8(v[k].x * inv, __NV_SATFINITE, __NV_E4M3);
+        const uint32_t b1 = __nv_cvt_float_to_fp8(v[k].y * inv, __NV_SATFINITE, __NV_E4M3);
+        const uint32_t b2 = __nv_cvt_float_to_fp8(v[k].z * inv, __NV_SATFINITE, __NV_E4M3);
+        const uint32_t b3 = __nv_cvt_float_to_fp8(v[k].w * inv, __NV_SATFINITE, __NV_E4M3);
+        o32[lane + 32 * k] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    }
+}
+
+// bf16 [rows x 4096] -> e4m3 [rows x 4096] + per-row scale (one warp per row, the row stays in registers).
+__global__ void __launch_bounds__(256)
+quantize_rows4096_kernel(const bf16* __restrict__ in, uint8_t* __restrict__ out, float* __restrict__ row_scale,
+                         int rows) {
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const uint4* src = reinterpret_cast<const uint4*>(in + (size_t)row * kFF);
+    uint4 raw[16];
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        raw[k] = src[lane + 32 * k];
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax > 0.0f ? amax * (1.0f / 448.0f) : 1.0f;
+    const float inv = 1.0f / scale;
+    if (lane == 0) row_scale[row] = scale;
+    uint2* dst = reinterpret_cast<uint2*>(out + (size_t)row * kFF);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
+        uint32_t w[2] = {0, 0};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            const uint32_t b0 = __nv_cvt_float_to_fp8(f.x * inv, __NV_SATFINITE, __NV_E4M3);
+            const uint32_t b1 = __nv_cvt_float_to_fp8(f.y * inv, __NV_SATFINITE, __NV_E4M3);
+            w[e >> 1] |= (b0 | (b1 << 8)) << (16 * (e & 1));
+        }
+        dst[lane + 32 * k] = make_uint2(w[0], w[1]);
     }
 }
 
@@ -345,6 +442,19 @@ cudaError_t run_gemm(sb_ctx* c, const char* label, const void* a, const bf16* w,
     return e;
 }
 
+cudaError_t run_gemm_fp8(sb_ctx* c, const char* label, const uint8_t* a, const float* a_scale, const uint8_t* w,
+                         const float* w_scale, const float* bias, void* out, int M, int N, int K, int act, int mode,
+                         float alpha) {
+    GemmArgs g{};
+    g.a = a; g.w = w; g.bias = bias; g.row_scale = a_scale; g.col_scale = w_scale; g.out = out; g.M = M; g.N = N; g.K = K;
+    g.ldo = N; g.act = act; g.out_mode = mode; g.alpha = alpha; g.fp8 = true;
+    c->launches += 1;
+    c->prof.begin(label, c->stream);
+    cudaError_t e = gemm_launch(g, c->sm_count, c->d_error, c->stream);
+    c->prof.end(c->stream);
+    return e;
+}
+
 #define PROF(label, launch)              \
     do {                                 \
         c->prof.begin(label, st);        \
@@ -417,6 +527,10 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     ENC_CUDA(ws.h.ensure((size_t)R3 * kFF * sizeof(bf16)));
     ENC_CUDA(ws.att.ensure((size_t)R3 * kDModel * sizeof(bf16)));
     ENC_CUDA(ws.vt.ensure(attention_vt_bytes(n)));
+    if (c->fp8 && m.has_fp8) {
+        ENC_CUDA(ws.h8.ensure((size_t)R3 * kFF));
+        ENC_CUDA(ws.rs.ensure((size_t)R3 * 2 * sizeof(float)));
+    }
 
     // sub-sampling
     PROF("sub_conv0", (sub_conv0_kernel<<<R1, 256, 0, st>>>(d_feats, d_t0, d_t1, n, m.sub0_w, m.sub0_b, ws.y0.as<bf16>())));
@@ -433,15 +547,60 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     bf16* a = ws.a.as<bf16>();
     bf16* h = ws.h.as<bf16>();
     bf16* att = ws.att.as<bf16>();
+    const bool fp8 = c->fp8 && m.has_fp8;
+    uint8_t* a8 = reinterpret_cast<uint8_t*>(a);        // e4m3 LayerNorm output shares the bf16 buffer
+    uint8_t* h8 = ws.h8.as<uint8_t>();
+    float* rs_a = ws.rs.as<float>();
+    float* rs_h = rs_a + R3;
+    // feed-forward module: x += 0.5 * W2 silu(W1 LN(x) + b1) + b2
+    auto feed_forward = [&](const float* g, const float* b, const bf16* w1, const uint8_t* w1q, const float* w1s,
+                            const float* b1, const bf16* w2, const uint8_t* w2q, const float* w2s,
+                            const float* b2) -> cudaError_t {
+        if (fp8 && (c->fp8_mask & 3)) {
+            if (c->fp8_mask & 1) {
+                PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, g, b, a8, rs_a, R3)));
+                ENC_CUDA(run_gemm_fp8(c, "gemm_ff_up_fp8", a8, rs_a, w1q, w1s, b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
+            } else {
+                PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, g, b, a, R3)));
+                ENC_CUDA(run_gemm(c, "gemm_ff_up", a, w1, b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
+            }
+            if (c->fp8_mask & 2) {
+                PROF("quantize_rows", (quantize_rows4096_kernel<<<ln_grid, 256, 0, st>>>(h, h8, rs_h, R3)));
+                ENC_CUDA(run_gemm_fp8(c, "gemm_ff_down_fp8", h8, rs_h, w2q, w2s, b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
+                c->launches += 1;
+            } else {
+                ENC_CUDA(run_gemm(c, "gemm_ff_down", h, w2, b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
+            }
+            c->launches += 1;
+        } else {
+            PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, g, b, a, R3)));
+            ENC_CUDA(run_gemm(c, "gemm_ff_up", a, w1, b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
+            ENC_CUDA(run_gemm(c, "gemm_ff_down", h, w2, b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
+            c->launches += 1;
+        }
+        return cudaSuccess;
+    };
+    // LayerNorm followed by a projection to bf16 (QKV, first pointwise conv)
+    auto norm_project = [&](const char* label, const char* label8, const float* g, const float* b, const bf16* w,
+                            const uint8_t* wq, const float* wsc, const float* bias, int N) -> cudaError_t {
+        if (fp8 && (c->fp8_mask & (N == 3 * kDModel ? 4 : 8))) {
+            PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, g, b, a8, rs_a, R3)));
+            ENC_CUDA(run_gemm_fp8(c, label8, a8, rs_a, wq, wsc, bias, h, R3, N, kDModel, kActNone, kOutBf16, 1.0f));
+        } else {
+            PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, g, b, a, R3)));
+            ENC_CUDA(run_gemm(c, label, a, w, bias, h, R3, N, kDModel, kActNone, kOutBf16, 1.0f));
+        }
+        c->launches += 1;
+        return cudaSuccess;
+    };
     for (int l = 0; l < m.layers; ++l) {
         const LayerWeights& L = m.L[l];
         // x += 0.5 * FF1(LN x)
-        PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_ff1_g, L.ln_ff1_b, a, R3)));
-        ENC_CUDA(run_gemm(c, "gemm_ff_up", a, L.ff1_w1, L.ff1_b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
-        ENC_CUDA(run_gemm(c, "gemm_ff_down", h, L.ff1_w2, L.ff1_b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
+        ENC_CUDA(feed_forward(L.ln_ff1_g, L.ln_ff1_b, L.ff1_w1, L.ff1_w1_q, L.ff1_w1_s, L.ff1_b1, L.ff1_w2, L.ff1_w2_q,
+                              L.ff1_w2_s, L.ff1_b2));
         // x += MHA(LN x)
-        PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_att_g, L.ln_att_b, a, R3)));
-        ENC_CUDA(run_gemm(c, "gemm_qkv", a, L.qkv_w, L.qkv_b, h, R3, 3 * kDModel, kDModel, kActNone, kOutBf16, 1.0f));
+        ENC_CUDA(norm_project("gemm_qkv", "gemm_qkv_fp8", L.ln_att_g, L.ln_att_b, L.qkv_w, L.qkv_w_q, L.qkv_w_s, L.qkv_b,
+                              3 * kDModel));
         if (c->simt_attention) {
             PROF("relpos_attention_simt", (relpos_attention_kernel<<<dim3(kHeads, n), kAttThreads, kAttSmemBytes, st>>>(
                                               h, d_t3, L.pos_proj, L.bias_u, L.bias_v, att)));
@@ -453,19 +612,18 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
         }
         ENC_CUDA(run_gemm(c, "gemm_attn_out", att, L.o_w, L.o_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
         // x += Conv(LN x)
-        PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_conv_g, L.ln_conv_b, a, R3)));
-        ENC_CUDA(run_gemm(c, "gemm_conv_pw1", a, L.pw1_w, L.pw1_b, h, R3, 2 * kDModel, kDModel, kActNone, kOutBf16, 1.0f));
+        ENC_CUDA(norm_project("gemm_conv_pw1", "gemm_conv_pw1_fp8", L.ln_conv_g, L.ln_conv_b, L.pw1_w, L.pw1_w_q,
+                              L.pw1_w_s, L.pw1_b, 2 * kDModel));
         PROF("glu_dwconv", (glu_dwconv_kernel<<<dim3((max_t3 + kDwRows - 1) / kDwRows, n, kDModel / 256), 256, 0, st>>>(
                                h, d_t3, L.dw_w, L.dw_b, att)));
         ENC_CUDA(run_gemm(c, "gemm_conv_pw2", att, L.pw2_w, L.pw2_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
         // x += 0.5 * FF2(LN x)
-        PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, L.ln_ff2_g, L.ln_ff2_b, a, R3)));
-        ENC_CUDA(run_gemm(c, "gemm_ff_up", a, L.ff2_w1, L.ff2_b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
-        ENC_CUDA(run_gemm(c, "gemm_ff_down", h, L.ff2_w2, L.ff2_b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
+        ENC_CUDA(feed_forward(L.ln_ff2_g, L.ln_ff2_b, L.ff2_w1, L.ff2_w1_q, L.ff2_w1_s, L.ff2_b1, L.ff2_w2, L.ff2_w2_q,
+                              L.ff2_w2_s, L.ff2_b2));
         // x = LN_out(x); the last block writes straight into the caller's buffer
         float* dst = (l == m.layers - 1) ? d_out + (size_t)enc_off_all[c0] * kDModel : x;
         PROF("layernorm", (layernorm_kernel<true><<<ln_grid, 256, 0, st>>>(x, L.ln_out_g, L.ln_out_b, dst, R3)));
-        c->launches += 7;
+        c->launches += 3;
     }
     if (m.layers == 0)
         ENC_CUDA(cudaMemcpyAsync(d_out + (size_t)enc_off_all[c0] * kDModel, x, (size_t)R3 * kDModel * sizeof(float),

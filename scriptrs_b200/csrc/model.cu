@@ -4,6 +4,8 @@
 // src/model.rs:22-35; asset layout src/models.rs:5-8).  Tensor names are those of the published
 // FastConformer / Parakeet checkpoints ("subsampling.layers.0.weight", "layers.3.self_attn.q_proj.weight",
 // ...) plus "predictor.*" / "joint.*" for the TDT decoder.
+#include <cuda_fp8.h>
+
 #include <cmath>
 #include <cstring>
 #include <map>
@@ -67,6 +69,29 @@ struct Loader {
         if (d && cudaMemcpy(d, tmp.data(), n * sizeof(bf16), cudaMemcpyHostToDevice) != cudaSuccess && err.empty())
             err = "cudaMemcpy failed while loading the model";
         return d;
+    }
+
+    // per-output-channel e4m3 quantisation: row n of w[rows x cols] becomes q[n][:] * scale[n]
+    void up_fp8(const float* h, size_t rows, size_t cols, uint8_t** q_out, float** s_out) {
+        *q_out = nullptr;
+        *s_out = nullptr;
+        if (!h) return;
+        std::vector<uint8_t> q(rows * cols);
+        std::vector<float> sc(rows);
+        for (size_t r = 0; r < rows; ++r) {
+            float amax = 0.0f;
+            for (size_t k = 0; k < cols; ++k) amax = std::fmax(amax, std::fabs(h[r * cols + k]));
+            const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+            const float inv = 1.0f / scale;
+            sc[r] = scale;
+            for (size_t k = 0; k < cols; ++k)
+                q[r * cols + k] = (uint8_t)__nv_cvt_float_to_fp8(h[r * cols + k] * inv, __NV_SATFINITE, __NV_E4M3);
+        }
+        uint8_t* d = static_cast<uint8_t*>(dalloc(q.size()));
+        if (d && cudaMemcpy(d, q.data(), q.size(), cudaMemcpyHostToDevice) != cudaSuccess && err.empty())
+            err = "cudaMemcpy failed while loading the model";
+        *q_out = d;
+        *s_out = up_f32(sc.data(), sc.size());
     }
 
     float* f32(const std::string& name, int64_t n) { return up_f32(get(name, n), (size_t)n); }
@@ -163,6 +188,13 @@ int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensor
             L.ff1_w2 = ld.b16(p + "feed_forward1.linear2.weight", d * ff); L.ff1_b2 = ld.f32(p + "feed_forward1.linear2.bias", d);
             L.ff2_w1 = ld.b16(p + "feed_forward2.linear1.weight", ff * d); L.ff2_b1 = ld.f32(p + "feed_forward2.linear1.bias", ff);
             L.ff2_w2 = ld.b16(p + "feed_forward2.linear2.weight", d * ff); L.ff2_b2 = ld.f32(p + "feed_forward2.linear2.bias", d);
+            if (desc->fp8_weights) {
+                ld.up_fp8(ld.get(p + "feed_forward1.linear1.weight", ff * d), ff, d, &L.ff1_w1_q, &L.ff1_w1_s);
+                ld.up_fp8(ld.get(p + "feed_forward1.linear2.weight", d * ff), d, ff, &L.ff1_w2_q, &L.ff1_w2_s);
+                ld.up_fp8(ld.get(p + "feed_forward2.linear1.weight", ff * d), ff, d, &L.ff2_w1_q, &L.ff2_w1_s);
+                ld.up_fp8(ld.get(p + "feed_forward2.linear2.weight", d * ff), d, ff, &L.ff2_w2_q, &L.ff2_w2_s);
+                ld.up_fp8(ld.get(p + "conv.pointwise_conv1.weight", 2 * d * d), 2 * d, d, &L.pw1_w_q, &L.pw1_w_s);
+            }
             const float* qw = ld.get(p + "self_attn.q_proj.weight", d * d);
             const float* kw = ld.get(p + "self_attn.k_proj.weight", d * d);
             const float* vw = ld.get(p + "self_attn.v_proj.weight", d * d);
@@ -178,6 +210,7 @@ int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensor
                 std::memcpy(b3.data() + d, kb, sizeof(float) * d);
                 std::memcpy(b3.data() + 2 * d, vb, sizeof(float) * d);
                 L.qkv_w = ld.up_bf16(w3.data(), w3.size());
+                if (desc->fp8_weights) ld.up_fp8(w3.data(), 3 * d, d, &L.qkv_w_q, &L.qkv_w_s);
                 L.qkv_b = ld.up_f32(b3.data(), b3.size());
             }
             L.o_w = ld.b16(p + "self_attn.o_proj.weight", d * d);
@@ -221,6 +254,7 @@ int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensor
             }
         }
         m->has_encoder = true;
+        m->has_fp8 = desc->fp8_weights != 0;
     }
 
     if (desc->has_decoder && ld.err.empty()) {

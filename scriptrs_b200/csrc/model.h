@@ -47,12 +47,15 @@ struct LayerWeights {
     float* dw_b;  // [1024], depthwise bias and BatchNorm shift folded
     bf16* pw2_w;  // [1024 x 1024]
     float* pw2_b;
+    // e4m3 copies with one scale per output channel (w = q * scale[n]) for the FP8 path
+    uint8_t *ff1_w1_q, *ff1_w2_q, *ff2_w1_q, *ff2_w2_q, *qkv_w_q, *pw1_w_q;
+    float *ff1_w1_s, *ff1_w2_s, *ff2_w1_s, *ff2_w2_s, *qkv_w_s, *pw1_w_s;
 };
 
 struct Model {
     int layers = 0;
     float xscale = 1.0f;
-    bool has_encoder = false, has_decoder = false;
+    bool has_encoder = false, has_decoder = false, has_fp8 = false;
     // sub-sampling
     float *sub0_w = nullptr, *sub0_b = nullptr;  // [256 x 9], [256]
     float *dw1_w = nullptr, *dw1_b = nullptr;    // [9 x 256] tap-major, [256]

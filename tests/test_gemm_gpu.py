@@ -81,3 +81,27 @@ def test_unsupported_shapes_are_rejected(ctx):
     with pytest.raises(sb.ScriptrsError) as e:
         sb.gemm(ctx, a.data_ptr(), w.data_ptr(), out.data_ptr(), 128, 128, 96, out_mode=1)
     assert e.value.status == 11
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 256, 1024), (4032, 4096, 1024), (4032, 1024, 4096)])
+def test_fp8_e4m3_with_row_and_channel_scales(ctx, M, N, K):
+    """e4m3 operands, fp32 accumulation, per-row and per-output-channel scales applied in the epilogue."""
+    import scriptrs_b200 as sb
+
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.05
+    rs = a.abs().amax(dim=1) / 448.0
+    cs = w.abs().amax(dim=1) / 448.0
+    aq = (a / rs[:, None]).to(torch.float8_e4m3fn)
+    wq = (w / cs[:, None]).to(torch.float8_e4m3fn)
+    bias = torch.randn(N, device="cuda", generator=g) * 0.1
+    ref = (aq.float() @ wq.float().t()) * rs[:, None] * cs[None, :] + bias
+    out = torch.full((M, N), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    sb.gemm(ctx, aq.data_ptr(), wq.data_ptr(), out.data_ptr(), M, N, K, d_bias=bias.data_ptr(), out_mode=1, fp8=True,
+            d_row_scale=rs.data_ptr(), d_col_scale=cs.data_ptr())
+    ctx.synchronize()
+    assert torch.isfinite(out).all()
+    err = (out - ref).norm() / ref.norm()
+    assert err < 1e-5, float(err)   # same quantised operands on both sides: only the summation order differs
