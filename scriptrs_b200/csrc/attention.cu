@@ -11,7 +11,7 @@
 //   MMA 2    S_bd = Q Pseg^T         (128 x 320, columns 192..511): column q of row i is relative
 //            position i - j for j = q - ((T'-1) - i - first_row); the "relative shift" is therefore a
 //            per-row offset, applied when each thread copies its own row out of tensor memory
-//   softmax  one thread per query row: scores = (S_ac + u.k_j + S_bd + v.p) / sqrt(128) in a private
+//   softmax  two threads per query row (each half of the columns): scores = (S_ac + u.k_j + S_bd + v.p) / sqrt(128) in a private
 //            fp32 row of shared memory, max, exp, sum; probabilities written as the bf16 A operand
 //   MMA 3    O = P V                  (128 x 128, V supplied transposed so that it is K-major)
 //   store    O / sum -> bf16, staged through shared memory, coalesced rows
@@ -32,7 +32,8 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kAT = 128;             // threads per CTA = query rows per block
+constexpr int kAT = 128;             // query rows per block
+constexpr int kATh = 256;            // threads per CTA: two per query row, each owning half of the columns
 constexpr int kNK = 192;             // key columns of S_ac (T' padded)
 constexpr int kNP = 320;             // table rows per query block (256 + 64)
 constexpr int kSStride = 189;        // floats per private score row (odd: conflict-free reads)
@@ -49,7 +50,7 @@ __device__ __forceinline__ uint32_t idesc_bf16(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(kAT, 1)
+__global__ void __launch_bounds__(kATh, 1)
 relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_pos,
                            const __grid_constant__ CUtensorMap map_vt, const int* __restrict__ t3_off,
                            const float* __restrict__ bias_u, const float* __restrict__ pos_vp,
@@ -85,7 +86,7 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
     }
-    us[tid] = bias_u[head * kHeadDim + tid];
+    if (tid < kHeadDim) us[tid] = bias_u[head * kHeadDim + tid];
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -122,13 +123,13 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
             }
         }
         // v . p for the table rows of this block
-        for (int q = tid; q < kNP; q += kAT) {
+        for (int q = tid; q < kNP; q += kATh) {
             const int p = p_first + plo + q;
             vp[q] = p < kPosRows ? pos_vp[p * kHeads + head] : 0.0f;
         }
         if (!__syncthreads_and(mbar_wait(bar_in, qb & 1, abort_flag))) { ok = false; break; }
         // u . k_j from the swizzled K tile
-        for (int j = tid; j < kNK; j += kAT) {
+        for (int j = tid; j < kNK; j += kATh) {
             float acc = 0.0f;
             if (j < t) {
 #pragma unroll
@@ -169,14 +170,18 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
         mma_phase ^= 1;
         tc_fence_after();
 
-        const int i = i0 + tid;
+        const int rl = tid & (kAT - 1), half = tid >> 7;  // row of the block, column half
+        const int i = i0 + rl;
         const bool row_ok = i < t;
-        float* srow = reinterpret_cast<float*>(p1) + tid * kSStride;
-        const uint32_t tq = tmem + ((uint32_t)(warp * 32) << 16);
-        // S_bd: relative shift while copying this thread's row out of tensor memory
+        float* srow = reinterpret_cast<float*>(p1) + rl * kSStride;
+        const uint32_t tq = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        float* sump = uk;            // [2][128] partial sums   (uk and the head of vp are dead by then)
+        float* mxp = uk + 2 * kAT;   // [2][128] partial maxima (inside vp, dead after the shift pass)
+        // S_bd: relative shift while copying this thread's row out of tensor memory (chunks alternate
+        // between the two threads of a row)
         const int shift = (t - 1) - i - plo;  // j = q - shift
 #pragma unroll 1
-        for (int c = 0; c < kNP / 32; ++c) {
+        for (int c = half; c < kNP / 32; c += 2) {
             uint32_t v[32];
             tmem_ld32(tq + kNK + 32 * c, v);
             tmem_wait_ld();
@@ -187,10 +192,11 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
                 if (row_ok && j >= 0 && j < t) srow[j] = __uint_as_float(v[jj]) + vp[q];
             }
         }
+        __syncthreads();  // both threads of a row have written their share of the shifted row
         // scores and row maximum
         float mx = -INFINITY;
 #pragma unroll 1
-        for (int c = 0; c < kNK / 32; ++c) {
+        for (int c = half; c < kNK / 32; c += 2) {
             uint32_t v[32];
             tmem_ld32(tq + 32 * c, v);
             tmem_wait_ld();
@@ -204,10 +210,13 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
                 }
             }
         }
+        mxp[half * kAT + rl] = mx;
+        __syncthreads();
+        mx = fmaxf(mxp[rl], mxp[kAT + rl]);
         // probabilities -> bf16 A operand (K-major, 128-byte swizzle, three blocks of 64 keys)
         float sum = 0.0f;
 #pragma unroll 1
-        for (int j8 = 0; j8 < kNK; j8 += 8) {
+        for (int j8 = 8 * half; j8 < kNK; j8 += 16) {
             float e[8];
 #pragma unroll
             for (int u8 = 0; u8 < 8; ++u8) {
@@ -223,8 +232,9 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
             pk.z = *reinterpret_cast<uint32_t*>(&q2);
             pk.w = *reinterpret_cast<uint32_t*>(&q3);
             const int kb = j8 >> 6, ch = (j8 & 63) >> 3;
-            *reinterpret_cast<uint4*>(p2 + kb * 16384 + tid * 128 + ((ch ^ (tid & 7)) << 4)) = pk;
+            *reinterpret_cast<uint4*>(p2 + kb * 16384 + rl * 128 + ((ch ^ (rl & 7)) << 4)) = pk;
         }
+        sump[half * kAT + rl] = sum;
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
@@ -243,9 +253,9 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
         mma_phase ^= 1;
         tc_fence_after();
         // O / sum -> bf16 -> staging rows -> coalesced global rows
-        const float inv = row_ok ? 1.0f / sum : 0.0f;
+        const float inv = row_ok ? 1.0f / (sump[rl] + sump[kAT + rl]) : 0.0f;
 #pragma unroll 1
-        for (int c = 0; c < kHeadDim / 32; ++c) {
+        for (int c = 2 * half; c < 2 * half + 2; ++c) {
             uint32_t v[32];
             tmem_ld32(tq + 32 * c, v);
             tmem_wait_ld();
@@ -260,13 +270,13 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
                 pk.y = *reinterpret_cast<uint32_t*>(&o1);
                 pk.z = *reinterpret_cast<uint32_t*>(&o2);
                 pk.w = *reinterpret_cast<uint32_t*>(&o3);
-                *reinterpret_cast<uint4*>(p1 + tid * kOStride + c * 64 + q * 16) = pk;
+                *reinterpret_cast<uint4*>(p1 + rl * kOStride + c * 64 + q * 16) = pk;
             }
         }
         tc_fence_before();
         __syncthreads();
         const int valid = min(kAT, t - i0);
-        for (int r = warp; r < valid; r += kAT / 32) {
+        for (int r = warp; r < valid; r += kATh / 32) {
             const uint2 val = *reinterpret_cast<const uint2*>(p1 + r * kOStride + lane * 8);
             *reinterpret_cast<uint2*>(out + (size_t)(row0 + i0 + r) * kDModel + head * kHeadDim + lane * 4) = val;
         }
@@ -368,7 +378,7 @@ cudaError_t attention_launch(const bf16* qkv, int rows, const int* d_t3_off, int
         !map_bf16(&mv, vt, (int64_t)n_clips * kHeads * kHeadDim, kNK))
         return cudaErrorInvalidValue;
     transpose_v_kernel<<<dim3(kHeads, n_clips), 256, 0, st>>>(qkv, d_t3_off, vt);
-    relpos_attention_tc_kernel<<<dim3(kHeads, n_clips), kAT, kAttSmem, st>>>(mq, mp, mv, d_t3_off, bias_u, pos_vp, out,
+    relpos_attention_tc_kernel<<<dim3(kHeads, n_clips), kATh, kAttSmem, st>>>(mq, mp, mv, d_t3_off, bias_u, pos_vp, out,
                                                                             d_error);
     return cudaGetLastError();
 }

@@ -13,8 +13,8 @@
 // Sequences advance at different rates, so every iteration first builds (redundantly in every CTA,
 // hence in a deterministic order) the list of live sequences and of those whose predictor must run,
 // then runs four skinny fp32 GEMM phases over those lists (LSTM layer 0, layer 1 with the cell update
-// fused into the epilogue, predictor projection, joint output) and a per-sequence arg-max / update
-// phase, with a grid-wide barrier between phases.  Weights (35 MB fp32) stay L2-resident; the
+// fused into the epilogue, predictor projection which also forms the joint input relu(enc + pred), joint
+// output) and a per-sequence arg-max / update phase, with a grid-wide barrier between phases.  Weights (35 MB fp32) stay L2-resident; the
 // encoder projection is hoisted out of the loop.  Sums run in a fixed order, so results are
 // reproducible; arg-max ties go to the lowest index.
 #include <cooperative_groups.h>
@@ -30,11 +30,10 @@ namespace sb {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kTileSeq = 32;   // sequences per tile
-constexpr int kTileRow = 64;   // weight rows per tile (LSTM: 16 units x 4 gates)
+constexpr int kTileRow = 64;   // weight rows per tile (LSTM: 16 units x 4 gates, gates adjacent)
 constexpr int kTileK = 32;
-constexpr int kWStride = kTileRow + 1;
-constexpr int kXStride = kTileSeq + 1;
+constexpr int kKPad = kTileK + 4;        // floats per operand row of a chunk in shared memory
+constexpr int kRingFloats = 4 * (kTileRow + 64) * kKPad;  // cp.async ring: 4 stages of 64 + 64 rows, or 6 of 64 + 16
 
 enum Phase { kLstm0 = 0, kLstm1 = 1, kPred = 2, kOut = 3 };
 
@@ -79,101 +78,140 @@ __device__ void build_lists(const DecodeState& s, int n_seq, int* act, int* upd,
     }
 }
 
-// One phase: C[list x rows] = X[list x K] * W[rows x K]^T, tiled 32 sequences x 64 rows, fp32, K in
-// ascending order.  Thread (sg = tid / 16, ul = tid % 16) owns sequences {2 sg, 2 sg + 1} and local rows
-// {ul, ul + 16, ul + 32, ul + 48}; for the LSTM phases those four rows are the i, f, g, o gates of one unit.
-template <int PHASE>
-__device__ void run_phase(const DecodeWeights& w, const DecodeState& s, const int* list, int n_list, float* Ws,
-                          float* Xs) {
+__device__ __forceinline__ void cp_async16(float* dst_smem, const float* src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst_smem);
+    const int bytes = valid ? 16 : 0;  // 0: nothing is read, the destination is zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One phase: C[list x rows] = X[list x K] * W[rows x K]^T in fp32.  Tiles of (16 SPT) sequences x 64 weight rows;
+// thread (sg = tid / 16, ul = tid % 16) owns sequences sg * SPT .. + SPT - 1 and local rows ul, ul + 16, ul + 32,
+// ul + 48, which for the LSTM phases are the i, f, g, o gates of unit 16 rt + ul, so the cell update stays in the
+// thread.  K is walked in chunks of 32 through a cp.async ring (both operands are plain 16-byte row copies; rows are
+// padded to 36 floats, which keeps the float4 reads of 8 neighbouring threads on distinct banks).  Every output is
+// one fp32 fused-multiply-add chain over ascending k, whatever SPT is, so a sequence's result does not depend on
+// how many other sequences are alive.
+template <int PHASE, int SPT>
+__device__ void run_phase(const DecodeWeights& w, const DecodeState& s, const int* list, int n_list, float* ring) {
     constexpr bool lstm = PHASE == kLstm0 || PHASE == kLstm1;
     constexpr int K = lstm ? 2 * kPredHidden : kPredHidden;
+    constexpr int ldw = lstm ? kPredHidden : K;  // row pitch of each weight matrix
     constexpr int rows_total = lstm ? 4 * kPredHidden : (PHASE == kPred ? kJointDim : kJointOut);
     constexpr int row_tiles = lstm ? kPredHidden / 16 : (rows_total + kTileRow - 1) / kTileRow;
     constexpr int layer = PHASE == kLstm1 ? 1 : 0;
-    const float* W_a = nullptr;  // first K-half
-    const float* W_b = nullptr;  // second K-half (LSTM: hidden-to-hidden)
-    if (PHASE == kLstm0 || PHASE == kLstm1) {
-        W_a = w.w_ih + (size_t)layer * 4 * kPredHidden * kPredHidden;
-        W_b = w.w_hh + (size_t)layer * 4 * kPredHidden * kPredHidden;
-    } else if (PHASE == kPred) {
-        W_a = w.w_pred;
-    } else {
-        W_a = w.w_out;
-    }
+    constexpr int seq_t = 16 * SPT;
+    constexpr int n_chunks = K / kTileK;
+    constexpr int stage_floats = (kTileRow + seq_t) * kKPad;
+    constexpr int stages = kRingFloats / stage_floats;
+    constexpr int n_xl = (seq_t * 8 + kThreads - 1) / kThreads;  // activation float4 slots per thread
+    static_assert(stages >= 3, "ring too small");
+    const float* W_a = lstm ? w.w_ih + (size_t)layer * 4 * kPredHidden * kPredHidden : (PHASE == kPred ? w.w_pred : w.w_out);
+    const float* W_b = lstm ? w.w_hh + (size_t)layer * 4 * kPredHidden * kPredHidden : W_a;
     const int tid = threadIdx.x;
     const int sg = tid >> 4, ul = tid & 15;
-    const int seq_tiles = (n_list + kTileSeq - 1) / kTileSeq;
+    const int seq_tiles = (n_list + seq_t - 1) / seq_t;
     const int n_tiles = seq_tiles * row_tiles;
     const size_t BH = (size_t)s.n_seq * kPredHidden;
+    const int lj = tid & 7, lrow = tid >> 3;  // load slots: float4 lj of rows lrow (+ 32)
 
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const int st = tile / row_tiles, rt = tile % row_tiles;
-        const int s0 = st * kTileSeq;
-        float acc[2][4];
+        const int s0 = st * seq_t;
+        size_t woff[2];
+        bool wok[2];
 #pragma unroll
-        for (int a = 0; a < 2; ++a)
+        for (int q = 0; q < 2; ++q) {
+            const int r = lrow + 32 * q;  // local weight row
+            const int grow = lstm ? (r >> 4) * kPredHidden + rt * 16 + (r & 15) : rt * kTileRow + r;
+            wok[q] = grow < rows_total;
+            woff[q] = (size_t)(wok[q] ? grow : 0) * ldw + 4 * lj;
+        }
+        const float* xsrc_a[n_xl];
+        const float* xsrc_b[n_xl];
+        bool xok[n_xl];
+#pragma unroll
+        for (int q = 0; q < n_xl; ++q) {
+            const int lsq = lrow + 32 * q;  // local sequence
+            const int li = s0 + lsq;
+            xok[q] = lsq < seq_t && li < n_list;
+            const int b = xok[q] ? list[li] : 0;
+            if (PHASE == kLstm0) {
+                xsrc_a[q] = w.embedding + (size_t)s.last_token[b] * kPredHidden;
+                xsrc_b[q] = s.h + (size_t)b * kPredHidden;
+            } else if (PHASE == kLstm1) {
+                xsrc_a[q] = s.h_new + (size_t)b * kPredHidden;
+                xsrc_b[q] = s.h + BH + (size_t)b * kPredHidden;
+            } else if (PHASE == kPred) {
+                xsrc_a[q] = s.h_new + BH + (size_t)b * kPredHidden;
+                xsrc_b[q] = xsrc_a[q];
+            } else {
+                xsrc_a[q] = s.z + (size_t)b * kJointDim;
+                xsrc_b[q] = xsrc_a[q];
+            }
+        }
+        auto issue = [&](int chunk) {
+            float* Ws = ring + (chunk % stages) * stage_floats;
+            float* Xs = Ws + kTileRow * kKPad;
+            const bool second = lstm && chunk >= n_chunks / 2;  // LSTM: k >= 640 comes from the recurrent operands
+            const int k0 = (second ? chunk - n_chunks / 2 : chunk) * kTileK;
+            const float* Wm = second ? W_b : W_a;
+#pragma unroll
+            for (int q = 0; q < 2; ++q)
+                cp_async16(Ws + (lrow + 32 * q) * kKPad + 4 * lj, Wm + woff[q] + k0, wok[q]);
+#pragma unroll
+            for (int q = 0; q < n_xl; ++q) {
+                const int lsq = lrow + 32 * q;
+                if (lsq < seq_t)
+                    cp_async16(Xs + lsq * kKPad + 4 * lj, (second ? xsrc_b[q] : xsrc_a[q]) + k0 + 4 * lj, xok[q]);
+            }
+        };
+        float acc[SPT][4];
+#pragma unroll
+        for (int a = 0; a < SPT; ++a)
 #pragma unroll
             for (int r = 0; r < 4; ++r) acc[a][r] = 0.0f;
 
-        for (int k0 = 0; k0 < K; k0 += kTileK) {
-            __syncthreads();
-            // weights chunk: 64 rows x 32 k, stored k-major
-            for (int i = tid; i < kTileRow * kTileK; i += kThreads) {
-                const int r = i >> 5, k = i & 31;
-                int grow;
-                if (lstm) grow = (r >> 4) * kPredHidden + rt * 16 + (r & 15);
-                else grow = rt * kTileRow + r;
-                float v = 0.0f;
-                if (grow < rows_total) {
-                    if (lstm) {
-                        const int kk = k0 + k;
-                        v = kk < kPredHidden ? W_a[(size_t)grow * kPredHidden + kk]
-                                             : W_b[(size_t)grow * kPredHidden + kk - kPredHidden];
-                    } else {
-                        v = W_a[(size_t)grow * K + k0 + k];
-                    }
-                }
-                Ws[k * kWStride + r] = v;
-            }
-            // activations chunk: 32 sequences x 32 k, stored k-major
-            for (int i = tid; i < kTileSeq * kTileK; i += kThreads) {
-                const int sl = i >> 5, k = i & 31;
-                const int li = s0 + sl;
-                float v = 0.0f;
-                if (li < n_list) {
-                    const int b = list[li];
-                    const int kk = k0 + k;
-                    if (PHASE == kLstm0) {
-                        v = kk < kPredHidden ? w.embedding[(size_t)s.last_token[b] * kPredHidden + kk]
-                                             : s.h[(size_t)b * kPredHidden + kk - kPredHidden];
-                    } else if (PHASE == kLstm1) {
-                        v = kk < kPredHidden ? s.h_new[(size_t)b * kPredHidden + kk]
-                                             : s.h[BH + (size_t)b * kPredHidden + kk - kPredHidden];
-                    } else if (PHASE == kPred) {
-                        v = s.h_new[BH + (size_t)b * kPredHidden + kk];
-                    } else {
-                        const size_t row = (size_t)(s.enc_off[b] + s.frame_idx[b]);
-                        v = fmaxf(s.enc_proj[row * kJointDim + kk] + s.pred[(size_t)b * kJointDim + kk], 0.0f);
-                    }
-                }
-                Xs[k * kXStride + sl] = v;
-            }
-            __syncthreads();
-#pragma unroll 8
-            for (int k = 0; k < kTileK; ++k) {
-                const float x0 = Xs[k * kXStride + 2 * sg], x1 = Xs[k * kXStride + 2 * sg + 1];
+        __syncthreads();  // the previous tile's readers are done with the ring
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const float wv = Ws[k * kWStride + ul + 16 * r];
-                    acc[0][r] = fmaf(x0, wv, acc[0][r]);
-                    acc[1][r] = fmaf(x1, wv, acc[1][r]);
-                }
+        for (int c = 0; c < stages - 1; ++c) {
+            if (c < n_chunks) issue(c);
+            cp_async_commit();
+        }
+        for (int c = 0; c < n_chunks; ++c) {
+            cp_async_wait<stages - 2>();
+            __syncthreads();
+            if (c + stages - 1 < n_chunks) issue(c + stages - 1);
+            cp_async_commit();
+            const float* Ws = ring + (c % stages) * stage_floats;
+            const float* Xs = Ws + kTileRow * kKPad;
+#pragma unroll
+            for (int k = 0; k < kTileK; k += 4) {
+                float4 wv[4], xv[SPT];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) wv[r] = *reinterpret_cast<const float4*>(Ws + (ul + 16 * r) * kKPad + k);
+#pragma unroll
+                for (int a = 0; a < SPT; ++a) xv[a] = *reinterpret_cast<const float4*>(Xs + (sg * SPT + a) * kKPad + k);
+#pragma unroll
+                for (int a = 0; a < SPT; ++a)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        float t = acc[a][r];
+                        t = fmaf(xv[a].x, wv[r].x, t);
+                        t = fmaf(xv[a].y, wv[r].y, t);
+                        t = fmaf(xv[a].z, wv[r].z, t);
+                        t = fmaf(xv[a].w, wv[r].w, t);
+                        acc[a][r] = t;
+                    }
             }
         }
+        cp_async_wait<0>();
         // epilogue
 #pragma unroll
-        for (int a = 0; a < 2; ++a) {
-            const int li = s0 + 2 * sg + a;
+        for (int a = 0; a < SPT; ++a) {
+            const int li = s0 + sg * SPT + a;
             if (li >= n_list) continue;
             const int b = list[li];
             if (lstm) {
@@ -186,31 +224,37 @@ __device__ void run_phase(const DecodeWeights& w, const DecodeState& s, const in
                 s.c_new[idx] = cn;
                 s.h_new[idx] = sigmoid_f(go) * tanhf(cn);
             } else {
+                const size_t erow = (size_t)(s.enc_off[b] + s.frame_idx[b]) * kJointDim;
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const int row = rt * kTileRow + ul + 16 * r;
                     if (row >= rows_total) continue;
-                    if (PHASE == kPred) s.pred[(size_t)b * kJointDim + row] = acc[a][r] + w.b_pred[row];
-                    else s.logits[(size_t)b * kJointOut + row] = acc[a][r] + w.b_out[row];
+                    if (PHASE == kPred) {
+                        const float pv = acc[a][r] + w.b_pred[row];
+                        s.pred[(size_t)b * kJointDim + row] = pv;
+                        s.z[(size_t)b * kJointDim + row] = fmaxf(s.enc_proj[erow + row] + pv, 0.0f);
+                    } else {
+                        s.logits[(size_t)b * kJointOut + row] = acc[a][r] + w.b_out[row];
+                    }
                 }
             }
         }
     }
 }
 
-// One warp per live sequence: arg-max, confidence, record, commit, advance (model.rs:79-90,180-209).
-__device__ void decide_phase(const DecodeState& s, const int* act, int n_act, int step) {
-    const int lane = threadIdx.x & 31;
-    const int warps_per_cta = kThreads / 32;
+// One CTA per live sequence: arg-max, confidence, record, commit, advance (model.rs:79-90,180-209).
+// redf / redi: shared scratch of 16 floats and 8 ints.
+__device__ void decide_phase(const DecodeState& s, const int* act, int n_act, float* redf, int* redi) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t BH = (size_t)s.n_seq * kPredHidden;
-    for (int li = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); li < n_act; li += gridDim.x * warps_per_cta) {
+    for (int li = blockIdx.x; li < n_act; li += gridDim.x) {
         const int b = act[li];
         const float* lg = s.logits + (size_t)b * kJointOut;
         float best = -INFINITY;
         int bi = 0x7fffffff;
-        for (int i = lane; i < kVocab; i += 32) {
+        for (int i = tid; i < kVocab; i += kThreads) {
             const float v = lg[i];
-            if (v > best) { best = v; bi = i; }  // ascending i per lane: first maximum kept
+            if (v > best) { best = v; bi = i; }  // ascending i per thread: first maximum kept
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -218,10 +262,26 @@ __device__ void decide_phase(const DecodeState& s, const int* act, int n_act, in
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
         }
+        __syncthreads();  // the scratch is free again
+        if (lane == 0) { redf[warp] = best; redi[warp] = bi; }
+        __syncthreads();
+        best = redf[0];
+        bi = redi[0];
+#pragma unroll
+        for (int wv = 1; wv < kThreads / 32; ++wv) {
+            const float ov = redf[wv];
+            const int oi = redi[wv];
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
         float sum = 0.0f;
-        for (int i = lane; i < kVocab; i += 32) sum += expf(lg[i] - best);
+        for (int i = tid; i < kVocab; i += kThreads) sum += expf(lg[i] - best);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) redf[8 + warp] = sum;
+        __syncthreads();
+        sum = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < kThreads / 32; ++wv) sum += redf[8 + wv];
         int dur = 0;
         {
             float dv = lg[kVocab];
@@ -229,25 +289,32 @@ __device__ void decide_phase(const DecodeState& s, const int* act, int n_act, in
                 if (lg[kVocab + i] > dv) { dv = lg[kVocab + i]; dur = i; }
         }
         const int token = bi;
-        if (s.trace && step < s.trace_cap) {
-            float* tr = s.trace + ((size_t)b * s.trace_cap + s.n_steps[b]) * kJointOut;
-            if (s.n_steps[b] < s.trace_cap)
-                for (int i = lane; i < kJointOut; i += 32) tr[i] = lg[i];
+        const int nsteps = s.n_steps[b];
+        if (s.trace && nsteps < s.trace_cap) {
+            float* tr = s.trace + ((size_t)b * s.trace_cap + nsteps) * kJointOut;
+            for (int i = tid; i < kJointOut; i += kThreads) tr[i] = lg[i];
         }
         const int frame = s.frame_idx[b];
         const bool emit = token != kVocab - 1;
+        int emitted = s.emitted[b] + (emit ? 1 : 0);
+        int nf = frame;
+        if (dur > 0) { nf += dur; emitted = 0; }
+        else if (!emit || emitted >= kMaxSymbols) { nf += 1; emitted = 0; }
         if (emit) {
-            // commit the cached predictor state (model.rs:188-189)
-            for (int l = 0; l < kPredLayers; ++l)
-                for (int i = lane; i < kPredHidden; i += 32) {
-                    const size_t idx = (size_t)l * BH + (size_t)b * kPredHidden + i;
-                    s.h[idx] = s.h_new[idx];
-                    s.c[idx] = s.c_new[idx];
-                }
+            // commit the cached predictor state (model.rs:188-189); the predictor runs again next iteration
+            for (int i = tid; i < kPredLayers * kPredHidden; i += kThreads) {
+                const size_t idx = (size_t)(i / kPredHidden) * BH + (size_t)b * kPredHidden + (i % kPredHidden);
+                s.h[idx] = s.h_new[idx];
+                s.c[idx] = s.c_new[idx];
+            }
+        } else if (nf < s.enc_len[b]) {
+            // the cached predictor output stays valid: refresh the joint input for the new frame
+            const size_t erow = (size_t)(s.enc_off[b] + nf) * kJointDim;
+            for (int i = tid; i < kJointDim; i += kThreads)
+                s.z[(size_t)b * kJointDim + i] = fmaxf(s.enc_proj[erow + i] + s.pred[(size_t)b * kJointDim + i], 0.0f);
         }
-        __syncwarp();
-        if (lane == 0) {
-            int emitted = s.emitted[b];
+        __syncthreads();  // every thread has read the state it needs before thread 0 updates it
+        if (tid == 0) {
             if (emit) {
                 const int n = s.n_tokens[b];
                 if (n < s.max_tokens) {
@@ -262,16 +329,12 @@ __device__ void decide_phase(const DecodeState& s, const int* act, int n_act, in
                 s.n_tokens[b] = n + 1;
                 s.last_token[b] = token;
                 s.cache_valid[b] = 0;
-                emitted += 1;
             } else {
                 s.cache_valid[b] = 1;
             }
-            int nf = frame;
-            if (dur > 0) { nf += dur; emitted = 0; }
-            else if (!emit || emitted >= kMaxSymbols) { nf += 1; emitted = 0; }
             s.frame_idx[b] = nf;
             s.emitted[b] = emitted;
-            s.n_steps[b] += 1;
+            s.n_steps[b] = nsteps + 1;
         }
     }
 }
@@ -280,29 +343,60 @@ __global__ void __launch_bounds__(kThreads, 2)
 tdt_decode_kernel(DecodeWeights w, DecodeState s, int max_steps) {
     cg::grid_group grid = cg::this_grid();
     extern __shared__ __align__(16) unsigned char dsm[];
-    float* Ws = reinterpret_cast<float*>(dsm);
-    float* Xs = Ws + kTileK * kWStride;
-    int* act = reinterpret_cast<int*>(Xs + kTileK * kXStride);
+    float* ring = reinterpret_cast<float*>(dsm);
+    float* redf = ring + kRingFloats;
+    int* redi = reinterpret_cast<int*>(redf + 16);
+    int* act = redi + 16;
     int* upd = act + s.n_seq;
     int* counts = upd + s.n_seq;
     int* scan = counts + 2;
 
+    long long tacc[12] = {};
+    const bool timed = s.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+    long long tprev = clock64();
+    auto lap = [&](int slot) {
+        if (timed) {
+            const long long now = clock64();
+            tacc[slot] += now - tprev;
+            tprev = now;
+        }
+    };
+    int steps_done = 0;
     for (int step = 0; step < max_steps; ++step) {
         build_lists(s, s.n_seq, act, upd, counts, scan);
         const int n_act = counts[0], n_upd = counts[1];
+        lap(0);
         if (n_act == 0) break;
+        ++steps_done;
+        // few sequences: 16 per tile (one per thread) so that a phase is short; many: 64 per tile (four per thread)
+        const bool small_upd = ((n_upd + 15) / 16) * (kPredHidden / 16) <= (int)gridDim.x;
+        const bool small_act = ((n_act + 15) / 16) * ((kJointOut + kTileRow - 1) / kTileRow) <= (int)gridDim.x;
         if (n_upd > 0) {
-            run_phase<kLstm0>(w, s, upd, n_upd, Ws, Xs);
+            if (small_upd) run_phase<kLstm0, 1>(w, s, upd, n_upd, ring); else run_phase<kLstm0, 4>(w, s, upd, n_upd, ring);
+            lap(1);
             grid.sync();
-            run_phase<kLstm1>(w, s, upd, n_upd, Ws, Xs);
+            lap(2);
+            if (small_upd) run_phase<kLstm1, 1>(w, s, upd, n_upd, ring); else run_phase<kLstm1, 4>(w, s, upd, n_upd, ring);
+            lap(3);
             grid.sync();
-            run_phase<kPred>(w, s, upd, n_upd, Ws, Xs);
+            lap(4);
+            if (small_upd) run_phase<kPred, 1>(w, s, upd, n_upd, ring); else run_phase<kPred, 4>(w, s, upd, n_upd, ring);
+            lap(5);
             grid.sync();
+            lap(6);
         }
-        run_phase<kOut>(w, s, act, n_act, Ws, Xs);
+        if (small_act) run_phase<kOut, 1>(w, s, act, n_act, ring); else run_phase<kOut, 4>(w, s, act, n_act, ring);
+        lap(7);
         grid.sync();
-        decide_phase(s, act, n_act, step);
+        lap(8);
+        decide_phase(s, act, n_act, redf, redi);
+        lap(9);
         grid.sync();
+        lap(10);
+    }
+    if (timed) {
+        for (int i = 0; i < 11; ++i) s.timing[i] = tacc[i];
+        s.timing[11] = steps_done;
     }
 }
 
@@ -344,7 +438,7 @@ sgemm_nt_bias_kernel(const float* __restrict__ A, const float* __restrict__ W, c
 }
 
 size_t decode_smem_bytes(int n_seq) {
-    return sizeof(float) * (kTileK * kWStride + kTileK * kXStride) + sizeof(int) * (2 * (size_t)n_seq + 2 + 16);
+    return sizeof(float) * (kRingFloats + 16) + sizeof(int) * (16 + 2 * (size_t)n_seq + 2 + 16);
 }
 
 }  // namespace
@@ -366,7 +460,10 @@ cudaError_t decode_launch(const DecodeWeights& w, const DecodeState& s, int max_
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tdt_decode_kernel, kThreads, smem);
     if (e != cudaSuccess) return e;
     if (per_sm < 1) return cudaErrorInvalidConfiguration;
+    // A grid-wide barrier over two CTAs per SM costs several times one over a single CTA per SM (measured: about
+    // 17 us against 2 us), which only a batch large enough to keep both CTAs in arithmetic repays.
     if (per_sm > 2) per_sm = 2;
+    if (s.n_seq < 1024) per_sm = 1;
     const int grid = sm_count * per_sm;
     DecodeWeights wl = w;
     DecodeState sl = s;

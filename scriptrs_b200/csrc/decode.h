@@ -22,11 +22,13 @@ struct DecodeState {
     const int* enc_len;     // [n_seq] T'
     int *frame_idx, *emitted, *last_token, *cache_valid, *n_tokens, *n_steps;
     float *h, *c, *h_new, *c_new, *pred, *logits;
+    float* z;  // [n_seq][640] joint input relu(enc_proj[frame] + pred), kept current for every live sequence
     uint32_t* out_tokens;
     int *out_frames, *out_durs;
     float* out_conf;
     float* trace;   // [n_seq][trace_cap][1030] or null
     int* overflow;  // set if a sequence produced more than max_tokens tokens
+    long long* timing;  // optional [12]: clock cycles block 0 spent per phase / barrier (null = off)
 };
 
 cudaError_t decode_enc_projection(const float* d_enc, const float* w_enc, const float* b_enc, float* d_proj, int rows,

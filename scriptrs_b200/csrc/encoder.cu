@@ -75,9 +75,10 @@ sub_conv0_kernel(const float* __restrict__ feats, const int64_t* __restrict__ t0
     }
 }
 
-// in bf16 [sum Tin x Fin x 256] -> out bf16 [sum Tout x Fin/2 x 256]; one CTA per output time row,
-// 128 threads, two channels each.  w is tap-major [9 x 256].
-__global__ void __launch_bounds__(128)
+// in bf16 [sum Tin x Fin x 256] -> out bf16 [sum Tout x Fin/2 x 256]; one CTA per output time row, 256 threads:
+// a warp covers the 256 channels with 16-byte loads (8 channels per lane), the 8 warps share the frequency
+// positions.  w is tap-major [9 x 256].
+__global__ void __launch_bounds__(256)
 sub_dw_kernel(const bf16* __restrict__ in, const int* __restrict__ tin_off, const int* __restrict__ tout_off,
               int n_clips, int fin, const float* __restrict__ w, const float* __restrict__ b, bf16* __restrict__ out) {
     const int go = blockIdx.x;
@@ -86,16 +87,21 @@ sub_dw_kernel(const bf16* __restrict__ in, const int* __restrict__ tin_off, cons
     const int in_base = tin_off[clip];
     const int Tin = tin_off[clip + 1] - in_base;
     const int fout = fin >> 1;
-    const int c = threadIdx.x * 2;
-    float w0[9], w1[9];
+    const int c = (threadIdx.x & 31) * 8, wgrp = threadIdx.x >> 5;
+    float wt[9][8], bias[8];
 #pragma unroll
     for (int i = 0; i < 9; ++i) {
-        w0[i] = w[i * kSubC + c];
-        w1[i] = w[i * kSubC + c + 1];
+        const float4 w0 = *reinterpret_cast<const float4*>(w + i * kSubC + c);
+        const float4 w1 = *reinterpret_cast<const float4*>(w + i * kSubC + c + 4);
+        wt[i][0] = w0.x; wt[i][1] = w0.y; wt[i][2] = w0.z; wt[i][3] = w0.w;
+        wt[i][4] = w1.x; wt[i][5] = w1.y; wt[i][6] = w1.z; wt[i][7] = w1.w;
     }
-    const float b0 = b[c], b1 = b[c + 1];
-    for (int fo = 0; fo < fout; ++fo) {
-        float a0 = b0, a1 = b1;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) bias[e] = b[c + e];
+    for (int fo = wgrp; fo < fout; fo += 8) {
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = bias[e];
 #pragma unroll
         for (int dt = 0; dt < 3; ++dt) {
             const int r = 2 * to - 1 + dt;
@@ -104,13 +110,24 @@ sub_dw_kernel(const bf16* __restrict__ in, const int* __restrict__ tin_off, cons
             for (int df = 0; df < 3; ++df) {
                 const int f = 2 * fo - 1 + df;
                 if (f < 0 || f >= fin) continue;
-                const __nv_bfloat162 v =
-                    *reinterpret_cast<const __nv_bfloat162*>(in + ((size_t)(in_base + r) * fin + f) * kSubC + c);
-                a0 = fmaf(w0[dt * 3 + df], __low2float(v), a0);
-                a1 = fmaf(w1[dt * 3 + df], __high2float(v), a1);
+                const uint4 raw = *reinterpret_cast<const uint4*>(in + ((size_t)(in_base + r) * fin + f) * kSubC + c);
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 v = __bfloat1622float2(h2[e]);
+                    acc[2 * e] = fmaf(wt[dt * 3 + df][2 * e], v.x, acc[2 * e]);
+                    acc[2 * e + 1] = fmaf(wt[dt * 3 + df][2 * e + 1], v.y, acc[2 * e + 1]);
+                }
             }
         }
-        *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)go * fout + fo) * kSubC + c) = __floats2bfloat162_rn(a0, a1);
+        uint4 pk;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[0], acc[1]), p1 = __floats2bfloat162_rn(acc[2], acc[3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[4], acc[5]), p3 = __floats2bfloat162_rn(acc[6], acc[7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&p0);
+        pk.y = *reinterpret_cast<uint32_t*>(&p1);
+        pk.z = *reinterpret_cast<uint32_t*>(&p2);
+        pk.w = *reinterpret_cast<uint32_t*>(&p3);
+        *reinterpret_cast<uint4*>(out + ((size_t)go * fout + fo) * kSubC + c) = pk;
     }
 }
 
@@ -165,10 +182,17 @@ layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gamma, c
     }
 }
 
+__device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);  // cvt2_e4m3 pairs: byte 0 = a, 1 = b, 2 = c, 3 = d
+}
+
 // LayerNorm with an e4m3 output row and its scale: q = y / scale, scale = max|y| / 448.
 __global__ void __launch_bounds__(256)
 layernorm_fp8_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
-                     uint8_t* __restrict__ out, float* __restrict__ row_scale, int rows) {
+                     uint8_t* __restrict__ out, float* __restrict__ row_scale, int rows, float* __restrict__ next_scale,
+                     float wn, float bmax) {
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
@@ -194,7 +218,7 @@ layernorm_fp8_kernel(const float* __restrict__ x, const float* __restrict__ gamm
     const float rstd = rsqrtf(q * (1.0f / kDModel) + 1e-5f);
     const float4* g4 = reinterpret_cast<const float4*>(gamma);
     const float4* b4 = reinterpret_cast<const float4*>(beta);
-    float amax = 0.0f;
+    float amax = 0.0f, ss = 0.0f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         const float4 g = g4[lane + 32 * k], b = b4[lane + 32 * k];
@@ -203,20 +227,24 @@ layernorm_fp8_kernel(const float* __restrict__ x, const float* __restrict__ gamm
         v[k].z = (v[k].z - mean) * rstd * g.z + b.z;
         v[k].w = (v[k].w - mean) * rstd * g.w + b.w;
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[k].x), fabsf(v[k].y)), fmaxf(fabsf(v[k].z), fabsf(v[k].w))));
+        ss += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    for (int o = 16; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    }
+    // Scale of the NEXT GEMM's e4m3 output row: |silu(w . y + b)| <= ||y|| max_n ||w_n|| + max |b| (Cauchy-Schwarz;
+    // 7 % head-room for the rounding of y and w to e4m3).  Loose by a few binades, which e4m3 absorbs.
+    if (next_scale && lane == 0)
+        next_scale[row] = fmaxf(1.07f * sqrtf(ss) * wn + bmax, 0.28f) * (1.0f / 448.0f);
     const float scale = amax > 0.0f ? amax * (1.0f / 448.0f) : 1.0f;
     const float inv = 1.0f / scale;
     if (lane == 0) row_scale[row] = scale;
     uint32_t* o32 = reinterpret_cast<uint32_t*>(out + (size_t)row * kDModel);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-        const uint32_t b0 = __nv_cvt_float_to_fp8(v[k].x * inv, __NV_SATFINITE, __NV_E4M3);
-        const uint32_t b1 = __nv_cvt_float_to_fp8(v[k].y * inv, __NV_SATFINITE, __NV_E4M3);
-        const uint32_t b2 = __nv_cvt_float_to_fp8(v[k].z * inv, __NV_SATFINITE, __NV_E4M3);
-        const uint32_t b3 = __nv_cvt_float_to_fp8(v[k].w * inv, __NV_SATFINITE, __NV_E4M3);
-        o32[lane + 32 * k] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+        o32[lane + 32 * k] = cvt4_e4m3(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
     }
 }
 
@@ -249,14 +277,11 @@ quantize_rows4096_kernel(const bf16* __restrict__ in, uint8_t* __restrict__ out,
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
         const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
-        uint32_t w[2] = {0, 0};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h2[e]);
-            const uint32_t b0 = __nv_cvt_float_to_fp8(f.x * inv, __NV_SATFINITE, __NV_E4M3);
-            const uint32_t b1 = __nv_cvt_float_to_fp8(f.y * inv, __NV_SATFINITE, __NV_E4M3);
-            w[e >> 1] |= (b0 | (b1 << 8)) << (16 * (e & 1));
-        }
+        const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+        const float2 f2 = __bfloat1622float2(h2[2]), f3 = __bfloat1622float2(h2[3]);
+        uint32_t w[2];
+        w[0] = cvt4_e4m3(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv);
+        w[1] = cvt4_e4m3(f2.x * inv, f2.y * inv, f3.x * inv, f3.y * inv);
         dst[lane + 32 * k] = make_uint2(w[0], w[1]);
     }
 }
@@ -444,10 +469,10 @@ cudaError_t run_gemm(sb_ctx* c, const char* label, const void* a, const bf16* w,
 
 cudaError_t run_gemm_fp8(sb_ctx* c, const char* label, const uint8_t* a, const float* a_scale, const uint8_t* w,
                          const float* w_scale, const float* bias, void* out, int M, int N, int K, int act, int mode,
-                         float alpha) {
+                         float alpha, const float* out_row_scale = nullptr) {
     GemmArgs g{};
     g.a = a; g.w = w; g.bias = bias; g.row_scale = a_scale; g.col_scale = w_scale; g.out = out; g.M = M; g.N = N; g.K = K;
-    g.ldo = N; g.act = act; g.out_mode = mode; g.alpha = alpha; g.fp8 = true;
+    g.ldo = N; g.act = act; g.out_mode = mode; g.alpha = alpha; g.fp8 = true; g.out_row_scale = out_row_scale;
     c->launches += 1;
     c->prof.begin(label, c->stream);
     cudaError_t e = gemm_launch(g, c->sm_count, c->d_error, c->stream);
@@ -534,10 +559,10 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
 
     // sub-sampling
     PROF("sub_conv0", (sub_conv0_kernel<<<R1, 256, 0, st>>>(d_feats, d_t0, d_t1, n, m.sub0_w, m.sub0_b, ws.y0.as<bf16>())));
-    PROF("sub_dw1", (sub_dw_kernel<<<R2, 128, 0, st>>>(ws.y0.as<bf16>(), d_t1, d_t2, n, 64, m.dw1_w, m.dw1_b, ws.y1.as<bf16>())));
+    PROF("sub_dw1", (sub_dw_kernel<<<R2, 256, 0, st>>>(ws.y0.as<bf16>(), d_t1, d_t2, n, 64, m.dw1_w, m.dw1_b, ws.y1.as<bf16>())));
     c->launches += 2;
     ENC_CUDA(run_gemm(c, "gemm_sub_pw", ws.y1.p, m.pw1_w, m.pw1_b, ws.y2.p, R2 * 32, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
-    PROF("sub_dw2", (sub_dw_kernel<<<R3, 128, 0, st>>>(ws.y2.as<bf16>(), d_t2, d_t3, n, 32, m.dw2_w, m.dw2_b, ws.y3.as<bf16>())));
+    PROF("sub_dw2", (sub_dw_kernel<<<R3, 256, 0, st>>>(ws.y2.as<bf16>(), d_t2, d_t3, n, 32, m.dw2_w, m.dw2_b, ws.y3.as<bf16>())));
     c->launches += 1;
     ENC_CUDA(run_gemm(c, "gemm_sub_pw", ws.y3.p, m.pw2_w, m.pw2_b, ws.y4.p, R3 * 16, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
     float* x = ws.x.as<float>();
@@ -555,10 +580,16 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     // feed-forward module: x += 0.5 * W2 silu(W1 LN(x) + b1) + b2
     auto feed_forward = [&](const float* g, const float* b, const bf16* w1, const uint8_t* w1q, const float* w1s,
                             const float* b1, const bf16* w2, const uint8_t* w2q, const float* w2s,
-                            const float* b2) -> cudaError_t {
-        if (fp8 && (c->fp8_mask & 3)) {
+                            const float* b2, float wn, float bmax) -> cudaError_t {
+        if (fp8 && (c->fp8_mask & 3) == 3) {
+            // LayerNorm -> e4m3; up-projection writes the e4m3 hidden row with a scale bounded in advance
+            PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, g, b, a8, rs_a, R3, rs_h, wn, bmax)));
+            ENC_CUDA(run_gemm_fp8(c, "gemm_ff_up_fp8", a8, rs_a, w1q, w1s, b1, h8, R3, kFF, kDModel, kActSilu, kOutFp8, 1.0f, rs_h));
+            ENC_CUDA(run_gemm_fp8(c, "gemm_ff_down_fp8", h8, rs_h, w2q, w2s, b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
+            c->launches += 1;
+        } else if (fp8 && (c->fp8_mask & 3)) {
             if (c->fp8_mask & 1) {
-                PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, g, b, a8, rs_a, R3)));
+                PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, g, b, a8, rs_a, R3, nullptr, 0.0f, 0.0f)));
                 ENC_CUDA(run_gemm_fp8(c, "gemm_ff_up_fp8", a8, rs_a, w1q, w1s, b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
             } else {
                 PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, g, b, a, R3)));
@@ -584,7 +615,7 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     auto norm_project = [&](const char* label, const char* label8, const float* g, const float* b, const bf16* w,
                             const uint8_t* wq, const float* wsc, const float* bias, int N) -> cudaError_t {
         if (fp8 && (c->fp8_mask & (N == 3 * kDModel ? 4 : 8))) {
-            PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, g, b, a8, rs_a, R3)));
+            PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, g, b, a8, rs_a, R3, nullptr, 0.0f, 0.0f)));
             ENC_CUDA(run_gemm_fp8(c, label8, a8, rs_a, wq, wsc, bias, h, R3, N, kDModel, kActNone, kOutBf16, 1.0f));
         } else {
             PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, g, b, a, R3)));
@@ -597,7 +628,7 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
         const LayerWeights& L = m.L[l];
         // x += 0.5 * FF1(LN x)
         ENC_CUDA(feed_forward(L.ln_ff1_g, L.ln_ff1_b, L.ff1_w1, L.ff1_w1_q, L.ff1_w1_s, L.ff1_b1, L.ff1_w2, L.ff1_w2_q,
-                              L.ff1_w2_s, L.ff1_b2));
+                              L.ff1_w2_s, L.ff1_b2, L.ff1_wn, L.ff1_bmax));
         // x += MHA(LN x)
         ENC_CUDA(norm_project("gemm_qkv", "gemm_qkv_fp8", L.ln_att_g, L.ln_att_b, L.qkv_w, L.qkv_w_q, L.qkv_w_s, L.qkv_b,
                               3 * kDModel));
@@ -619,7 +650,7 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
         ENC_CUDA(run_gemm(c, "gemm_conv_pw2", att, L.pw2_w, L.pw2_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
         // x += 0.5 * FF2(LN x)
         ENC_CUDA(feed_forward(L.ln_ff2_g, L.ln_ff2_b, L.ff2_w1, L.ff2_w1_q, L.ff2_w1_s, L.ff2_b1, L.ff2_w2, L.ff2_w2_q,
-                              L.ff2_w2_s, L.ff2_b2));
+                              L.ff2_w2_s, L.ff2_b2, L.ff2_wn, L.ff2_bmax));
         // x = LN_out(x); the last block writes straight into the caller's buffer
         float* dst = (l == m.layers - 1) ? d_out + (size_t)enc_off_all[c0] * kDModel : x;
         PROF("layernorm", (layernorm_kernel<true><<<ln_grid, 256, 0, st>>>(x, L.ln_out_g, L.ln_out_b, dst, R3)));

@@ -21,6 +21,7 @@
 // *error, drains, frees its tensor memory and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -62,10 +63,17 @@ __device__ __forceinline__ float apply_act(float x, int act) {
     return x;
 }
 
+__device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);  // cvt2_e4m3 pairs: byte 0 = a, 1 = b, 2 = c, 3 = d
+}
+
 struct EpiParams {
     const float* bias;
     const float* row_scale;
     const float* col_scale;
+    const float* out_row_scale;
     void* out;
     int M, N, K, ldo, act, out_mode;
     float alpha;
@@ -180,7 +188,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         const uint32_t slab = slab_base + ew * kSlabBytes;
         unsigned char* slab_ptr = base_ptr + S * C::kStageBytes + ew * kSlabBytes;
         const bool out_bf16 = ep.out_mode == kOutBf16;
-        const int slab_cols = out_bf16 ? 64 : 32;  // 128 bytes per row either way
+        const bool out_fp8 = ep.out_mode == kOutFp8;
+        const int slab_cols = out_fp8 ? 128 : (out_bf16 ? 64 : 32);  // 128 bytes per row in every mode
         const int sw = lane & 7;
         uint32_t lt = 0;
         bool ok = true;
@@ -192,6 +201,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             tc_fence_after();
             const int row = m0 + quad * 32 + lane;
             const float rs = (FP8 && ep.row_scale && row < ep.M) ? ep.row_scale[row] : 1.0f;
+            const float out_inv = (out_fp8 && row < ep.M) ? 1.0f / ep.out_row_scale[row] : 1.0f;
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
             const int cbeg = half * (BN / 2), cend = cbeg + BN / 2;
 #pragma unroll 1
@@ -229,7 +239,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 #pragma unroll
                         for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
                     }
-                    if (out_bf16) {
+                    if (out_fp8) {
+                        // 32 columns = 32 bytes = chunks 2*sub, 2*sub + 1 of this row
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            uint32_t wd[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float* xv = x + 16 * q + 4 * e;
+                                wd[e] = cvt4_e4m3(xv[0] * out_inv, xv[1] * out_inv, xv[2] * out_inv, xv[3] * out_inv);
+                            }
+                            const int ch = 2 * sub + q;
+                            *reinterpret_cast<uint4*>(slab_ptr + lane * 128 + ((ch ^ sw) << 4)) =
+                                make_uint4(wd[0], wd[1], wd[2], wd[3]);
+                        }
+                    } else if (out_bf16) {
                         // 32 columns = 64 bytes = chunks 4*sub .. 4*sub + 3 of this row
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
@@ -299,12 +323,13 @@ cudaError_t launch_t(const GemmArgs& g, int sm_count, int* d_error, cudaStream_t
     alignas(64) CUtensorMap ma, mb, mo;
     const int eb = FP8 ? 1 : 2;
     const CUtensorMapDataType in_dt = FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    const bool ob = g.out_mode == kOutBf16;
+    const bool ob = g.out_mode == kOutBf16, o8 = g.out_mode == kOutFp8;
+    const CUtensorMapDataType out_dt = o8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                          : (ob ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
     if (!make_map(&ma, g.a, g.M, g.K, g.K, in_dt, eb, kBM) || !make_map(&mb, g.w, g.N, g.K, g.K, in_dt, eb, BN) ||
-        !make_map(&mo, g.out, g.M, g.N, g.ldo, ob ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
-                  ob ? 2 : 4, 32))
+        !make_map(&mo, g.out, g.M, g.N, g.ldo, out_dt, o8 ? 1 : (ob ? 2 : 4), 32))
         return cudaErrorInvalidValue;
-    EpiParams ep{g.bias, g.row_scale, g.col_scale, g.out, g.M, g.N, g.K, g.ldo, g.act, g.out_mode, g.alpha};
+    EpiParams ep{g.bias, g.row_scale, g.col_scale, g.out_row_scale, g.out, g.M, g.N, g.K, g.ldo, g.act, g.out_mode, g.alpha};
     const int tiles = ((g.M + kBM - 1) / kBM) * (g.N / BN);
     const int grid = tiles < sm_count ? tiles : sm_count;
     gemm_kernel<BN, FP8><<<grid, kGemmThreads, Cfg<BN>::kSmemBytes, stream>>>(ma, mb, mo, ep, d_error);
@@ -348,7 +373,8 @@ cudaError_t gemm_launch(const GemmArgs& g, int sm_count, int* d_error, cudaStrea
         return cudaErrorInvalidValue;
     // BN = 256 when it divides N and still leaves at least one tile per SM; else 128.
     const int m_tiles = (g.M + kBM - 1) / kBM;
-    const bool wide = (g.N % 256 == 0) && (m_tiles * (g.N / 256) >= sm_count);
+    if (g.out_mode == kOutFp8 && (g.N % 256 != 0 || !g.out_row_scale || (g.ldo & 15))) return cudaErrorInvalidValue;
+    const bool wide = (g.N % 256 == 0) && (g.out_mode == kOutFp8 || m_tiles * (g.N / 256) >= sm_count);
     if (g.fp8) return wide ? launch_t<256, true>(g, sm_count, d_error, stream) : launch_t<128, true>(g, sm_count, d_error, stream);
     return wide ? launch_t<256, false>(g, sm_count, d_error, stream) : launch_t<128, false>(g, sm_count, d_error, stream);
 }

@@ -10,6 +10,7 @@ enum GemmOut : int {
     kOutBf16 = 0,      // out[M x N] bf16 = act(acc * scales + bias)
     kOutF32 = 1,       // out[M x N] f32  = act(acc * scales + bias) * alpha
     kOutResidual = 2,  // out[M x N] f32 += alpha * act(acc * scales + bias)
+    kOutFp8 = 3,       // out[M x N] e4m3 = act(acc * scales + bias) / out_row_scale[m]   (N % 256 == 0)
 };
 
 struct GemmArgs {
@@ -18,6 +19,7 @@ struct GemmArgs {
     const float* bias;       // [N] or null
     const float* row_scale;  // fp8 only: per-row activation scale [M], or null
     const float* col_scale;  // fp8 only: per-output-channel weight scale [N], or null
+    const float* out_row_scale;  // kOutFp8: per-row scale of the e4m3 output [M]
     void* out;
     int M, N, K;
     int ldo;                 // leading dimension of out in elements

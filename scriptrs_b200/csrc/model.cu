@@ -189,6 +189,21 @@ int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensor
             L.ff2_w1 = ld.b16(p + "feed_forward2.linear1.weight", ff * d); L.ff2_b1 = ld.f32(p + "feed_forward2.linear1.bias", ff);
             L.ff2_w2 = ld.b16(p + "feed_forward2.linear2.weight", d * ff); L.ff2_b2 = ld.f32(p + "feed_forward2.linear2.bias", d);
             if (desc->fp8_weights) {
+                auto bound = [&](const std::string& wname, const std::string& bname, float* wn, float* bmax) {
+                    const float* w = ld.get(wname, ff * d);
+                    const float* b = ld.get(bname, ff);
+                    *wn = 0.0f;
+                    *bmax = 0.0f;
+                    if (!w || !b) return;
+                    for (int64_t r = 0; r < ff; ++r) {
+                        double ss = 0.0;
+                        for (int64_t k = 0; k < d; ++k) ss += (double)w[r * d + k] * w[r * d + k];
+                        *wn = std::fmax(*wn, (float)std::sqrt(ss));
+                        *bmax = std::fmax(*bmax, std::fabs(b[r]));
+                    }
+                };
+                bound(p + "feed_forward1.linear1.weight", p + "feed_forward1.linear1.bias", &L.ff1_wn, &L.ff1_bmax);
+                bound(p + "feed_forward2.linear1.weight", p + "feed_forward2.linear1.bias", &L.ff2_wn, &L.ff2_bmax);
                 ld.up_fp8(ld.get(p + "feed_forward1.linear1.weight", ff * d), ff, d, &L.ff1_w1_q, &L.ff1_w1_s);
                 ld.up_fp8(ld.get(p + "feed_forward1.linear2.weight", d * ff), d, ff, &L.ff1_w2_q, &L.ff1_w2_s);
                 ld.up_fp8(ld.get(p + "feed_forward2.linear1.weight", ff * d), ff, d, &L.ff2_w1_q, &L.ff2_w1_s);

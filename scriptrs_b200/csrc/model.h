@@ -50,6 +50,8 @@ struct LayerWeights {
     // e4m3 copies with one scale per output channel (w = q * scale[n]) for the FP8 path
     uint8_t *ff1_w1_q, *ff1_w2_q, *ff2_w1_q, *ff2_w2_q, *qkv_w_q, *pw1_w_q;
     float *ff1_w1_s, *ff1_w2_s, *ff2_w1_s, *ff2_w2_s, *qkv_w_s, *pw1_w_s;
+    // bound on |W1 y + b1| per unit of ||y||_2: largest row norm of W1, and max |b1| (scale of the e4m3 hidden row)
+    float ff1_wn, ff1_bmax, ff2_wn, ff2_bmax;
 };
 
 struct Model {

@@ -2,6 +2,8 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -13,12 +15,12 @@
 namespace sb {
 
 struct DecodeWorkspace {
-    Buffer ints, floats, enc_proj, out_tok, out_frm, out_dur, out_conf, trace;
+    Buffer ints, floats, enc_proj, out_tok, out_frm, out_dur, out_conf, trace, timing;
     Buffer h_tok, h_frm, h_dur, h_conf;  // pinned host staging
     DecodeWorkspace() { h_tok.pinned_host = h_frm.pinned_host = h_dur.pinned_host = h_conf.pinned_host = true; }
     void release() {
         ints.release(); floats.release(); enc_proj.release(); out_tok.release(); out_frm.release(); out_dur.release();
-        out_conf.release(); trace.release(); h_tok.release(); h_frm.release(); h_dur.release(); h_conf.release();
+        out_conf.release(); trace.release(); timing.release(); h_tok.release(); h_frm.release(); h_dur.release(); h_conf.release();
     }
 };
 
@@ -70,7 +72,7 @@ int32_t tdt_decode(sb_ctx* c, const float* d_enc, const int64_t* enc_offsets, in
         SB_CUDA(cudaMemcpyAsync(di, hi.data(), n_int * sizeof(int), cudaMemcpyHostToDevice, st));
         // float state: h, c, h_new, c_new [2][n][640], pred [n][640], logits [n][1030]
         const size_t BH = (size_t)n * kPredHidden;
-        const size_t n_f = 8 * BH + (size_t)n * kJointDim + (size_t)n * kJointOut;
+        const size_t n_f = 8 * BH + 2 * (size_t)n * kJointDim + (size_t)n * kJointOut;
         SB_CUDA(ws.floats.ensure(n_f * sizeof(float)));
         float* df = ws.floats.as<float>();
         SB_CUDA(cudaMemsetAsync(df, 0, 4 * BH * sizeof(float), st));  // h = c = 0 (model.rs:114-115)
@@ -106,12 +108,22 @@ int32_t tdt_decode(sb_ctx* c, const float* d_enc, const int64_t* enc_offsets, in
         s.h_new = df + 4 * BH;
         s.c_new = df + 6 * BH;
         s.pred = df + 8 * BH;
-        s.logits = s.pred + (size_t)n * kJointDim;
+        s.z = s.pred + (size_t)n * kJointDim;
+        s.logits = s.z + (size_t)n * kJointDim;
         s.out_tokens = ws.out_tok.as<uint32_t>();
         s.out_frames = ws.out_frm.as<int>();
         s.out_durs = ws.out_dur.as<int>();
         s.out_conf = ws.out_conf.as<float>();
         s.trace = logits_trace ? ws.trace.as<float>() : nullptr;
+        // SB_DECODE_TIMING=1: block 0's cycle counts per phase / barrier, printed after the kernel
+        static const bool want_timing = std::getenv("SB_DECODE_TIMING") != nullptr;
+        long long* d_timing = nullptr;
+        if (want_timing) {
+            SB_CUDA(ws.timing.ensure(12 * sizeof(long long)));
+            d_timing = ws.timing.as<long long>();
+            SB_CUDA(cudaMemsetAsync(d_timing, 0, 12 * sizeof(long long), st));
+        }
+        s.timing = d_timing;
         const int max_steps = (kMaxSymbols + 1) * max_len + 2;
         if (max_len > 0) {
             c->prof.begin("tdt_decode", st);
@@ -123,6 +135,14 @@ int32_t tdt_decode(sb_ctx* c, const float* d_enc, const int64_t* enc_offsets, in
         std::vector<int> cnt((size_t)2 * n + 1);
         SB_CUDA(cudaMemcpyAsync(cnt.data(), s.n_tokens, sizeof(int) * (2 * n + 1), cudaMemcpyDeviceToHost, st));
         SB_CUDA(cudaStreamSynchronize(st));
+        if (d_timing) {
+            long long t[12];
+            SB_CUDA(cudaMemcpy(t, d_timing, sizeof(t), cudaMemcpyDeviceToHost));
+            static const char* names[11] = {"lists", "lstm0", "sync", "lstm1", "sync", "pred", "sync", "out", "sync", "decide", "sync"};
+            std::fprintf(stderr, "[decode timing] n_seq=%d steps=%lld kcycles:", n, t[11]);
+            for (int i = 0; i < 11; ++i) std::fprintf(stderr, " %s=%lld", names[i], t[i] / 1000);
+            std::fprintf(stderr, "\n");
+        }
         if (cnt[2 * n]) return fail(SB_BUFFER_TOO_SMALL, "a clip emitted more tokens than max_tokens");
         int max_n = 0;
         for (int i = 0; i < n; ++i) max_n = std::max(max_n, cnt[i]);
