@@ -11,12 +11,14 @@
 //   MMA 2    S_bd = Q Pseg^T         (128 x 320, columns 192..511): column q of row i is relative
 //            position i - j for j = q - ((T'-1) - i - first_row); the "relative shift" is therefore a
 //            per-row offset, applied when each thread copies its own row out of tensor memory
-//   softmax  two threads per query row (each half of the columns): scores = (S_ac + u.k_j + S_bd + v.p) / sqrt(128) in a private
-//            fp32 row of shared memory, max, exp, sum; probabilities written as the bf16 A operand
+//   softmax  four threads per query row (each a quarter of the columns): the shifted S_bd row goes through a private
+//            fp32 row of shared memory, the scores S_ac + S_bd stay in registers; max, exp2, sum; probabilities
+//            written as the bf16 A operand
 //   MMA 3    O = P V                  (128 x 128, V supplied transposed so that it is K-major)
 //   store    O / sum -> bf16, staged through shared memory, coalesced rows
 // The u and v biases enter as per-key (u.k_j, computed here) and per-position (v.p, computed at model
-// load) scalars, so Q goes to the tensor cores untouched.  All mbarrier waits are bounded, and every
+// load) scalars written into the accumulators before the products are issued, so Q goes to the tensor
+// cores untouched.  All mbarrier waits are bounded, and every
 // wait is followed by a block-wide vote so that all threads leave the loop together.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -33,18 +35,23 @@ namespace {
 using namespace ptx;
 
 constexpr int kAT = 128;             // query rows per block
-constexpr int kATh = 256;            // threads per CTA: two per query row, each owning half of the columns
+constexpr int kATh = 512;            // threads per CTA: four per query row, each owning a quarter of the columns
 constexpr int kNK = 192;             // key columns of S_ac (T' padded)
 constexpr int kNP = 320;             // table rows per query block (256 + 64)
-constexpr int kSStride = 189;        // floats per private score row (odd: conflict-free reads)
-constexpr int kR1 = 97280;           // table rows (2 x 40 KB) / score rows (128 x 189 x 4) / output staging
-constexpr int kR2 = 49152;           // K (2 x 24 KB) / probabilities (3 x 16 KB)
+constexpr int kSStride = 189;        // floats per shifted S_bd row (odd: conflict-free reads)
+constexpr int kR1 = 97280;           // table rows (2 x 40 KB) / shifted S_bd rows (128 x 189 x 4) / probabilities + output staging
+constexpr int kR2 = 49152;           // K (2 x 24 KB), resident for both query blocks
 constexpr int kR3 = 32768;           // Q (2 x 16 KB)
 constexpr int kR4 = 49152;           // V^T (3 x 16 KB)
-constexpr int kSmall = 192 * 4 + 320 * 4 + 128 * 4 + 64;
-constexpr int kAttSmem = kR1 + kR2 + kR3 + kR4 + kSmall + 1024;
+constexpr int kPOff = 0;             // probabilities inside region 1 (3 x 16 KB)
+constexpr int kOOff = 49152;         // output staging inside region 1
+constexpr int kTailOff = 128 * kSStride * 4;  // 512 spare bytes of region 1 that no other use touches
+constexpr int kSmall = (kNK + kNP) * 4 + 3 * kAT * 4 + 32;
+constexpr int kAttSmem = kR1 + kR2 + kR3 + kR4 + kSmall;
 constexpr int kOStride = 272;        // bytes per staged output row (256 + 16)
 constexpr uint32_t kBoxBytes = 64 * 128;  // one TMA box: 64 rows x 128 bytes
+static_assert(kAttSmem <= 232448, "shared memory budget");
+static_assert(kOOff + kAT * kOStride <= kTailOff && 2 * 40960 <= kTailOff && kTailOff + kAT * 4 <= kR1, "region 1 layout");
 
 __device__ __forceinline__ uint32_t idesc_bf16(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -55,17 +62,23 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
                            const __grid_constant__ CUtensorMap map_vt, const int* __restrict__ t3_off,
                            const float* __restrict__ bias_u, const float* __restrict__ pos_vp,
                            bf16* __restrict__ out, int* __restrict__ error) {
-    extern __shared__ unsigned char att_dyn[];
-    const uint32_t base = (smem_u32(att_dyn) + 1023u) & ~1023u;
-    unsigned char* bp = att_dyn + (base - smem_u32(att_dyn));
+    extern __shared__ __align__(1024) unsigned char att_dyn[];
+    const uint32_t base = smem_u32(att_dyn);
+    if (base & 1023u) {  // the swizzled operand tiles need 1024-byte alignment
+        if (threadIdx.x == 0) atomicExch(error, 2);
+        return;
+    }
+    unsigned char* bp = att_dyn;
     const uint32_t r1 = base, r2 = r1 + kR1, r3 = r2 + kR2, r4 = r3 + kR3;
     unsigned char* p1 = bp;
     unsigned char* p2 = bp + kR1;
-    float* uk = reinterpret_cast<float*>(bp + kR1 + kR2 + kR3 + kR4);
-    float* vp = uk + 192;
-    float* us = vp + 320;
-    const uint32_t bar0 = r4 + kR4 + 192 * 4 + 320 * 4 + 128 * 4;  // bar_in, bar_v, bar_mma, then tmem slot, abort flag
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(us + 128) + 6;
+    float* pre = reinterpret_cast<float*>(bp + kR1 + kR2 + kR3 + kR4);  // [uk (192) | vp (320)]: accumulator preload
+    float* uk = pre;
+    float* vp = pre + kNK;
+    float* part = vp + kNP;  // [3][128] row partials of quarters 0..2 (maxima, later sums); also u while u.k is formed
+    float* part3 = reinterpret_cast<float*>(p1 + kTailOff);  // [128] partials of quarter 3
+    const uint32_t bar0 = r4 + kR4 + (kNK + kNP + 3 * kAT) * 4;  // bar_in, bar_v, bar_mma, then tmem slot, abort flag
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part + 3 * kAT) + 6;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t bar_in = bar0, bar_v = bar0 + 8, bar_mma = bar0 + 16;
 
@@ -74,6 +87,10 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
     const int t = t3_off[clip + 1] - row0;
     if (t <= 0) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int lg = warp & 3;   // tensor-memory lane group of this warp: rows 32 lg .. 32 lg + 31 of the block
+    const int qd = warp >> 2;  // column quarter
+    const int rl = 32 * lg + lane;
+    auto part_of = [&](int q) -> float* { return q < 3 ? part + q * kAT : part3; };
 
     if (tid == 0) {
         mbar_init(bar_in, 1);
@@ -86,11 +103,12 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
     }
-    if (tid < kHeadDim) us[tid] = bias_u[head * kHeadDim + tid];
+    if (tid < kHeadDim) part[tid] = bias_u[head * kHeadDim + tid];
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    const uint32_t tq = tmem + ((uint32_t)(lg * 32) << 16);
 
     // V^T of this (clip, head): [128 d x 192 j], three K-blocks of 64 j
     if (tid == 0) {
@@ -101,7 +119,7 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
                 tma_load_2d(r4 + kb * 16384 + h * kBoxBytes, &map_vt, bar_v, kb * 64, vrow + h * 64);
     }
 
-    const float scale = 0.08838834764831845f;  // 1 / sqrt(128)
+    const float sc2 = 0.08838834764831845f * 1.4426950408889634f;  // log2(e) / sqrt(128)
     const int p_first = (kMaxEncFrames - 1) - (t - 1);  // table row of relative position t - 1
     const int n_blocks = (t + kAT - 1) / kAT;
     uint32_t mma_phase = 0;
@@ -111,153 +129,191 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
         const int i0 = qb * kAT;
         const int plo = max(0, (t - 1) - (i0 + kAT - 1));  // first local table row this block can reach
         if (tid == 0) {
-            mbar_expect_tx(bar_in, 20 * kBoxBytes);
+            mbar_expect_tx(bar_in, (qb == 0 ? 20 : 14) * kBoxBytes);
             for (int kb = 0; kb < 2; ++kb) {
                 const int col = head * kHeadDim + kb * 64;
                 for (int h = 0; h < 2; ++h)   // Q rows i0 .. i0 + 127
                     tma_load_2d(r3 + kb * 16384 + h * kBoxBytes, &map_qkv, bar_in, col, row0 + i0 + h * 64);
-                for (int h = 0; h < 3; ++h)   // K rows 0 .. 191
-                    tma_load_2d(r2 + kb * 24576 + h * kBoxBytes, &map_qkv, bar_in, kDModel + col, row0 + h * 64);
+                if (qb == 0)
+                    for (int h = 0; h < 3; ++h)   // K rows 0 .. 191 (kept for the second block)
+                        tma_load_2d(r2 + kb * 24576 + h * kBoxBytes, &map_qkv, bar_in, kDModel + col, row0 + h * 64);
                 for (int h = 0; h < 5; ++h)   // table rows plo .. plo + 319
                     tma_load_2d(r1 + kb * 40960 + h * kBoxBytes, &map_pos, bar_in, col, p_first + plo + h * 64);
             }
         }
         // v . p for the table rows of this block
-        for (int q = tid; q < kNP; q += kATh) {
-            const int p = p_first + plo + q;
-            vp[q] = p < kPosRows ? pos_vp[p * kHeads + head] : 0.0f;
+        if (tid < kNP) {
+            const int p = p_first + plo + tid;
+            vp[tid] = p < kPosRows ? pos_vp[p * kHeads + head] : 0.0f;
         }
         if (!__syncthreads_and(mbar_wait(bar_in, qb & 1, abort_flag))) { ok = false; break; }
-        // u . k_j from the swizzled K tile
-        for (int j = tid; j < kNK; j += kATh) {
-            float acc = 0.0f;
-            if (j < t) {
+        if (qb == 0) {
+            // u . k_j from the swizzled K tile (u sits in part[0..127] until the first partials are written)
+            if (tid < kNK) {
+                const int j = tid;
+                float acc = 0.0f;
+                if (j < t) {
 #pragma unroll
-                for (int ch = 0; ch < 16; ++ch) {
-                    const int kb = ch >> 3, c8 = ch & 7;
-                    const uint4 raw = *reinterpret_cast<const uint4*>(p2 + kb * 24576 + j * 128 + ((c8 ^ (j & 7)) << 4));
-                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                    for (int ch = 0; ch < 16; ++ch) {
+                        const int kb = ch >> 3, c8 = ch & 7;
+                        const uint4 raw = *reinterpret_cast<const uint4*>(p2 + kb * 24576 + j * 128 + ((c8 ^ (j & 7)) << 4));
+                        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = __bfloat1622float2(h2[e]);
-                        acc = fmaf(us[ch * 8 + 2 * e], f.x, acc);
-                        acc = fmaf(us[ch * 8 + 2 * e + 1], f.y, acc);
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __bfloat1622float2(h2[e]);
+                            acc = fmaf(part[ch * 8 + 2 * e], f.x, acc);
+                            acc = fmaf(part[ch * 8 + 2 * e + 1], f.y, acc);
+                        }
                     }
                 }
+                uk[j] = acc;
             }
-            uk[j] = acc;
+            __syncthreads();
         }
+        // the accumulators start from the per-key and per-position bias terms: columns [0, 192) u . k_j,
+        // columns [192, 512) v . p_q, the same in every row
+#pragma unroll 1
+        for (int c = qd; c < (kNK + kNP) / 16; c += 4) {
+            uint32_t v[16];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const uint4 x = *reinterpret_cast<const uint4*>(pre + 16 * c + 4 * g);
+                v[4 * g] = x.x; v[4 * g + 1] = x.y; v[4 * g + 2] = x.z; v[4 * g + 3] = x.w;
+            }
+            tmem_st16(tq + 16 * c, v);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncthreads();
         if (tid == 0) {
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const int kb = k >> 2, ko = (k & 3) * 2;
                 const uint64_t a = make_smem_desc(r3 + kb * 16384) + ko;
-                tc_mma<false>(tmem, a, make_smem_desc(r2 + kb * 24576) + ko, idesc_bf16(kNK), k ? 1u : 0u);
+                tc_mma<false>(tmem, a, make_smem_desc(r2 + kb * 24576) + ko, idesc_bf16(kNK), 1u);
             }
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const int kb = k >> 2, ko = (k & 3) * 2;
                 const uint64_t a = make_smem_desc(r3 + kb * 16384) + ko;
-                tc_mma<false>(tmem + kNK, a, make_smem_desc(r1 + kb * 40960) + ko, idesc_bf16(256), k ? 1u : 0u);
-                tc_mma<false>(tmem + kNK + 256, a, make_smem_desc(r1 + kb * 40960 + 256 * 128) + ko, idesc_bf16(64),
-                              k ? 1u : 0u);
+                tc_mma<false>(tmem + kNK, a, make_smem_desc(r1 + kb * 40960) + ko, idesc_bf16(256), 1u);
+                tc_mma<false>(tmem + kNK + 256, a, make_smem_desc(r1 + kb * 40960 + 256 * 128) + ko, idesc_bf16(64), 1u);
             }
             tc_commit(bar_mma);
         }
-        // (the vote also makes uk and vp visible to all threads)
         if (!__syncthreads_and(mbar_wait(bar_mma, mma_phase, abort_flag))) { ok = false; break; }
         mma_phase ^= 1;
         tc_fence_after();
 
-        const int rl = tid & (kAT - 1), half = tid >> 7;  // row of the block, column half
         const int i = i0 + rl;
-        const bool row_ok = i < t;
+        const bool warp_live = i0 + 32 * lg < t;  // some row of this warp exists
         float* srow = reinterpret_cast<float*>(p1) + rl * kSStride;
-        const uint32_t tq = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        float* sump = uk;            // [2][128] partial sums   (uk and the head of vp are dead by then)
-        float* mxp = uk + 2 * kAT;   // [2][128] partial maxima (inside vp, dead after the shift pass)
-        // S_bd: relative shift while copying this thread's row out of tensor memory (chunks alternate
-        // between the two threads of a row)
-        const int shift = (t - 1) - i - plo;  // j = q - shift
-#pragma unroll 1
-        for (int c = half; c < kNP / 32; c += 2) {
-            uint32_t v[32];
-            tmem_ld32(tq + kNK + 32 * c, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) {
-                const int q = 32 * c + jj;
-                const int j = q - shift;
-                if (row_ok && j >= 0 && j < t) srow[j] = __uint_as_float(v[jj]) + vp[q];
-            }
-        }
-        __syncthreads();  // both threads of a row have written their share of the shifted row
-        // scores and row maximum
+        float s[48];
         float mx = -INFINITY;
+        if (warp_live) {
+            // S_bd: the relative shift is a per-row offset, applied while each thread copies its quarter of its
+            // row out of tensor memory: column q of S_bd is key j = q - shift
+            const int shift = (t - 1) - i - plo;
+            const int shift_hi = __shfl_sync(0xffffffffu, shift, 0), shift_lo = shift_hi - 31;
+            float* srow_sh = srow - shift;
 #pragma unroll 1
-        for (int c = half; c < kNK / 32; c += 2) {
-            uint32_t v[32];
-            tmem_ld32(tq + 32 * c, v);
-            tmem_wait_ld();
+            for (int c = 0; c < 5; ++c) {
+                const int q0 = 80 * qd + 16 * c;
+                if (q0 + 15 < shift_lo || q0 >= shift_hi + t) continue;  // no lane has a key in this chunk
+                uint32_t v[16];
+                tmem_ld16(tq + kNK + q0, v);
+                tmem_wait_ld();
+                if (q0 >= shift_hi && q0 + 15 < shift_lo + t) {
 #pragma unroll
-            for (int jj = 0; jj < 32; ++jj) {
-                const int j = 32 * c + jj;
-                if (row_ok && j < t) {
-                    const float s = (__uint_as_float(v[jj]) + uk[j] + srow[j]) * scale;
-                    srow[j] = s;
-                    mx = fmaxf(mx, s);
+                    for (int jj = 0; jj < 16; ++jj) srow_sh[q0 + jj] = __uint_as_float(v[jj]);
+                } else {
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj)
+                        if ((unsigned)(q0 + jj - shift) < (unsigned)t) srow_sh[q0 + jj] = __uint_as_float(v[jj]);
                 }
             }
         }
-        mxp[half * kAT + rl] = mx;
-        __syncthreads();
-        mx = fmaxf(mxp[rl], mxp[kAT + rl]);
-        // probabilities -> bf16 A operand (K-major, 128-byte swizzle, three blocks of 64 keys)
-        float sum = 0.0f;
-#pragma unroll 1
-        for (int j8 = 8 * half; j8 < kNK; j8 += 16) {
-            float e[8];
+        __syncthreads();  // the four threads of a row have written their shares of the shifted row
+        if (warp_live) {
+            // scores (kept in registers, unscaled) and the row maximum over this thread's 48 keys
 #pragma unroll
-            for (int u8 = 0; u8 < 8; ++u8) {
-                const int j = j8 + u8;
-                e[u8] = (row_ok && j < t) ? __expf(srow[j] - mx) : 0.0f;
-                sum += e[u8];
+            for (int m = 0; m < 3; ++m) {
+                const int j0 = 48 * qd + 16 * m;
+                if (j0 + 15 < t) {
+                    uint32_t v[16];
+                    tmem_ld16(tq + j0, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) {
+                        s[16 * m + jj] = __uint_as_float(v[jj]) + srow[j0 + jj];
+                        mx = fmaxf(mx, s[16 * m + jj]);
+                    }
+                } else if (j0 < t) {
+                    uint32_t v[16];
+                    tmem_ld16(tq + j0, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) {
+                        s[16 * m + jj] = j0 + jj < t ? __uint_as_float(v[jj]) + srow[j0 + jj] : -INFINITY;
+                        mx = fmaxf(mx, s[16 * m + jj]);
+                    }
+                } else {
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) s[16 * m + jj] = -INFINITY;
+                }
             }
-            uint4 pk;
-            __nv_bfloat162 q0 = __floats2bfloat162_rn(e[0], e[1]), q1 = __floats2bfloat162_rn(e[2], e[3]);
-            __nv_bfloat162 q2 = __floats2bfloat162_rn(e[4], e[5]), q3 = __floats2bfloat162_rn(e[6], e[7]);
-            pk.x = *reinterpret_cast<uint32_t*>(&q0);
-            pk.y = *reinterpret_cast<uint32_t*>(&q1);
-            pk.z = *reinterpret_cast<uint32_t*>(&q2);
-            pk.w = *reinterpret_cast<uint32_t*>(&q3);
-            const int kb = j8 >> 6, ch = (j8 & 63) >> 3;
-            *reinterpret_cast<uint4*>(p2 + kb * 16384 + rl * 128 + ((ch ^ (rl & 7)) << 4)) = pk;
+            part_of(qd)[rl] = mx;
         }
-        sump[half * kAT + rl] = sum;
+        __syncthreads();
+        float sum = 0.0f;
+        if (warp_live) {
+            mx = fmaxf(fmaxf(part[rl], part[kAT + rl]), fmaxf(part[2 * kAT + rl], part3[rl]));
+            const float mc = mx * sc2;
+            // probabilities -> bf16 A operand (K-major, 128-byte swizzle, three blocks of 64 keys)
+#pragma unroll
+            for (int m8 = 0; m8 < 6; ++m8) {
+                float e[8];
+#pragma unroll
+                for (int u8 = 0; u8 < 8; ++u8) {
+                    e[u8] = ex2_approx(fmaf(s[8 * m8 + u8], sc2, -mc));
+                    sum += e[u8];
+                }
+                uint4 pk;
+                __nv_bfloat162 q0 = __floats2bfloat162_rn(e[0], e[1]), q1 = __floats2bfloat162_rn(e[2], e[3]);
+                __nv_bfloat162 q2 = __floats2bfloat162_rn(e[4], e[5]), q3 = __floats2bfloat162_rn(e[6], e[7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&q0);
+                pk.y = *reinterpret_cast<uint32_t*>(&q1);
+                pk.z = *reinterpret_cast<uint32_t*>(&q2);
+                pk.w = *reinterpret_cast<uint32_t*>(&q3);
+                const int j8 = 48 * qd + 8 * m8;
+                const int kb = j8 >> 6, ch = (j8 & 63) >> 3;
+                *reinterpret_cast<uint4*>(p1 + kPOff + kb * 16384 + rl * 128 + ((ch ^ (rl & 7)) << 4)) = pk;
+            }
+        }
         fence_proxy_async();
         tc_fence_before();
-        __syncthreads();
+        __syncthreads();  // probabilities complete; every thread has read the row maxima
         if (qb == 0 && !__syncthreads_and(mbar_wait(bar_v, 0, abort_flag))) { ok = false; break; }
         if (tid == 0) {
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < kNK / 16; ++k) {
                 const int kb = k >> 2, ko = (k & 3) * 2;
-                tc_mma<false>(tmem, make_smem_desc(r2 + kb * 16384) + ko, make_smem_desc(r4 + kb * 16384) + ko,
+                tc_mma<false>(tmem, make_smem_desc(r1 + kPOff + kb * 16384) + ko, make_smem_desc(r4 + kb * 16384) + ko,
                               idesc_bf16(kHeadDim), k ? 1u : 0u);
             }
             tc_commit(bar_mma);
         }
+        if (warp_live) part_of(qd)[rl] = sum;  // the partial maxima are dead: the slots now carry the partial sums
         if (!__syncthreads_and(mbar_wait(bar_mma, mma_phase, abort_flag))) { ok = false; break; }
         mma_phase ^= 1;
         tc_fence_after();
         // O / sum -> bf16 -> staging rows -> coalesced global rows
-        const float inv = row_ok ? 1.0f / (sump[rl] + sump[kAT + rl]) : 0.0f;
-#pragma unroll 1
-        for (int c = 2 * half; c < 2 * half + 2; ++c) {
+        if (warp_live) {
+            const float inv = i < t ? 1.0f / ((part[rl] + part[kAT + rl]) + (part[2 * kAT + rl] + part3[rl])) : 0.0f;
             uint32_t v[32];
-            tmem_ld32(tq + 32 * c, v);
+            tmem_ld32(tq + 32 * qd, v);
             tmem_wait_ld();
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -270,14 +326,14 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
                 pk.y = *reinterpret_cast<uint32_t*>(&o1);
                 pk.z = *reinterpret_cast<uint32_t*>(&o2);
                 pk.w = *reinterpret_cast<uint32_t*>(&o3);
-                *reinterpret_cast<uint4*>(p1 + rl * kOStride + c * 64 + q * 16) = pk;
+                *reinterpret_cast<uint4*>(p1 + kOOff + rl * kOStride + qd * 64 + q * 16) = pk;
             }
         }
         tc_fence_before();
         __syncthreads();
         const int valid = min(kAT, t - i0);
         for (int r = warp; r < valid; r += kATh / 32) {
-            const uint2 val = *reinterpret_cast<const uint2*>(p1 + r * kOStride + lane * 8);
+            const uint2 val = *reinterpret_cast<const uint2*>(p1 + kOOff + r * kOStride + lane * 8);
             *reinterpret_cast<uint2*>(out + (size_t)(row0 + i0 + r) * kDModel + head * kHeadDim + lane * 4) = val;
         }
         fence_proxy_async();  // generic accesses to the operand regions are ordered before the next block's TMA writes

@@ -40,38 +40,95 @@ __device__ __forceinline__ int find_clip(const int* __restrict__ off, int n, int
 }
 
 // ---------------------------------------------------------------- sub-sampling
-// feats f32 [sum T x 128] -> y0 bf16 [sum T1 x 64 x 256], one CTA per output time row.
+// First two stages in one kernel: 3x3 stride-2 convolution of the mel image (1 -> 256 channels, ReLU) followed by
+// the 3x3 stride-2 depthwise convolution, without the [T/2 x 64 x 256] intermediate ever reaching memory.
+//   feats f32 [sum T x 128]  ->  out bf16 [sum T2 x 32 x 256]
+// grid (ceil(max T2 / TO), clips), 256 threads = 256 channels.  A CTA produces TO output time rows: it stages the
+// 4 TO + 3 mel rows they depend on in shared memory, and every thread walks the 32 output frequencies keeping a
+// sliding window: per step it reads four new mel columns of each staged row (one 16-byte broadcast read), forms
+// the two new columns of the 2 TO + 1 first-stage rows, and combines them with the column carried over from the
+// previous step.  First-stage values outside [0, T1) x [0, 64) are the second stage's zero padding.
+template <int TO>
 __global__ void __launch_bounds__(256)
-sub_conv0_kernel(const float* __restrict__ feats, const int64_t* __restrict__ t0_off, const int* __restrict__ t1_off,
-                 int n_clips, const float* __restrict__ w, const float* __restrict__ b, bf16* __restrict__ out) {
-    __shared__ float in[3][kMels + 2];
-    const int g1 = blockIdx.x;
-    const int clip = find_clip(t1_off, n_clips, g1);
-    const int t1 = g1 - t1_off[clip];
+sub_conv0_dw1_kernel(const float* __restrict__ feats, const int64_t* __restrict__ t0_off,
+                     const int* __restrict__ t1_off, const int* __restrict__ t2_off, const float* __restrict__ w0,
+                     const float* __restrict__ b0, const float* __restrict__ w1, const float* __restrict__ b1,
+                     bf16* __restrict__ out) {
+    constexpr int NY = 2 * TO + 1, NX = 4 * TO + 3, XS = kMels + 8;  // mel column f sits at index f + 4
+    __shared__ __align__(16) float xs[NX][XS];
+    const int clip = blockIdx.y, to0 = blockIdx.x * TO;
+    const int out_base = t2_off[clip];
+    const int T2 = t2_off[clip + 1] - out_base;
+    if (to0 >= T2) return;
     const int64_t base = t0_off[clip];
     const int T = (int)(t0_off[clip + 1] - base);
-    for (int i = threadIdx.x; i < 3 * (kMels + 2); i += 256) {
-        const int dt = i / (kMels + 2), f = i % (kMels + 2) - 1;
-        const int r = 2 * t1 - 1 + dt;
+    const int T1 = t1_off[clip + 1] - t1_off[clip];
+    for (int i = threadIdx.x; i < NX * XS; i += 256) {
+        const int row = i / XS, col = i % XS - 4;
+        const int r = 4 * to0 - 3 + row;
         float v = 0.0f;
-        if (r >= 0 && r < T && f >= 0 && f < kMels) v = feats[(base + r) * kMels + f];
-        in[dt][f + 1] = v;
+        if (r >= 0 && r < T && col >= 0 && col < kMels) v = feats[(base + r) * kMels + col];
+        xs[row][i % XS] = v;
     }
     __syncthreads();
     const int c = threadIdx.x;
-    float wr[9];
+    float wa[9], wb[9];
 #pragma unroll
-    for (int i = 0; i < 9; ++i) wr[i] = w[c * 9 + i];
-    const float bias = b[c];
-    bf16* o = out + (size_t)g1 * 64 * kSubC + c;
-#pragma unroll 4
-    for (int f1 = 0; f1 < 64; ++f1) {
-        float acc = bias;
+    for (int i = 0; i < 9; ++i) {
+        wa[i] = w0[c * 9 + i];
+        wb[i] = w1[i * kSubC + c];
+    }
+    const float ba = b0[c], bb = b1[c];
+    float ymask[NY], prev[NY], carry[NX];
 #pragma unroll
-        for (int dt = 0; dt < 3; ++dt)
+    for (int k = 0; k < NY; ++k) {
+        const int r = 2 * to0 - 1 + k;
+        ymask[k] = (r >= 0 && r < T1) ? 1.0f : 0.0f;
+        prev[k] = 0.0f;  // first-stage column -1
+    }
 #pragma unroll
-            for (int df = 0; df < 3; ++df) acc = fmaf(wr[dt * 3 + df], in[dt][2 * f1 + df], acc);
-        o[(size_t)f1 * kSubC] = __float2bfloat16(fmaxf(acc, 0.0f));
+    for (int x = 0; x < NX; ++x) carry[x] = 0.0f;  // mel column -1
+    bf16* o = out + (size_t)(out_base + to0) * 32 * kSubC + c;
+#pragma unroll 1
+    for (int fo = 0; fo < 32; ++fo) {
+        float ya[NY], yb[NY];  // first-stage columns 2 fo and 2 fo + 1
+#pragma unroll
+        for (int k = 0; k < NY; ++k) ya[k] = yb[k] = ba;
+#pragma unroll
+        for (int x = 0; x < NX; ++x) {
+            const float4 nw = *reinterpret_cast<const float4*>(&xs[x][4 * fo + 4]);  // mel columns 4 fo .. 4 fo + 3
+            const float x0 = carry[x];
+            carry[x] = nw.w;
+#pragma unroll
+            for (int et = 0; et < 3; ++et) {
+                if ((x - et) % 2 != 0 || x - et < 0 || (x - et) / 2 >= NY) continue;
+                const int k = (x - et) / 2;
+                ya[k] = fmaf(wa[et * 3 + 0], x0, ya[k]);
+                ya[k] = fmaf(wa[et * 3 + 1], nw.x, ya[k]);
+                ya[k] = fmaf(wa[et * 3 + 2], nw.y, ya[k]);
+                yb[k] = fmaf(wa[et * 3 + 0], nw.y, yb[k]);
+                yb[k] = fmaf(wa[et * 3 + 1], nw.z, yb[k]);
+                yb[k] = fmaf(wa[et * 3 + 2], nw.w, yb[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < NY; ++k) {
+            ya[k] = fmaxf(ya[k], 0.0f) * ymask[k];
+            yb[k] = fmaxf(yb[k], 0.0f) * ymask[k];
+        }
+#pragma unroll
+        for (int j = 0; j < TO; ++j) {
+            float acc = bb;
+#pragma unroll
+            for (int dt = 0; dt < 3; ++dt) {
+                acc = fmaf(wb[dt * 3 + 0], prev[2 * j + dt], acc);
+                acc = fmaf(wb[dt * 3 + 1], ya[2 * j + dt], acc);
+                acc = fmaf(wb[dt * 3 + 2], yb[2 * j + dt], acc);
+            }
+            if (to0 + j < T2) o[((size_t)j * 32 + fo) * kSubC] = __float2bfloat16(acc);
+        }
+#pragma unroll
+        for (int k = 0; k < NY; ++k) prev[k] = yb[k];
     }
 }
 
@@ -526,7 +583,7 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
         t2[i + 1] = t2[i] + b;
         t3[i + 1] = t3[i] + d;
     }
-    const int R1 = t1[n], R2 = t2[n], R3 = t3[n];
+    const int R2 = t2[n], R3 = t3[n];
     const int max_t3 = [&] { int mx = 0; for (int i = 0; i < n; ++i) mx = std::max(mx, t3[i + 1] - t3[i]); return mx; }();
     if (max_t3 > kMaxEncFrames) return cudaErrorInvalidValue;
     cudaStream_t st = c->stream;
@@ -542,7 +599,6 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     ENC_CUDA(cudaMemcpyAsync(d_t2, t2.data(), sizeof(int) * (n + 1), cudaMemcpyHostToDevice, st));
     ENC_CUDA(cudaMemcpyAsync(d_t3, t3.data(), sizeof(int) * (n + 1), cudaMemcpyHostToDevice, st));
 
-    ENC_CUDA(ws.y0.ensure((size_t)R1 * 64 * kSubC * sizeof(bf16)));
     ENC_CUDA(ws.y1.ensure((size_t)R2 * 32 * kSubC * sizeof(bf16)));
     ENC_CUDA(ws.y2.ensure((size_t)R2 * 32 * kSubC * sizeof(bf16)));
     ENC_CUDA(ws.y3.ensure((size_t)R3 * 16 * kSubC * sizeof(bf16)));
@@ -558,9 +614,15 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     }
 
     // sub-sampling
-    PROF("sub_conv0", (sub_conv0_kernel<<<R1, 256, 0, st>>>(d_feats, d_t0, d_t1, n, m.sub0_w, m.sub0_b, ws.y0.as<bf16>())));
-    PROF("sub_dw1", (sub_dw_kernel<<<R2, 256, 0, st>>>(ws.y0.as<bf16>(), d_t1, d_t2, n, 64, m.dw1_w, m.dw1_b, ws.y1.as<bf16>())));
-    c->launches += 2;
+    {
+        constexpr int kTO = 2;
+        int max_t2 = 0;
+        for (int i = 0; i < n; ++i) max_t2 = std::max(max_t2, t2[i + 1] - t2[i]);
+        const dim3 grid((max_t2 + kTO - 1) / kTO, n);
+        PROF("sub_conv0_dw1", (sub_conv0_dw1_kernel<kTO><<<grid, 256, 0, st>>>(d_feats, d_t0, d_t1, d_t2, m.sub0_w, m.sub0_b,
+                                                                              m.dw1_w, m.dw1_b, ws.y1.as<bf16>())));
+        c->launches += 1;
+    }
     ENC_CUDA(run_gemm(c, "gemm_sub_pw", ws.y1.p, m.pw1_w, m.pw1_b, ws.y2.p, R2 * 32, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
     PROF("sub_dw2", (sub_dw_kernel<<<R3, 256, 0, st>>>(ws.y2.as<bf16>(), d_t2, d_t3, n, 32, m.dw2_w, m.dw2_b, ws.y3.as<bf16>())));
     c->launches += 1;
@@ -667,15 +729,19 @@ cudaError_t encoder_forward(sb_ctx* c, const Model& m, const float* d_feats, con
     enc_off[0] = 0;
     for (int i = 0; i < n_clips; ++i)
         enc_off[i + 1] = enc_off[i] + encoder_out_frames((int)(frame_off[i + 1] - frame_off[i]));
-    // group clips so that the largest intermediate (conv0 output: T/2 x 64 x 256 bf16 per clip) fits the budget
+    // group clips so that the intermediates of a group fit the budget
     int c0 = 0;
     while (c0 < n_clips) {
         size_t bytes = 0;
         int c1 = c0;
         while (c1 < n_clips) {
             const size_t T = (size_t)(frame_off[c1 + 1] - frame_off[c1]);
-            const size_t need = ((T + 1) / 2) * 64 * kSubC * sizeof(bf16) * 2;  // y0 plus the rest, roughly
-            if (c1 > c0 && bytes + need > workspace_budget_bytes) break;
+            const size_t T2 = ((T - 1) / 2 + 1 - 1) / 2 + 1, T3 = (T2 - 1) / 2 + 1;
+            // two [T2 x 32 x 256] and two [T3 x 16 x 256] bf16 sub-sampling stages, then per encoder frame the f32
+            // stream, bf16 LayerNorm / attention outputs, the 4096-wide hidden row (bf16 and e4m3) and V^T
+            const size_t need = T2 * 32 * kSubC * 2 * 2 + T3 * 16 * kSubC * 2 * 2 +
+                                T3 * (kDModel * (4 + 2 + 2) + kFF * (2 + 1) + 16) + attention_vt_bytes(1);
+            if (c1 > c0 && (bytes + need > workspace_budget_bytes || c1 - c0 >= 32768)) break;
             bytes += need;
             ++c1;
         }

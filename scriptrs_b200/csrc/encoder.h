@@ -5,9 +5,9 @@
 namespace sb {
 
 struct EncoderWorkspace {
-    Buffer offsets, y0, y1, y2, y3, y4, x, a, h, att, vt, h8, rs;
+    Buffer offsets, y1, y2, y3, y4, x, a, h, att, vt, h8, rs;
     void release() {
-        offsets.release(); y0.release(); y1.release(); y2.release(); y3.release(); y4.release();
+        offsets.release(); y1.release(); y2.release(); y3.release(); y4.release();
         x.release(); a.release(); h.release(); att.release(); vt.release(); h8.release(); rs.release();
     }
 };
