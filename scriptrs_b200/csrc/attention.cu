@@ -14,7 +14,7 @@
 //   softmax  four threads per query row (each a quarter of the columns): the shifted S_bd row goes through a private
 //            fp32 row of shared memory, the scores S_ac + S_bd stay in registers; max, exp2, sum; probabilities
 //            written as the bf16 A operand
-//   MMA 3    O = P V                  (128 x 128, V supplied transposed so that it is K-major)
+//   MMA 3    O = P V                  (128 x 128; V is read as it lies in memory, as an MN-major B operand)
 //   store    O / sum -> bf16, staged through shared memory, coalesced rows
 // The u and v biases enter as per-key (u.k_j, computed here) and per-position (v.p, computed at model
 // load) scalars written into the accumulators before the products are issued, so Q goes to the tensor
@@ -42,7 +42,7 @@ constexpr int kSStride = 189;        // floats per shifted S_bd row (odd: confli
 constexpr int kR1 = 97280;           // table rows (2 x 40 KB) / shifted S_bd rows (128 x 189 x 4) / probabilities + output staging
 constexpr int kR2 = 49152;           // K (2 x 24 KB), resident for both query blocks
 constexpr int kR3 = 32768;           // Q (2 x 16 KB)
-constexpr int kR4 = 49152;           // V^T (3 x 16 KB)
+constexpr int kR4 = 49152;           // V (2 blocks of 64 d x 192 key rows)
 constexpr int kPOff = 0;             // probabilities inside region 1 (3 x 16 KB)
 constexpr int kOOff = 49152;         // output staging inside region 1
 constexpr int kTailOff = 128 * kSStride * 4;  // 512 spare bytes of region 1 that no other use touches
@@ -59,7 +59,7 @@ __device__ __forceinline__ uint32_t idesc_bf16(int n) {
 
 __global__ void __launch_bounds__(kATh, 1)
 relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_pos,
-                           const __grid_constant__ CUtensorMap map_vt, const int* __restrict__ t3_off,
+                           const int* __restrict__ t3_off,
                            const float* __restrict__ bias_u, const float* __restrict__ pos_vp,
                            bf16* __restrict__ out, int* __restrict__ error) {
     extern __shared__ __align__(1024) unsigned char att_dyn[];
@@ -110,13 +110,15 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
     const uint32_t tmem = *tmem_slot;
     const uint32_t tq = tmem + ((uint32_t)(lg * 32) << 16);
 
-    // V^T of this (clip, head): [128 d x 192 j], three K-blocks of 64 j
+    // V of this (clip, head) as it lies in memory, [192 j x 128 d]: an MN-major B operand, two blocks of 64 d,
+    // each 192 key rows of 128 bytes.  Rows beyond T' belong to the next clip (or are zero fill) and meet
+    // probabilities that are exactly zero.
     if (tid == 0) {
         mbar_expect_tx(bar_v, 6 * kBoxBytes);
-        const int vrow = (clip * kHeads + head) * kHeadDim;
-        for (int kb = 0; kb < 3; ++kb)
-            for (int h = 0; h < 2; ++h)
-                tma_load_2d(r4 + kb * 16384 + h * kBoxBytes, &map_vt, bar_v, kb * 64, vrow + h * 64);
+        for (int h = 0; h < 2; ++h)
+            for (int kb = 0; kb < 3; ++kb)
+                tma_load_2d(r4 + h * 24576 + kb * kBoxBytes, &map_qkv, bar_v, 2 * kDModel + head * kHeadDim + h * 64,
+                            row0 + kb * 64);
     }
 
     const float sc2 = 0.08838834764831845f * 1.4426950408889634f;  // log2(e) / sqrt(128)
@@ -300,8 +302,8 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
 #pragma unroll
             for (int k = 0; k < kNK / 16; ++k) {
                 const int kb = k >> 2, ko = (k & 3) * 2;
-                tc_mma<false>(tmem, make_smem_desc(r1 + kPOff + kb * 16384) + ko, make_smem_desc(r4 + kb * 16384) + ko,
-                              idesc_bf16(kHeadDim), k ? 1u : 0u);
+                tc_mma<false>(tmem, make_smem_desc(r1 + kPOff + kb * 16384) + ko, make_smem_desc_mn(r4 + k * 2048, 24576),
+                              idesc_bf16(kHeadDim) | (1u << 16), k ? 1u : 0u);
             }
             tc_commit(bar_mma);
         }
@@ -354,30 +356,6 @@ relpos_attention_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __
     if (tid == 0 && *abort_flag) atomicExch(error, 1);
 }
 
-// qkv [rows x 3072] -> vt [(clip * 8 + head) * 128 + d][192] (keys beyond T' are zero).  grid (8, clips).
-__global__ void __launch_bounds__(256)
-transpose_v_kernel(const bf16* __restrict__ qkv, const int* __restrict__ t3_off, bf16* __restrict__ vt) {
-    __shared__ bf16 tile[32][kHeadDim + 2];
-    const int head = blockIdx.x, clip = blockIdx.y;
-    const int row0 = t3_off[clip];
-    const int t = t3_off[clip + 1] - row0;
-    bf16* dst = vt + (size_t)(clip * kHeads + head) * kHeadDim * kNK;
-    for (int j0 = 0; j0 < kNK; j0 += 32) {
-        for (int idx = threadIdx.x; idx < 32 * kHeadDim; idx += 256) {
-            const int jl = idx >> 7, d = idx & 127;
-            const int j = j0 + jl;
-            tile[jl][d] = j < t ? qkv[(size_t)(row0 + j) * (3 * kDModel) + 2 * kDModel + head * kHeadDim + d]
-                                : __float2bfloat16(0.0f);
-        }
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < 32 * kHeadDim; idx += 256) {
-            const int d = idx >> 5, jl = idx & 31;
-            dst[(size_t)d * kNK + j0 + jl] = tile[jl][d];
-        }
-        __syncthreads();
-    }
-}
-
 // vp[p][h] = sum_d v[h][d] * pos[p][h * 128 + d].  grid kPosRows, 256 threads (8 warps = 8 heads).
 __global__ void __launch_bounds__(256)
 pos_bias_kernel(const bf16* __restrict__ pos, const float* __restrict__ bias_v, float* __restrict__ vp) {
@@ -418,23 +396,19 @@ cudaError_t attention_configure() {
     return cudaFuncSetAttribute(relpos_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttSmem);
 }
 
-size_t attention_vt_bytes(int n_clips) { return (size_t)n_clips * kHeads * kHeadDim * kNK * sizeof(bf16); }
-
 cudaError_t pos_bias_launch(const bf16* pos_proj, const float* bias_v, float* vp, cudaStream_t st) {
     pos_bias_kernel<<<kPosRows, 256, 0, st>>>(pos_proj, bias_v, vp);
     return cudaGetLastError();
 }
 
 cudaError_t attention_launch(const bf16* qkv, int rows, const int* d_t3_off, int n_clips, const bf16* pos_proj,
-                             const float* bias_u, const float* pos_vp, bf16* vt, bf16* out, int* d_error,
+                             const float* bias_u, const float* pos_vp, bf16* out, int* d_error,
                              cudaStream_t st) {
     if (n_clips <= 0 || rows <= 0) return cudaSuccess;
-    alignas(64) CUtensorMap mq, mp, mv;
-    if (!map_bf16(&mq, qkv, rows, 3 * kDModel) || !map_bf16(&mp, pos_proj, kPosRows, kDModel) ||
-        !map_bf16(&mv, vt, (int64_t)n_clips * kHeads * kHeadDim, kNK))
+    alignas(64) CUtensorMap mq, mp;
+    if (!map_bf16(&mq, qkv, rows, 3 * kDModel) || !map_bf16(&mp, pos_proj, kPosRows, kDModel))
         return cudaErrorInvalidValue;
-    transpose_v_kernel<<<dim3(kHeads, n_clips), 256, 0, st>>>(qkv, d_t3_off, vt);
-    relpos_attention_tc_kernel<<<dim3(kHeads, n_clips), kATh, kAttSmem, st>>>(mq, mp, mv, d_t3_off, bias_u, pos_vp, out,
+    relpos_attention_tc_kernel<<<dim3(kHeads, n_clips), kATh, kAttSmem, st>>>(mq, mp, d_t3_off, bias_u, pos_vp, out,
                                                                             d_error);
     return cudaGetLastError();
 }

@@ -189,22 +189,12 @@ sub_dw_kernel(const bf16* __restrict__ in, const int* __restrict__ tin_off, cons
 }
 
 // ---------------------------------------------------------------- LayerNorm
-// One warp per row of 1024.  OUT_F32: write f32 (in place allowed), else bf16.
-template <bool OUT_F32>
-__global__ void __launch_bounds__(256)
-layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
-                 void* __restrict__ out, int rows) {
-    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const int lane = threadIdx.x & 31;
-    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * kDModel);
-    float4 v[8];
+// One warp per row of 1024; the row stays in registers (8 float4 per lane).
+__device__ __forceinline__ void ln_row(float4 (&v)[8], const float* __restrict__ gamma, const float* __restrict__ beta,
+                                       int lane) {
     float s = 0.0f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        v[k] = xr[lane + 32 * k];
-        s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
-    }
+    for (int k = 0; k < 8; ++k) s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     const float mean = s * (1.0f / kDModel);
@@ -222,15 +212,39 @@ layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gamma, c
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         const float4 g = g4[lane + 32 * k], b = b4[lane + 32 * k];
-        float4 y;
-        y.x = (v[k].x - mean) * rstd * g.x + b.x;
-        y.y = (v[k].y - mean) * rstd * g.y + b.y;
-        y.z = (v[k].z - mean) * rstd * g.z + b.z;
-        y.w = (v[k].w - mean) * rstd * g.w + b.w;
+        v[k].x = (v[k].x - mean) * rstd * g.x + b.x;
+        v[k].y = (v[k].y - mean) * rstd * g.y + b.y;
+        v[k].z = (v[k].z - mean) * rstd * g.z + b.z;
+        v[k].w = (v[k].w - mean) * rstd * g.w + b.w;
+    }
+}
+
+// OUT_F32: write f32 (in place allowed), else bf16.  With pre_gamma the row is first normalised with
+// (pre_gamma, pre_beta) and that result written back to x as f32: the closing LayerNorm of one Conformer block
+// and the opening one of the next in a single pass over the row.
+template <bool OUT_F32>
+__global__ void __launch_bounds__(256)
+layernorm_kernel(float* x, const float* __restrict__ pre_gamma, const float* __restrict__ pre_beta,
+                 const float* __restrict__ gamma, const float* __restrict__ beta, void* out, int rows) {
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)row * kDModel);
+    float4 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = xr[lane + 32 * k];
+    if (pre_gamma) {
+        ln_row(v, pre_gamma, pre_beta, lane);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) xr[lane + 32 * k] = v[k];
+    }
+    ln_row(v, gamma, beta, lane);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
         if (OUT_F32) {
-            reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)row * kDModel)[lane + 32 * k] = y;
+            reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)row * kDModel)[lane + 32 * k] = v[k];
         } else {
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(y.x, y.y), p1 = __floats2bfloat162_rn(y.z, y.w);
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[k].x, v[k].y), p1 = __floats2bfloat162_rn(v[k].z, v[k].w);
             uint2 pk;
             pk.x = *reinterpret_cast<uint32_t*>(&p0);
             pk.y = *reinterpret_cast<uint32_t*>(&p1);
@@ -245,44 +259,27 @@ __device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d
     return lo | (hi << 16);  // cvt2_e4m3 pairs: byte 0 = a, 1 = b, 2 = c, 3 = d
 }
 
-// LayerNorm with an e4m3 output row and its scale: q = y / scale, scale = max|y| / 448.
+// LayerNorm with an e4m3 output row and its scale: q = y / scale, scale = max|y| / 448.  pre_gamma as above.
 __global__ void __launch_bounds__(256)
-layernorm_fp8_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
-                     uint8_t* __restrict__ out, float* __restrict__ row_scale, int rows, float* __restrict__ next_scale,
-                     float wn, float bmax) {
+layernorm_fp8_kernel(float* x, const float* __restrict__ pre_gamma, const float* __restrict__ pre_beta,
+                     const float* __restrict__ gamma, const float* __restrict__ beta, uint8_t* __restrict__ out,
+                     float* __restrict__ row_scale, int rows, float* __restrict__ next_scale, float wn, float bmax) {
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
-    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * kDModel);
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)row * kDModel);
     float4 v[8];
-    float s = 0.0f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        v[k] = xr[lane + 32 * k];
-        s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    for (int k = 0; k < 8; ++k) v[k] = xr[lane + 32 * k];
+    if (pre_gamma) {
+        ln_row(v, pre_gamma, pre_beta, lane);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) xr[lane + 32 * k] = v[k];
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    const float mean = s * (1.0f / kDModel);
-    float q = 0.0f;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
-        q += (a * a + b * b) + (c * c + d * d);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
-    const float rstd = rsqrtf(q * (1.0f / kDModel) + 1e-5f);
-    const float4* g4 = reinterpret_cast<const float4*>(gamma);
-    const float4* b4 = reinterpret_cast<const float4*>(beta);
+    ln_row(v, gamma, beta, lane);
     float amax = 0.0f, ss = 0.0f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-        const float4 g = g4[lane + 32 * k], b = b4[lane + 32 * k];
-        v[k].x = (v[k].x - mean) * rstd * g.x + b.x;
-        v[k].y = (v[k].y - mean) * rstd * g.y + b.y;
-        v[k].z = (v[k].z - mean) * rstd * g.z + b.z;
-        v[k].w = (v[k].w - mean) * rstd * g.w + b.w;
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[k].x), fabsf(v[k].y)), fmaxf(fabsf(v[k].z), fabsf(v[k].w))));
         ss += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
     }
@@ -474,8 +471,8 @@ glu_dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, c
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float2 af = __bfloat1622float2(a2[e]), gf = __bfloat1622float2(g2[e]);
-                g[2 * e] = af.x / (1.0f + __expf(-gf.x));
-                g[2 * e + 1] = af.y / (1.0f + __expf(-gf.y));
+                g[2 * e] = __fdividef(af.x, 1.0f + __expf(-gf.x));
+                g[2 * e + 1] = __fdividef(af.y, 1.0f + __expf(-gf.y));
             }
         } else {
 #pragma unroll
@@ -505,8 +502,8 @@ glu_dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, c
             a0 = fmaf(w0[k], win[r + k].x, a0);
             a1 = fmaf(w1[k], win[r + k].y, a1);
         }
-        a0 = a0 / (1.0f + __expf(-a0));
-        a1 = a1 / (1.0f + __expf(-a1));
+        a0 = __fdividef(a0, 1.0f + __expf(-a0));
+        a1 = __fdividef(a1, 1.0f + __expf(-a1));
         *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(r0 + tb + rh + r) * kDModel + c0 + cp) =
             __floats2bfloat162_rn(a0, a1);
     }
@@ -607,7 +604,6 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     ENC_CUDA(ws.a.ensure((size_t)R3 * kDModel * sizeof(bf16)));
     ENC_CUDA(ws.h.ensure((size_t)R3 * kFF * sizeof(bf16)));
     ENC_CUDA(ws.att.ensure((size_t)R3 * kDModel * sizeof(bf16)));
-    ENC_CUDA(ws.vt.ensure(attention_vt_bytes(n)));
     if (c->fp8 && m.has_fp8) {
         ENC_CUDA(ws.h8.ensure((size_t)R3 * kFF));
         ENC_CUDA(ws.rs.ensure((size_t)R3 * 2 * sizeof(float)));
@@ -640,21 +636,21 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     float* rs_a = ws.rs.as<float>();
     float* rs_h = rs_a + R3;
     // feed-forward module: x += 0.5 * W2 silu(W1 LN(x) + b1) + b2
-    auto feed_forward = [&](const float* g, const float* b, const bf16* w1, const uint8_t* w1q, const float* w1s,
+    auto feed_forward = [&](const float* pg, const float* pb, const float* g, const float* b, const bf16* w1, const uint8_t* w1q, const float* w1s,
                             const float* b1, const bf16* w2, const uint8_t* w2q, const float* w2s,
                             const float* b2, float wn, float bmax) -> cudaError_t {
         if (fp8 && (c->fp8_mask & 3) == 3) {
             // LayerNorm -> e4m3; up-projection writes the e4m3 hidden row with a scale bounded in advance
-            PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, g, b, a8, rs_a, R3, rs_h, wn, bmax)));
+            PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, pg, pb, g, b, a8, rs_a, R3, rs_h, wn, bmax)));
             ENC_CUDA(run_gemm_fp8(c, "gemm_ff_up_fp8", a8, rs_a, w1q, w1s, b1, h8, R3, kFF, kDModel, kActSilu, kOutFp8, 1.0f, rs_h));
             ENC_CUDA(run_gemm_fp8(c, "gemm_ff_down_fp8", h8, rs_h, w2q, w2s, b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
             c->launches += 1;
         } else if (fp8 && (c->fp8_mask & 3)) {
             if (c->fp8_mask & 1) {
-                PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, g, b, a8, rs_a, R3, nullptr, 0.0f, 0.0f)));
+                PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, pg, pb, g, b, a8, rs_a, R3, nullptr, 0.0f, 0.0f)));
                 ENC_CUDA(run_gemm_fp8(c, "gemm_ff_up_fp8", a8, rs_a, w1q, w1s, b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
             } else {
-                PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, g, b, a, R3)));
+                PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, pg, pb, g, b, a, R3)));
                 ENC_CUDA(run_gemm(c, "gemm_ff_up", a, w1, b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
             }
             if (c->fp8_mask & 2) {
@@ -666,7 +662,7 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
             }
             c->launches += 1;
         } else {
-            PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, g, b, a, R3)));
+            PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, pg, pb, g, b, a, R3)));
             ENC_CUDA(run_gemm(c, "gemm_ff_up", a, w1, b1, h, R3, kFF, kDModel, kActSilu, kOutBf16, 1.0f));
             ENC_CUDA(run_gemm(c, "gemm_ff_down", h, w2, b2, x, R3, kDModel, kFF, kActNone, kOutResidual, 0.5f));
             c->launches += 1;
@@ -677,10 +673,10 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     auto norm_project = [&](const char* label, const char* label8, const float* g, const float* b, const bf16* w,
                             const uint8_t* wq, const float* wsc, const float* bias, int N) -> cudaError_t {
         if (fp8 && (c->fp8_mask & (N == 3 * kDModel ? 4 : 8))) {
-            PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, g, b, a8, rs_a, R3, nullptr, 0.0f, 0.0f)));
+            PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, nullptr, nullptr, g, b, a8, rs_a, R3, nullptr, 0.0f, 0.0f)));
             ENC_CUDA(run_gemm_fp8(c, label8, a8, rs_a, wq, wsc, bias, h, R3, N, kDModel, kActNone, kOutBf16, 1.0f));
         } else {
-            PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, g, b, a, R3)));
+            PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, nullptr, nullptr, g, b, a, R3)));
             ENC_CUDA(run_gemm(c, label, a, w, bias, h, R3, N, kDModel, kActNone, kOutBf16, 1.0f));
         }
         c->launches += 1;
@@ -689,7 +685,10 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     for (int l = 0; l < m.layers; ++l) {
         const LayerWeights& L = m.L[l];
         // x += 0.5 * FF1(LN x)
-        ENC_CUDA(feed_forward(L.ln_ff1_g, L.ln_ff1_b, L.ff1_w1, L.ff1_w1_q, L.ff1_w1_s, L.ff1_b1, L.ff1_w2, L.ff1_w2_q,
+        // (for blocks after the first, the previous block's closing LayerNorm runs inside this one's first)
+        const float* pre_g = l > 0 ? m.L[l - 1].ln_out_g : nullptr;
+        const float* pre_b = l > 0 ? m.L[l - 1].ln_out_b : nullptr;
+        ENC_CUDA(feed_forward(pre_g, pre_b, L.ln_ff1_g, L.ln_ff1_b, L.ff1_w1, L.ff1_w1_q, L.ff1_w1_s, L.ff1_b1, L.ff1_w2, L.ff1_w2_q,
                               L.ff1_w2_s, L.ff1_b2, L.ff1_wn, L.ff1_bmax));
         // x += MHA(LN x)
         ENC_CUDA(norm_project("gemm_qkv", "gemm_qkv_fp8", L.ln_att_g, L.ln_att_b, L.qkv_w, L.qkv_w_q, L.qkv_w_s, L.qkv_b,
@@ -698,8 +697,8 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
             PROF("relpos_attention_simt", (relpos_attention_kernel<<<dim3(kHeads, n), kAttThreads, kAttSmemBytes, st>>>(
                                               h, d_t3, L.pos_proj, L.bias_u, L.bias_v, att)));
         } else {
-            c->prof.begin("relpos_attention(transpose+tcgen05)", st);
-            ENC_CUDA(attention_launch(h, R3, d_t3, n, L.pos_proj, L.bias_u, L.pos_vp, ws.vt.as<bf16>(), att, c->d_error, st));
+            c->prof.begin("relpos_attention_tc", st);
+            ENC_CUDA(attention_launch(h, R3, d_t3, n, L.pos_proj, L.bias_u, L.pos_vp, att, c->d_error, st));
             c->prof.end(st);
             c->launches += 1;
         }
@@ -711,12 +710,16 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
                                h, d_t3, L.dw_w, L.dw_b, att)));
         ENC_CUDA(run_gemm(c, "gemm_conv_pw2", att, L.pw2_w, L.pw2_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
         // x += 0.5 * FF2(LN x)
-        ENC_CUDA(feed_forward(L.ln_ff2_g, L.ln_ff2_b, L.ff2_w1, L.ff2_w1_q, L.ff2_w1_s, L.ff2_b1, L.ff2_w2, L.ff2_w2_q,
+        ENC_CUDA(feed_forward(nullptr, nullptr, L.ln_ff2_g, L.ln_ff2_b, L.ff2_w1, L.ff2_w1_q, L.ff2_w1_s, L.ff2_b1, L.ff2_w2, L.ff2_w2_q,
                               L.ff2_w2_s, L.ff2_b2, L.ff2_wn, L.ff2_bmax));
-        // x = LN_out(x); the last block writes straight into the caller's buffer
-        float* dst = (l == m.layers - 1) ? d_out + (size_t)enc_off_all[c0] * kDModel : x;
-        PROF("layernorm", (layernorm_kernel<true><<<ln_grid, 256, 0, st>>>(x, L.ln_out_g, L.ln_out_b, dst, R3)));
-        c->launches += 3;
+        // x = LN_out(x): the last block writes straight into the caller's buffer; the others leave it to the
+        // next block's first LayerNorm
+        if (l == m.layers - 1) {
+            float* dst = d_out + (size_t)enc_off_all[c0] * kDModel;
+            PROF("layernorm", (layernorm_kernel<true><<<ln_grid, 256, 0, st>>>(x, nullptr, nullptr, L.ln_out_g, L.ln_out_b, dst, R3)));
+            c->launches += 1;
+        }
+        c->launches += 1;  // GLU + depthwise convolution
     }
     if (m.layers == 0)
         ENC_CUDA(cudaMemcpyAsync(d_out + (size_t)enc_off_all[c0] * kDModel, x, (size_t)R3 * kDModel * sizeof(float),
@@ -738,9 +741,9 @@ cudaError_t encoder_forward(sb_ctx* c, const Model& m, const float* d_feats, con
             const size_t T = (size_t)(frame_off[c1 + 1] - frame_off[c1]);
             const size_t T2 = ((T - 1) / 2 + 1 - 1) / 2 + 1, T3 = (T2 - 1) / 2 + 1;
             // two [T2 x 32 x 256] and two [T3 x 16 x 256] bf16 sub-sampling stages, then per encoder frame the f32
-            // stream, bf16 LayerNorm / attention outputs, the 4096-wide hidden row (bf16 and e4m3) and V^T
+            // stream, bf16 LayerNorm / attention outputs, the 4096-wide hidden row (bf16 and e4m3)
             const size_t need = T2 * 32 * kSubC * 2 * 2 + T3 * 16 * kSubC * 2 * 2 +
-                                T3 * (kDModel * (4 + 2 + 2) + kFF * (2 + 1) + 16) + attention_vt_bytes(1);
+                                T3 * (kDModel * (4 + 2 + 2) + kFF * (2 + 1) + 16);
             if (c1 > c0 && (bytes + need > workspace_budget_bytes || c1 - c0 >= 32768)) break;
             bytes += need;
             ++c1;

@@ -5,10 +5,10 @@
 namespace sb {
 
 struct EncoderWorkspace {
-    Buffer offsets, y1, y2, y3, y4, x, a, h, att, vt, h8, rs;
+    Buffer offsets, y1, y2, y3, y4, x, a, h, att, h8, rs;
     void release() {
         offsets.release(); y1.release(); y2.release(); y3.release(); y4.release();
-        x.release(); a.release(); h.release(); att.release(); vt.release(); h8.release(); rs.release();
+        x.release(); a.release(); h.release(); att.release(); h8.release(); rs.release();
     }
 };
 

@@ -146,6 +146,13 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
     return ((uint64_t)hi << 32) | lo;
 }
+// The same for an MN-major operand (the 128-byte rows run along M or N; each 8-row group holds 8 consecutive K
+// indices): groups of 8 K rows are 1024 bytes apart, blocks of 64 M/N elements are lbo_bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+    const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
 
 
 }  // namespace ptx
