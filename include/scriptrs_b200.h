@@ -105,8 +105,9 @@ int64_t sb_ctx_kernel_launches(const sb_ctx* ctx);
 /* Tuning and test switches.  "fp8" (0/1): run the feed-forward, QKV and first pointwise GEMMs of every
  * Conformer block in FP8 e4m3 (per-row activation scales, per-output-channel weight scales, fp32
  * accumulation); needs a model loaded with fp8_weights.  "simt_attention" (0/1): run the relative-position attention on CUDA cores
- * instead of the tensor-core kernel; "workspace_budget_mb": bytes of encoder intermediates per group
- * of clips (default 12288). */
+ * instead of the tensor-core kernel; "simt_decode" (0/1): run the TDT predictor and joint in plain fp32 on
+ * CUDA cores (one persistent kernel) instead of the split-bf16 tensor-core steps; "workspace_budget_mb":
+ * bytes of encoder intermediates per group of clips (default 12288). */
 int32_t sb_ctx_set_option(sb_ctx* ctx, const char* name, int64_t value);
 
 /* In-situ timing (off by default): CUDA events around every kernel launch, summed per kernel label.

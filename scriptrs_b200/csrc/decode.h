@@ -36,4 +36,16 @@ cudaError_t decode_enc_projection(const float* d_enc, const float* w_enc, const 
 cudaError_t decode_launch(const DecodeWeights& w, const DecodeState& s, int max_steps, int sm_count,
                           cudaStream_t stream);
 
+
+size_t decode_tc_weight_bytes();
+cudaError_t decode_tc_prepare(const DecodeWeights& w, const float* w_enc, DecodeTcWeights* t, void* storage,
+                              cudaStream_t st);
+size_t decode_tc_scratch_bytes(int64_t enc_rows, int n_seq);
+cudaError_t decode_tc_enc_projection(const DecodeTcWeights& t, const float* d_enc, const float* b_enc, float* d_proj,
+                                     int64_t rows, void* scratch, int sm_count, int* d_error, int64_t* launches,
+                                     cudaStream_t st);
+cudaError_t decode_tc_run(const DecodeWeights& w, const DecodeTcWeights& t, const DecodeState& s, int max_steps,
+                          void* scratch_after_enc, int* d_alive, int sm_count, int* d_error, int64_t* launches,
+                          cudaStream_t st);
+
 }  // namespace sb

@@ -16,6 +16,7 @@
 #include "attention.h"
 #include "encoder.h"
 #include "gemm.h"
+#include "decode.h"
 #include "model.h"
 #include "pipeline.h"
 
@@ -292,6 +293,17 @@ int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensor
         m->w_out = ld.f32("joint.out.weight", (int64_t)kJointOut * J);
         m->b_out = ld.f32("joint.out.bias", kJointOut);
         m->has_decoder = true;
+        if (ld.err.empty()) {
+            void* storage = nullptr;
+            if (cudaMalloc(&storage, decode_tc_weight_bytes()) != cudaSuccess) {
+                ld.err = "out of device memory for the decoder weights";
+            } else {
+                m->allocations.push_back(storage);
+                const DecodeWeights dw{m->embedding, m->w_ih, m->w_hh, m->b_gates, m->w_pred, m->b_pred, m->w_out, m->b_out};
+                if (decode_tc_prepare(dw, m->w_enc, &m->tc, storage, c->stream) != cudaSuccess)
+                    ld.err = "decoder weight preparation failed";
+            }
+        }
     }
 
     cudaError_t se = cudaStreamSynchronize(c->stream);

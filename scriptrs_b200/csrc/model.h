@@ -54,6 +54,16 @@ struct LayerWeights {
     float ff1_wn, ff1_bmax, ff2_wn, ff2_bmax;
 };
 
+// Split-bf16 copies of the predictor / joint weights for the tensor-core path (decode_tc.cu): every row is
+// [hi | lo | hi] over a tripled K; the joint output matrix and bias are padded to 1152 rows.
+struct DecodeTcWeights {
+    bf16 *w0 = nullptr, *w1 = nullptr;  // [2560 x 3 * 1280]  ([W_ih | W_hh] of each LSTM layer)
+    bf16* wp = nullptr;                 // [640 x 3 * 640]
+    bf16* wo = nullptr;                 // [1152 x 3 * 640]
+    bf16* wenc = nullptr;               // [640 x 3 * 1024]
+    float* b_out = nullptr;             // [1152]
+};
+
 struct Model {
     int layers = 0;
     float xscale = 1.0f;
@@ -71,6 +81,7 @@ struct Model {
     float *embedding = nullptr, *w_ih = nullptr, *w_hh = nullptr, *b_gates = nullptr;  // b_gates = b_ih + b_hh
     bf16* enc_proj_w = nullptr;  // [640 x 1024] bf16 copy for the tensor-core projection
     float *w_enc = nullptr, *b_enc = nullptr, *w_pred = nullptr, *b_pred = nullptr, *w_out = nullptr, *b_out = nullptr;
+    DecodeTcWeights tc;  // split-bf16 copies for the tensor-core decoder
     std::vector<void*> allocations;
 };
 

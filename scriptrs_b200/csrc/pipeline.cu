@@ -15,12 +15,12 @@
 namespace sb {
 
 struct DecodeWorkspace {
-    Buffer ints, floats, enc_proj, out_tok, out_frm, out_dur, out_conf, trace, timing;
+    Buffer ints, floats, enc_proj, out_tok, out_frm, out_dur, out_conf, trace, timing, tc;
     Buffer h_tok, h_frm, h_dur, h_conf;  // pinned host staging
     DecodeWorkspace() { h_tok.pinned_host = h_frm.pinned_host = h_dur.pinned_host = h_conf.pinned_host = true; }
     void release() {
         ints.release(); floats.release(); enc_proj.release(); out_tok.release(); out_frm.release(); out_dur.release();
-        out_conf.release(); trace.release(); timing.release(); h_tok.release(); h_frm.release(); h_dur.release(); h_conf.release();
+        out_conf.release(); trace.release(); timing.release(); tc.release(); h_tok.release(); h_frm.release(); h_dur.release(); h_conf.release();
     }
 };
 
@@ -83,10 +83,19 @@ int32_t tdt_decode(sb_ctx* c, const float* d_enc, const int64_t* enc_offsets, in
         SB_CUDA(ws.out_conf.ensure((size_t)n * max_tokens * sizeof(float)));
         if (logits_trace) SB_CUDA(ws.trace.ensure((size_t)n * trace_cap * kJointOut * sizeof(float)));
 
-        c->prof.begin("decode_enc_projection", st);
-        SB_CUDA(decode_enc_projection(d_enc + row0 * kDModel, m.w_enc, m.b_enc, ws.enc_proj.as<float>(), (int)rows, st));
-        c->prof.end(st);
-        c->launches += rows > 0 ? 1 : 0;
+        const bool tc = !c->simt_decode;
+        if (tc) {
+            SB_CUDA(ws.tc.ensure(decode_tc_scratch_bytes(rows, n)));
+            c->prof.begin("decode_enc_projection_tc", st);
+            SB_CUDA(decode_tc_enc_projection(m.tc, d_enc + row0 * kDModel, m.b_enc, ws.enc_proj.as<float>(), rows, ws.tc.p,
+                                             c->sm_count, c->d_error, &c->launches, st));
+            c->prof.end(st);
+        } else {
+            c->prof.begin("decode_enc_projection", st);
+            SB_CUDA(decode_enc_projection(d_enc + row0 * kDModel, m.w_enc, m.b_enc, ws.enc_proj.as<float>(), (int)rows, st));
+            c->prof.end(st);
+            c->launches += rows > 0 ? 1 : 0;
+        }
 
         DecodeWeights w{m.embedding, m.w_ih, m.w_hh, m.b_gates, m.w_pred, m.b_pred, m.w_out, m.b_out};
         DecodeState s{};
@@ -125,7 +134,13 @@ int32_t tdt_decode(sb_ctx* c, const float* d_enc, const int64_t* enc_offsets, in
         }
         s.timing = d_timing;
         const int max_steps = (kMaxSymbols + 1) * max_len + 2;
-        if (max_len > 0) {
+        if (max_len > 0 && tc) {
+            // the per-sequence buffers follow the split encoder rows in the scratch area
+            char* after_enc = static_cast<char*>(ws.tc.p) + sizeof(bf16) * (size_t)rows * 3 * kDModel;
+            c->prof.begin("tdt_decode_tc", st);
+            SB_CUDA(decode_tc_run(w, m.tc, s, max_steps, after_enc, di + 8 * n + 1, c->sm_count, c->d_error, &c->launches, st));
+            c->prof.end(st);
+        } else if (max_len > 0) {
             c->prof.begin("tdt_decode", st);
             SB_CUDA(decode_launch(w, s, max_steps, c->sm_count, st));
             c->prof.end(st);

@@ -2,7 +2,8 @@
 
 Bit-exactness: the token ids, frame indices and durations the GPU emits must equal what the
 reference's state machine produces when it is fed the very logits the GPU computed (logit replay).
-Numerics: the GPU's fp32 logits must agree with the fp32 oracle's to 1e-4 relative."""
+Numerics: the GPU's logits (fp32 CUDA-core path, and the three-term split-bf16 tensor-core path) must agree with
+the fp32 oracle's to 1e-4 relative."""
 import numpy as np
 import pytest
 
@@ -23,6 +24,14 @@ def decode_gpu(ctx, encs, trace=True):
     torch.cuda.synchronize()
     tmax = int(max(e.shape[0] for e in encs))
     return sb.tdt_decode_device(ctx, d_enc.data_ptr(), offs, trace_cap=(11 * tmax + 2) if trace else 0)
+
+
+@pytest.fixture(params=["tensor", "simt"], autouse=True)
+def decode_path(request, ctx):
+    """Every test runs on both decoders: split-bf16 tensor-core steps (default) and the fp32 persistent kernel."""
+    ctx.set_option("simt_decode", 1 if request.param == "simt" else 0)
+    yield request.param
+    ctx.set_option("simt_decode", 0)
 
 
 @pytest.fixture(scope="module")
