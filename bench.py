@@ -385,11 +385,13 @@ def run_longform(args, rank, world, local):
         return sbd.gather_and_finish(vocab, n, raws, rank, world)
 
     phases = {"transcribe_ms": 0.0, "gather_merge_text_ms": 0.0}
+    host_raws = []
 
     def host_step():
         t_a = time.perf_counter()
         raws = sb.transcribe_chunks(ctx, None, mine, audio_ptr=h_audio.data_ptr(), n_samples=n)
         t_b = time.perf_counter()
+        host_raws[:] = [raws]
         r = gather_and_finish(raws)
         phases["transcribe_ms"] += (t_b - t_a) * 1e3
         phases["gather_merge_text_ms"] += (time.perf_counter() - t_b) * 1e3
@@ -433,6 +435,8 @@ def run_longform(args, rank, world, local):
     barrier_sync(world)
     e2e_ms = max_over_ranks(e2e_ms, world, device)
     span = (mine[-1][1] - mine[0][0]) if mine else 0
+    # the host-buffer path (PCM copied in pieces under the kernels) must give the token streams of the resident path
+    same = bool(host_raws) and all(np.array_equal(x, y) for x, y in zip(host_raws[0].flat(), raws.flat()))
 
     # the other precision of the encoder GEMMs, same device-resident step (reported beside the headline, which stays
     # at the precision asked for on the command line)
@@ -514,7 +518,7 @@ def run_longform(args, rank, world, local):
                      "whole_step_tflops_per_gpu": enc_flops / world / (ms_per_step * 1e-3) / 1e12},
         "e2e": {"value": audio_s / (e2e_ms * 1e-3), "unit": "audio-sec/sec", "h2d_bytes_per_step": int(span * 4),
                 "d2h_bytes_per_step": int(n_tokens * 16), "steps": e2e_steps, "ms_per_step": e2e_ms,
-                "transcript_tokens": (len(res) if res is not None else None),
+                "transcript_tokens": (len(res) if res is not None else None), "equals_resident_path_rank0": same,
                 "rank0_phases_ms": {k: v / e2e_steps for k, v in phases.items()}},
         "gpu_launches": int(launches),
         "fp8_variant": variant,

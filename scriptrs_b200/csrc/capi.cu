@@ -242,6 +242,8 @@ void sb_ctx_destroy(sb_ctx* c) {
     if (c->d_tables) cudaFree(c->d_tables);
     if (c->d_error) cudaFree(c->d_error);
     c->prof.release();
+    for (cudaEvent_t e : c->copy_events) cudaEventDestroy(e);
+    if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     if (c->own_stream) cudaStreamDestroy(c->own_stream);
     delete c;
 }

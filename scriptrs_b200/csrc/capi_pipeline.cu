@@ -59,15 +59,9 @@ int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const s
     }
     SB_CUDA(cudaSetDevice(c->device));
     cudaStream_t st = c->stream;
-    // PCM span of this batch -> device
-    const float* d_pcm = pcm + lo;
-    if (!pcm_on_device) {
-        SB_CUDA(c->pcm_stage.ensure(sizeof(float) * (size_t)(hi - lo)));
-        SB_CUDA(cudaMemcpyAsync(c->pcm_stage.p, pcm + lo, sizeof(float) * (size_t)(hi - lo), cudaMemcpyHostToDevice, st));
-        d_pcm = c->pcm_stage.as<float>();
-    }
     std::vector<int64_t> start(n_tasks), len(n_tasks), fo(n_tasks + 1), eo(n_tasks + 1);
     int64_t frames = 0, enc_rows = 0, max_enc = 0;
+    bool ordered = true;  // tasks run left to right through the audio (what the planner produces)
     for (int64_t i = 0; i < n_tasks; ++i) {
         start[i] = tasks[i].audio_start - lo;
         len[i] = tasks[i].audio_end - tasks[i].audio_start;
@@ -76,20 +70,59 @@ int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const s
         const int64_t e = encoder_out_frames((int)t);
         enc_rows += e;
         max_enc = std::max(max_enc, e);
+        if (i > 0 && (tasks[i].audio_start < tasks[i - 1].audio_start || tasks[i].audio_end < tasks[i - 1].audio_end))
+            ordered = false;
     }
     SB_CUDA(c->feat_stage.ensure(sizeof(float) * kMels * (size_t)frames));
     SB_CUDA(c->enc_stage.ensure(sizeof(float) * kDModel * (size_t)enc_rows));
     if (n_tasks > 65535) return fail(SB_INVALID_ARGUMENT, "more than 65535 tasks in one batch");
-    {
-        int32_t s = frontend_run(c, d_pcm, start.data(), len.data(), n_tasks, cfg.preemphasis, true,
-                                 c->feat_stage.as<float>(), fo.data());
-        if (s != SB_OK) return s;
+    // Host PCM goes to the device in pieces on a second stream, so that all but the first piece's copy overlaps the
+    // kernels of the piece before it; frontend and encoder run piece by piece, the decoder once over everything.
+    const float* d_pcm = pcm + lo;
+    int n_pieces = 1;
+    if (!pcm_on_device) {
+        SB_CUDA(c->pcm_stage.ensure(sizeof(float) * (size_t)(hi - lo)));
+        d_pcm = c->pcm_stage.as<float>();
+        if (ordered) n_pieces = (int)std::max<int64_t>(1, std::min<int64_t>(8, n_tasks / 192));
+        if (!c->copy_stream) SB_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+        while ((int)c->copy_events.size() < n_pieces + 1) {
+            cudaEvent_t ev;
+            SB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+            c->copy_events.push_back(ev);
+        }
+        // the staging buffer may still be read by kernels of an earlier call
+        SB_CUDA(cudaEventRecord(c->copy_events[n_pieces], st));
+        SB_CUDA(cudaStreamWaitEvent(c->copy_stream, c->copy_events[n_pieces], 0));
     }
     std::vector<int> eoi(n_tasks + 1);
-    cudaError_t e = encoder_forward(c, *c->model, c->feat_stage.as<float>(), fo.data(), (int)n_tasks,
-                                    c->enc_stage.as<float>(), eoi.data(), *c->enc_ws, c->workspace_budget);
-    SB_CUDA(e);
-    for (int64_t i = 0; i <= n_tasks; ++i) eo[i] = eoi[i];
+    fo[0] = 0;
+    eo[0] = 0;
+    int64_t copied_to = lo;
+    for (int p = 0; p < n_pieces; ++p) {
+        const int64_t i0 = n_tasks * p / n_pieces, i1 = n_tasks * (p + 1) / n_pieces;
+        if (i1 <= i0) continue;
+        if (!pcm_on_device) {
+            const int64_t end = (p == n_pieces - 1) ? hi : tasks[i1 - 1].audio_end;
+            if (end > copied_to)
+                SB_CUDA(cudaMemcpyAsync(c->pcm_stage.as<float>() + (copied_to - lo), pcm + copied_to,
+                                        sizeof(float) * (size_t)(end - copied_to), cudaMemcpyHostToDevice, c->copy_stream));
+            copied_to = std::max(copied_to, end);
+            SB_CUDA(cudaEventRecord(c->copy_events[p], c->copy_stream));
+            SB_CUDA(cudaStreamWaitEvent(st, c->copy_events[p], 0));
+        }
+        std::vector<int64_t> rel(i1 - i0 + 1);
+        int32_t s = frontend_run(c, d_pcm, start.data() + i0, len.data() + i0, i1 - i0, cfg.preemphasis, true,
+                                 c->feat_stage.as<float>() + (size_t)fo[i0] * kMels, rel.data());
+        if (s != SB_OK) return s;
+        for (int64_t k = 1; k <= i1 - i0; ++k) fo[i0 + k] = fo[i0] + rel[k];
+        cudaError_t e = encoder_forward(c, *c->model, c->feat_stage.as<float>() + (size_t)fo[i0] * kMels, rel.data(),
+                                        (int)(i1 - i0), c->enc_stage.as<float>() + (size_t)eo[i0] * kDModel,
+                                        eoi.data() + i0, *c->enc_ws, c->workspace_budget);
+        SB_CUDA(e);
+        // encoder_forward writes offsets relative to its first clip
+        const int64_t ebase = eo[i0];
+        for (int64_t k = 1; k <= i1 - i0; ++k) eo[i0 + k] = ebase + eoi[i0 + k];
+    }
     const int64_t max_tokens = std::max<int64_t>(1, kMaxSymbols * max_enc);
     std::vector<uint32_t> tok((size_t)n_tasks * max_tokens);
     std::vector<int64_t> frm((size_t)n_tasks * max_tokens), dur((size_t)n_tasks * max_tokens), cnt(n_tasks);

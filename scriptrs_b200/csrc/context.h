@@ -58,6 +58,8 @@ struct sb_ctx {
     int device = 0;
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;     // host-to-device PCM pieces, ahead of the kernels that read them
+    std::vector<cudaEvent_t> copy_events;  // one per piece, plus one that orders the copies after earlier work
     int sm_count = 0;
     int64_t launches = 0;
     sb::FrontendTables* d_tables = nullptr;

@@ -29,16 +29,6 @@ namespace sb {
 
 namespace {
 
-__device__ __forceinline__ int find_clip(const int* __restrict__ off, int n, int row) {
-    // largest c with off[c] <= row
-    int lo = 0, hi = n;
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (off[mid] <= row) lo = mid; else hi = mid;
-    }
-    return lo;
-}
-
 // ---------------------------------------------------------------- sub-sampling
 // First two stages in one kernel: 3x3 stride-2 convolution of the mel image (1 -> 256 channels, ReLU) followed by
 // the 3x3 stride-2 depthwise convolution, without the [T/2 x 64 x 256] intermediate ever reaching memory.
@@ -132,59 +122,69 @@ sub_conv0_dw1_kernel(const float* __restrict__ feats, const int64_t* __restrict_
     }
 }
 
-// in bf16 [sum Tin x Fin x 256] -> out bf16 [sum Tout x Fin/2 x 256]; one CTA per output time row, 256 threads:
-// a warp covers the 256 channels with 16-byte loads (8 channels per lane), the 8 warps share the frequency
-// positions.  w is tap-major [9 x 256].
+// Depthwise 3x3 stride-2 stage: in bf16 [sum Tin x Fin x 256] -> out bf16 [sum Tout x Fin/2 x 256], channels last.
+// grid (ceil(max Tout / (2 TO)), clips), 256 threads: each half of the CTA produces TO output time rows, a thread
+// owns two channels (4-byte loads, a warp reads 128 contiguous bytes) and walks the output frequencies with a
+// sliding window: per step it loads the two new input columns of the 2 TO + 1 rows it needs and reuses the column
+// carried over from the previous step.  w is tap-major [9 x 256].
+template <int TO>
 __global__ void __launch_bounds__(256)
-sub_dw_kernel(const bf16* __restrict__ in, const int* __restrict__ tin_off, const int* __restrict__ tout_off,
-              int n_clips, int fin, const float* __restrict__ w, const float* __restrict__ b, bf16* __restrict__ out) {
-    const int go = blockIdx.x;
-    const int clip = find_clip(tout_off, n_clips, go);
-    const int to = go - tout_off[clip];
+sub_dw_kernel(const bf16* __restrict__ in, const int* __restrict__ tin_off, const int* __restrict__ tout_off, int fin,
+              const float* __restrict__ w, const float* __restrict__ b, bf16* __restrict__ out) {
+    constexpr int NR = 2 * TO + 1;
+    const int clip = blockIdx.y;
+    const int out_base = tout_off[clip];
+    const int Tout = tout_off[clip + 1] - out_base;
+    const int to0 = (blockIdx.x * 2 + (threadIdx.x >> 7)) * TO;
+    if (to0 >= Tout) return;
     const int in_base = tin_off[clip];
     const int Tin = tin_off[clip + 1] - in_base;
     const int fout = fin >> 1;
-    const int c = (threadIdx.x & 31) * 8, wgrp = threadIdx.x >> 5;
-    float wt[9][8], bias[8];
+    const int cp = (threadIdx.x & 127) * 2;
+    float2 wt[9];
 #pragma unroll
-    for (int i = 0; i < 9; ++i) {
-        const float4 w0 = *reinterpret_cast<const float4*>(w + i * kSubC + c);
-        const float4 w1 = *reinterpret_cast<const float4*>(w + i * kSubC + c + 4);
-        wt[i][0] = w0.x; wt[i][1] = w0.y; wt[i][2] = w0.z; wt[i][3] = w0.w;
-        wt[i][4] = w1.x; wt[i][5] = w1.y; wt[i][6] = w1.z; wt[i][7] = w1.w;
+    for (int i = 0; i < 9; ++i) wt[i] = *reinterpret_cast<const float2*>(w + i * kSubC + cp);
+    const float2 bias = *reinterpret_cast<const float2*>(b + cp);
+    const __nv_bfloat162* rowp[NR];
+    bool rok[NR];
+    float2 carry[NR];
+#pragma unroll
+    for (int k = 0; k < NR; ++k) {
+        const int r = 2 * to0 - 1 + k;
+        rok[k] = r >= 0 && r < Tin;
+        rowp[k] = reinterpret_cast<const __nv_bfloat162*>(in + (size_t)(in_base + (rok[k] ? r : 0)) * fin * kSubC + cp);
+        carry[k] = make_float2(0.0f, 0.0f);  // input column -1
     }
+    const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.0f, 0.0f);
+#pragma unroll 2
+    for (int fo = 0; fo < fout; ++fo) {
+        float2 ca[NR], cb[NR];  // input columns 2 fo and 2 fo + 1
 #pragma unroll
-    for (int e = 0; e < 8; ++e) bias[e] = b[c + e];
-    for (int fo = wgrp; fo < fout; fo += 8) {
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = bias[e];
-#pragma unroll
-        for (int dt = 0; dt < 3; ++dt) {
-            const int r = 2 * to - 1 + dt;
-            if (r < 0 || r >= Tin) continue;
-#pragma unroll
-            for (int df = 0; df < 3; ++df) {
-                const int f = 2 * fo - 1 + df;
-                if (f < 0 || f >= fin) continue;
-                const uint4 raw = *reinterpret_cast<const uint4*>(in + ((size_t)(in_base + r) * fin + f) * kSubC + c);
-                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 v = __bfloat1622float2(h2[e]);
-                    acc[2 * e] = fmaf(wt[dt * 3 + df][2 * e], v.x, acc[2 * e]);
-                    acc[2 * e + 1] = fmaf(wt[dt * 3 + df][2 * e + 1], v.y, acc[2 * e + 1]);
-                }
-            }
+        for (int k = 0; k < NR; ++k) {
+            const __nv_bfloat162 va = rok[k] ? __ldg(rowp[k] + (size_t)(2 * fo) * (kSubC / 2)) : zero2;
+            const __nv_bfloat162 vb = rok[k] ? __ldg(rowp[k] + (size_t)(2 * fo + 1) * (kSubC / 2)) : zero2;
+            ca[k] = __bfloat1622float2(va);
+            cb[k] = __bfloat1622float2(vb);
         }
-        uint4 pk;
-        __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[0], acc[1]), p1 = __floats2bfloat162_rn(acc[2], acc[3]);
-        __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[4], acc[5]), p3 = __floats2bfloat162_rn(acc[6], acc[7]);
-        pk.x = *reinterpret_cast<uint32_t*>(&p0);
-        pk.y = *reinterpret_cast<uint32_t*>(&p1);
-        pk.z = *reinterpret_cast<uint32_t*>(&p2);
-        pk.w = *reinterpret_cast<uint32_t*>(&p3);
-        *reinterpret_cast<uint4*>(out + ((size_t)go * fout + fo) * kSubC + c) = pk;
+#pragma unroll
+        for (int j = 0; j < TO; ++j) {
+            float2 acc = bias;
+#pragma unroll
+            for (int dt = 0; dt < 3; ++dt) {
+                const int k = 2 * j + dt;
+                acc.x = fmaf(wt[dt * 3 + 0].x, carry[k].x, acc.x);
+                acc.y = fmaf(wt[dt * 3 + 0].y, carry[k].y, acc.y);
+                acc.x = fmaf(wt[dt * 3 + 1].x, ca[k].x, acc.x);
+                acc.y = fmaf(wt[dt * 3 + 1].y, ca[k].y, acc.y);
+                acc.x = fmaf(wt[dt * 3 + 2].x, cb[k].x, acc.x);
+                acc.y = fmaf(wt[dt * 3 + 2].y, cb[k].y, acc.y);
+            }
+            if (to0 + j < Tout)
+                *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)(out_base + to0 + j) * fout + fo) * kSubC + cp) =
+                    __floats2bfloat162_rn(acc.x, acc.y);
+        }
+#pragma unroll
+        for (int k = 0; k < NR; ++k) carry[k] = cb[k];
     }
 }
 
@@ -620,7 +620,8 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
         c->launches += 1;
     }
     ENC_CUDA(run_gemm(c, "gemm_sub_pw", ws.y1.p, m.pw1_w, m.pw1_b, ws.y2.p, R2 * 32, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
-    PROF("sub_dw2", (sub_dw_kernel<<<R3, 256, 0, st>>>(ws.y2.as<bf16>(), d_t2, d_t3, n, 32, m.dw2_w, m.dw2_b, ws.y3.as<bf16>())));
+    PROF("sub_dw2", (sub_dw_kernel<2><<<dim3((max_t3 + 3) / 4, n), 256, 0, st>>>(ws.y2.as<bf16>(), d_t2, d_t3, 32, m.dw2_w, m.dw2_b,
+                                                                                ws.y3.as<bf16>())));
     c->launches += 1;
     ENC_CUDA(run_gemm(c, "gemm_sub_pw", ws.y3.p, m.pw2_w, m.pw2_b, ws.y4.p, R3 * 16, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));
     float* x = ws.x.as<float>();

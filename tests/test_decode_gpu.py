@@ -104,3 +104,21 @@ def test_max_tokens_overflow_is_reported(ctx, weights):
     with pytest.raises(sb.ScriptrsError) as e:
         sb.tdt_decode_device(ctx, enc.data_ptr(), np.array([0, 50], np.int64), max_tokens=2)
     assert e.value.status == 12
+
+
+def test_many_sequences_span_several_gemm_tiles(ctx, weights, decode_path):
+    """300 ragged sequences: more than two 128-row tiles of the tensor-core products, and the wide-tile launch
+    of the fp32 kernel; every sequence must equal its own replay and what it gives when decoded alone."""
+    rng = np.random.default_rng(77)
+    lens = rng.integers(1, 40, size=300)
+    encs = [rng.standard_normal((int(t), 1024)).astype(np.float32) for t in lens]
+    got = decode_gpu(ctx, encs)
+    for g, t in zip(got, lens):
+        rep = oracle.greedy_replay(g["logits"], time_steps=int(t))
+        assert rep["steps"] == g["steps"]
+        for k in ("tokens", "frames", "durations"):
+            assert np.array_equal(rep[k], g[k])
+    for i in (0, 131, 299):
+        alone = decode_gpu(ctx, [encs[i]], trace=False)[0]
+        for k in ("tokens", "frames", "durations", "conf"):
+            assert np.array_equal(alone[k], got[i][k])

@@ -122,3 +122,25 @@ def test_worker_count_does_not_change_the_result(ctx, pipe):
     a = lf.run_with_config(audio, sb.LongFormConfig(worker_count=1))
     b = lf.run_with_config(audio, sb.LongFormConfig(worker_count=8))
     assert a.text == b.text and a.tokens == b.tokens
+
+
+def test_pieced_host_copy_equals_resident_path(ctx, pipe):
+    """More than 384 ordered tasks: the host PCM goes up in pieces on a copy stream under the kernels; the token
+    streams must equal those of the same tasks over a device-resident buffer (single piece).  Short tasks keep
+    the 2-block encoder cheap."""
+    import scriptrs_b200 as sb
+
+    n_tasks, task_len, stride = 400, 4000, 3000
+    audio = synth.long_audio(stride * (n_tasks - 1) + task_len, 17)
+    tasks = [(i * stride, i * stride + task_len, i * stride, 0) for i in range(n_tasks)]
+    host = sb.transcribe_chunks(ctx, audio, tasks)
+    d_audio = torch.from_numpy(audio).cuda()
+    torch.cuda.synchronize()
+    dev = sb.transcribe_chunks(ctx, None, tasks, audio_ptr=d_audio.data_ptr(), n_samples=audio.size, on_device=True)
+    for x, y in zip(host.flat(), dev.flat()):
+        assert np.array_equal(x, y)
+    # unordered tasks fall back to one copy and must still give each task its own result
+    perm = list(reversed(range(n_tasks)))
+    shuffled = sb.transcribe_chunks(ctx, audio, [tasks[i] for i in perm])
+    for k in (0, 57, n_tasks - 1):
+        assert np.array_equal(shuffled[k].token_ids, host[perm[k]].token_ids)
