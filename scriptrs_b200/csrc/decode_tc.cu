@@ -100,8 +100,9 @@ dec_init_kernel(const float* __restrict__ embedding, bf16* __restrict__ a0, int 
 // h' = s(o) tanh(c').  Layer 0 also writes the next product's input [h0' | h1], layer 1 writes [h1'].
 template <int LAYER>
 __global__ void __launch_bounds__(256)
-dec_cell_kernel(const float* __restrict__ gates, DecodeState s, bf16* __restrict__ a_next) {
+dec_cell_kernel(const float* __restrict__ gates, DecodeState s, bf16* __restrict__ a_next, int* __restrict__ step_counter) {
     const int b = blockIdx.x;
+    if (LAYER == 0 && b == 0 && threadIdx.x == 0) *step_counter += 1;  // one iteration = one pass through these kernels
     const size_t BH = (size_t)s.n_seq * kH;
     const float* g = gates + (size_t)b * 4 * kH;
     for (int u = threadIdx.x; u < kH; u += 256) {
@@ -133,11 +134,11 @@ dec_joint_in_kernel(DecodeState s, bf16* __restrict__ a3) {
 }
 
 // One CTA per sequence: arg-max, confidence, record, commit, advance (src/model.rs:79-90,180-209), then the next
-// iteration's first predictor input [emb(last_token) | h0].  `alive` receives step + 1 if any sequence still has
-// frames left after this step.
+// iteration's first predictor input [emb(last_token) | h0].  `alive` receives the number of iterations run so far
+// (step_counter, advanced by the first cell kernel of the iteration) if any sequence still has frames left.
 __global__ void __launch_bounds__(256)
 dec_decide_kernel(DecodeState s, const float* __restrict__ embedding, const float* __restrict__ logits, int ld_logits,
-                  bf16* __restrict__ a0, int step, int* __restrict__ alive) {
+                  bf16* __restrict__ a0, const int* __restrict__ step_counter, int* __restrict__ alive) {
     __shared__ float redf[16];
     __shared__ int redi[8];
     const int b = blockIdx.x;
@@ -225,7 +226,7 @@ dec_decide_kernel(DecodeState s, const float* __restrict__ embedding, const floa
         s.frame_idx[b] = nf;
         s.emitted[b] = emitted;
         s.n_steps[b] = nsteps + 1;
-        if (nf < s.enc_len[b]) *alive = step + 1;  // every writer of a step stores the same value
+        if (nf < s.enc_len[b]) *alive = *step_counter;  // every writer of a step stores the same value
     }
 }
 
@@ -292,8 +293,10 @@ cudaError_t decode_tc_enc_projection(const DecodeTcWeights& t, const float* d_en
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-// Runs the greedy loop for s.n_seq sequences.  The host launches `check_every` steps at a time and then reads the
-// `alive` word; steps launched after the last sequence finished find nothing to do.
+// Runs the greedy loop for s.n_seq sequences.  One iteration (four products, four element-wise kernels) is
+// captured into a CUDA graph once per call and replayed; the host launches `check_every` iterations at a time and
+// then reads the `alive` word (d_alive[0]; d_alive[1] is the device-side iteration counter).  Iterations launched
+// after the last sequence finished find nothing to do.
 cudaError_t decode_tc_run(const DecodeWeights& w, const DecodeTcWeights& t, const DecodeState& s, int max_steps,
                           void* scratch_after_enc, int* d_alive, int sm_count, int* d_error, int64_t* launches,
                           cudaStream_t st) {
@@ -304,35 +307,56 @@ cudaError_t decode_tc_run(const DecodeWeights& w, const DecodeTcWeights& t, cons
     bf16* a3 = a2 + (size_t)B * 3 * kH;
     float* gates = reinterpret_cast<float*>(a3 + (size_t)B * 3 * kJointDim);
     float* logits = gates + (size_t)B * 4 * kH;
-    cudaError_t e = cudaMemsetAsync(d_alive, 0, sizeof(int), st);
+    int* d_step = d_alive + 1;
+    cudaError_t e = cudaMemsetAsync(d_alive, 0, 2 * sizeof(int), st);
     if (e != cudaSuccess) return e;
     dec_init_kernel<<<B, 256, 0, st>>>(w.embedding, a0, B);
     *launches += 1;
+
+    auto iteration = [&]() -> cudaError_t {
+        cudaError_t r = gemm_f32(a0, t.w0, w.b_gates, gates, B, 4 * kH, 3 * 2 * kH, sm_count, d_error, st);
+        if (r != cudaSuccess) return r;
+        dec_cell_kernel<0><<<B, 256, 0, st>>>(gates, s, a1, d_step);
+        r = gemm_f32(a1, t.w1, w.b_gates + 4 * kH, gates, B, 4 * kH, 3 * 2 * kH, sm_count, d_error, st);
+        if (r != cudaSuccess) return r;
+        dec_cell_kernel<1><<<B, 256, 0, st>>>(gates, s, a2, d_step);
+        r = gemm_f32(a2, t.wp, w.b_pred, s.pred, B, kJointDim, 3 * kH, sm_count, d_error, st);
+        if (r != cudaSuccess) return r;
+        dec_joint_in_kernel<<<B, 256, 0, st>>>(s, a3);
+        r = gemm_f32(a3, t.wo, t.b_out, logits, B, kOutPad, 3 * kJointDim, sm_count, d_error, st);
+        if (r != cudaSuccess) return r;
+        dec_decide_kernel<<<B, 256, 0, st>>>(s, w.embedding, logits, kOutPad, a0, d_step, d_alive);
+        return cudaGetLastError();
+    };
+
+    // capture one iteration; on any capture problem fall back to plain launches
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+        const cudaError_t ce = iteration();
+        const cudaError_t ee = cudaStreamEndCapture(st, &graph);
+        if (ce != cudaSuccess || ee != cudaSuccess || !graph ||
+            cudaGraphInstantiate(&exec, graph, nullptr, nullptr, 0) != cudaSuccess)
+            exec = nullptr;
+    }
+    (void)cudaGetLastError();  // a failed capture leaves a sticky-free error code behind
+
     constexpr int check_every = 8;
     int h_alive = 0;
     for (int step = 0; step < max_steps; ++step) {
-        e = gemm_f32(a0, t.w0, w.b_gates, gates, B, 4 * kH, 3 * 2 * kH, sm_count, d_error, st);
-        if (e != cudaSuccess) return e;
-        dec_cell_kernel<0><<<B, 256, 0, st>>>(gates, s, a1);
-        e = gemm_f32(a1, t.w1, w.b_gates + 4 * kH, gates, B, 4 * kH, 3 * 2 * kH, sm_count, d_error, st);
-        if (e != cudaSuccess) return e;
-        dec_cell_kernel<1><<<B, 256, 0, st>>>(gates, s, a2);
-        e = gemm_f32(a2, t.wp, w.b_pred, s.pred, B, kJointDim, 3 * kH, sm_count, d_error, st);
-        if (e != cudaSuccess) return e;
-        dec_joint_in_kernel<<<B, 256, 0, st>>>(s, a3);
-        e = gemm_f32(a3, t.wo, t.b_out, logits, B, kOutPad, 3 * kJointDim, sm_count, d_error, st);
-        if (e != cudaSuccess) return e;
-        dec_decide_kernel<<<B, 256, 0, st>>>(s, w.embedding, logits, kOutPad, a0, step, d_alive);
+        e = exec ? cudaGraphLaunch(exec, st) : iteration();
+        if (e != cudaSuccess) break;
         *launches += 8;
         if ((step + 1) % check_every == 0 || step + 1 == max_steps) {
             e = cudaMemcpyAsync(&h_alive, d_alive, sizeof(int), cudaMemcpyDeviceToHost, st);
-            if (e != cudaSuccess) return e;
-            e = cudaStreamSynchronize(st);
-            if (e != cudaSuccess) return e;
-            if (h_alive < step + 1) break;  // no sequence had frames left after the last launched step
+            if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+            if (e != cudaSuccess) break;
+            if (h_alive < step + 1) break;  // no sequence had frames left after the last launched iteration
         }
     }
-    return cudaGetLastError();
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace sb
