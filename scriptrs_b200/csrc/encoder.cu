@@ -699,7 +699,7 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
                                               h, d_t3, L.pos_proj, L.bias_u, L.bias_v, att)));
         } else {
             c->prof.begin("relpos_attention_tc", st);
-            ENC_CUDA(attention_launch(h, R3, d_t3, n, L.pos_proj, L.bias_u, L.pos_vp, att, c->d_error, st));
+            ENC_CUDA(attention_launch(h, R3, d_t3, n, L.pos_proj, L.bias_u, L.pos_vp, att, c->sm_count, c->d_error, st));
             c->prof.end(st);
             c->launches += 1;
         }
