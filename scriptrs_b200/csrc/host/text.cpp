@@ -12,6 +12,7 @@
 #include <cstdio>
 #include <fstream>
 #include <sstream>
+#include <utility>
 
 #include "longform.h"
 
@@ -171,6 +172,8 @@ TranscriptionResult decode_tokens(const Vocabulary& vocab, const RawTokens& raw,
     res.duration_seconds = duration_seconds;
     if (raw.token_ids.empty()) return res;
     std::string text;
+    res.tokens.reserve(raw.token_ids.size());
+    text.reserve(raw.token_ids.size() * 4);
     for (size_t index = 0; index < raw.token_ids.size(); ++index) {
         const uint32_t id = raw.token_ids[index];
         if (id >= vocab.id_to_token.size()) continue;
@@ -184,7 +187,7 @@ TranscriptionResult decode_tokens(const Vocabulary& vocab, const RawTokens& raw,
         if (needs_digit_spacing(text, display)) display.insert(display.begin(), ' ');
         text += display;
         const float conf = index < raw.confidences.size() ? raw.confidences[index] : 0.0f;
-        res.tokens.push_back(TimedToken{id, display, start, end, conf});
+        res.tokens.push_back(TimedToken{id, std::move(display), start, end, conf});
     }
     res.text = trim(text);
     if (!res.text.empty() && !res.tokens.empty())
@@ -197,6 +200,7 @@ TranscriptionResult long_form_result(std::vector<TimedToken> tokens, int64_t aud
     res.duration_seconds = static_cast<double>(audio_len) / 16000.0;
     if (!tokens.empty()) {
         std::string joined;
+        joined.reserve(tokens.size() * 4);
         for (const auto& t : tokens) joined += t.text;
         res.chunks.push_back(TranscriptChunk{tokens.front().start, tokens.back().end, trim(joined)});
         res.tokens = std::move(tokens);
