@@ -7,12 +7,12 @@
 // projections run as tcgen05 GEMMs over the packed rows (gemm.cu); the kernels in this file
 // cover what is not a GEMM and respect clip boundaries.
 //
-//   sub_conv0_kernel     conv2d(1 -> 256, k3, s2, p1) + ReLU, channels-last bf16 output
-//   sub_dw_kernel        depthwise conv2d(k3, s2, p1) + bias (feeds the pointwise GEMM)
+//   sub_conv0_dw1_kernel conv2d(1 -> 256, k3, s2, p1) + ReLU fused with the first depthwise conv2d(k3, s2, p1)
+//   sub_dw_kernel        second depthwise conv2d(k3, s2, p1) + bias (feeds the pointwise GEMM)
 //   layernorm_kernel     one warp per 1024-wide row, fp32 statistics, bf16 or f32 output
 //   relpos_attention_kernel  per (clip, head): scores = ((q + u) k^T + (q + v) p^T[i - j]) / sqrt(128),
 //                        softmax, PV; the relative shift is index arithmetic, never materialised
-//   glu_dwconv_kernel    GLU + depthwise conv k = 9 ('same' within the clip) + folded BatchNorm + SiLU
+//   dwconv_kernel        depthwise conv k = 9 ('same' within the clip) + folded BatchNorm + SiLU (GLU: GEMM epilogue)
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -441,15 +441,16 @@ relpos_attention_kernel(const bf16* __restrict__ qkv, const int* __restrict__ t3
 constexpr size_t kAttSmemBytes = ((size_t)(2 * kMaxEncFrames + kPosRows) * kRowStride) * sizeof(bf16) +
                                  (size_t)(kAttThreads / 32) * (2 * kHeadDim + 192) * sizeof(float);
 
-// ---------------------------------------------------------------- GLU + depthwise conv + BN + SiLU
-// in bf16 [rows x 2048] -> out bf16 [rows x 1024].  grid (time blocks of 32, clips, 4 channel blocks of 256).
-// Phase 1: 16-byte loads of the value and gate halves, GLU, fp32 tile [40 rows x 256 channels] in shared
-// memory (zero outside the clip).  Phase 2: each thread convolves two channels over 16 rows.
+// ---------------------------------------------------------------- depthwise conv + BN + SiLU
+// in bf16 [rows x 1024] (the GLU is applied by the epilogue of the first pointwise GEMM) -> out bf16 [rows x 1024].
+// grid (time blocks of 32, clips, 4 channel blocks of 256).  Phase 1: 16-byte loads into an fp32 tile
+// [40 rows x 256 channels] in shared memory (zero outside the clip).  Phase 2: each thread convolves two channels
+// over 16 rows.
 constexpr int kDwRows = 32;
 constexpr int kDwHalo = (kConvK - 1) / 2;
 constexpr int kDwTileRows = kDwRows + kConvK - 1;
 __global__ void __launch_bounds__(256)
-glu_dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, const float* __restrict__ w,
+dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, const float* __restrict__ w,
                   const float* __restrict__ b, bf16* __restrict__ out) {
     __shared__ __align__(16) float tile[kDwTileRows][256];
     const int clip = blockIdx.y;
@@ -463,16 +464,13 @@ glu_dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, c
         const int tt = tb - kDwHalo + r;
         float g[8];
         if (tt >= 0 && tt < t) {
-            const bf16* p = in + (size_t)(r0 + tt) * (2 * kDModel) + c0 + v8;
-            const uint4 av = *reinterpret_cast<const uint4*>(p);
-            const uint4 gv = *reinterpret_cast<const uint4*>(p + kDModel);
+            const uint4 av = *reinterpret_cast<const uint4*>(in + (size_t)(r0 + tt) * kDModel + c0 + v8);
             const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
-            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float2 af = __bfloat1622float2(a2[e]), gf = __bfloat1622float2(g2[e]);
-                g[2 * e] = __fdividef(af.x, 1.0f + __expf(-gf.x));
-                g[2 * e + 1] = __fdividef(af.y, 1.0f + __expf(-gf.y));
+                const float2 af = __bfloat1622float2(a2[e]);
+                g[2 * e] = af.x;
+                g[2 * e + 1] = af.y;
             }
         } else {
 #pragma unroll
@@ -512,8 +510,8 @@ glu_dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, c
 cudaError_t run_gemm(sb_ctx* c, const char* label, const void* a, const bf16* w, const float* bias, void* out, int M, int N,
                      int K, int act, int mode, float alpha) {
     GemmArgs g{};
-    g.a = a; g.w = w; g.bias = bias; g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = N; g.act = act; g.out_mode = mode;
-    g.alpha = alpha; g.fp8 = false;
+    g.a = a; g.w = w; g.bias = bias; g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = act == kActGlu ? N / 2 : N; g.act = act;
+    g.out_mode = mode; g.alpha = alpha; g.fp8 = false;
     c->launches += 1;
     c->prof.begin(label, c->stream);
     cudaError_t e = gemm_launch(g, c->sm_count, c->d_error, c->stream);
@@ -526,7 +524,7 @@ cudaError_t run_gemm_fp8(sb_ctx* c, const char* label, const uint8_t* a, const f
                          float alpha, const float* out_row_scale = nullptr) {
     GemmArgs g{};
     g.a = a; g.w = w; g.bias = bias; g.row_scale = a_scale; g.col_scale = w_scale; g.out = out; g.M = M; g.N = N; g.K = K;
-    g.ldo = N; g.act = act; g.out_mode = mode; g.alpha = alpha; g.fp8 = true; g.out_row_scale = out_row_scale;
+    g.ldo = act == kActGlu ? N / 2 : N; g.act = act; g.out_mode = mode; g.alpha = alpha; g.fp8 = true; g.out_row_scale = out_row_scale;
     c->launches += 1;
     c->prof.begin(label, c->stream);
     cudaError_t e = gemm_launch(g, c->sm_count, c->d_error, c->stream);
@@ -672,13 +670,13 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     };
     // LayerNorm followed by a projection to bf16 (QKV, first pointwise conv)
     auto norm_project = [&](const char* label, const char* label8, const float* g, const float* b, const bf16* w,
-                            const uint8_t* wq, const float* wsc, const float* bias, int N) -> cudaError_t {
+                            const uint8_t* wq, const float* wsc, const float* bias, int N, int act) -> cudaError_t {
         if (fp8 && (c->fp8_mask & (N == 3 * kDModel ? 4 : 8))) {
             PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, nullptr, nullptr, g, b, a8, rs_a, R3, nullptr, 0.0f, 0.0f)));
-            ENC_CUDA(run_gemm_fp8(c, label8, a8, rs_a, wq, wsc, bias, h, R3, N, kDModel, kActNone, kOutBf16, 1.0f));
+            ENC_CUDA(run_gemm_fp8(c, label8, a8, rs_a, wq, wsc, bias, h, R3, N, kDModel, act, kOutBf16, 1.0f));
         } else {
             PROF("layernorm", (layernorm_kernel<false><<<ln_grid, 256, 0, st>>>(x, nullptr, nullptr, g, b, a, R3)));
-            ENC_CUDA(run_gemm(c, label, a, w, bias, h, R3, N, kDModel, kActNone, kOutBf16, 1.0f));
+            ENC_CUDA(run_gemm(c, label, a, w, bias, h, R3, N, kDModel, act, kOutBf16, 1.0f));
         }
         c->launches += 1;
         return cudaSuccess;
@@ -693,7 +691,7 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
                               L.ff1_w2_s, L.ff1_b2, L.ff1_wn, L.ff1_bmax));
         // x += MHA(LN x)
         ENC_CUDA(norm_project("gemm_qkv", "gemm_qkv_fp8", L.ln_att_g, L.ln_att_b, L.qkv_w, L.qkv_w_q, L.qkv_w_s, L.qkv_b,
-                              3 * kDModel));
+                              3 * kDModel, kActNone));
         if (c->simt_attention) {
             PROF("relpos_attention_simt", (relpos_attention_kernel<<<dim3(kHeads, n), kAttThreads, kAttSmemBytes, st>>>(
                                               h, d_t3, L.pos_proj, L.bias_u, L.bias_v, att)));
@@ -706,8 +704,8 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
         ENC_CUDA(run_gemm(c, "gemm_attn_out", att, L.o_w, L.o_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
         // x += Conv(LN x)
         ENC_CUDA(norm_project("gemm_conv_pw1", "gemm_conv_pw1_fp8", L.ln_conv_g, L.ln_conv_b, L.pw1_w, L.pw1_w_q,
-                              L.pw1_w_s, L.pw1_b, 2 * kDModel));
-        PROF("glu_dwconv", (glu_dwconv_kernel<<<dim3((max_t3 + kDwRows - 1) / kDwRows, n, kDModel / 256), 256, 0, st>>>(
+                              L.pw1_w_s, L.pw1_b, 2 * kDModel, kActGlu));  // h = GLU(W1 LN(x) + b1), [rows x 1024]
+        PROF("dwconv", (dwconv_kernel<<<dim3((max_t3 + kDwRows - 1) / kDwRows, n, kDModel / 256), 256, 0, st>>>(
                                h, d_t3, L.dw_w, L.dw_b, att)));
         ENC_CUDA(run_gemm(c, "gemm_conv_pw2", att, L.pw2_w, L.pw2_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
         // x += 0.5 * FF2(LN x)
@@ -720,7 +718,7 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
             PROF("layernorm", (layernorm_kernel<true><<<ln_grid, 256, 0, st>>>(x, nullptr, nullptr, L.ln_out_g, L.ln_out_b, dst, R3)));
             c->launches += 1;
         }
-        c->launches += 1;  // GLU + depthwise convolution
+        c->launches += 1;  // depthwise convolution
     }
     if (m.layers == 0)
         ENC_CUDA(cudaMemcpyAsync(d_out + (size_t)enc_off_all[c0] * kDModel, x, (size_t)R3 * kDModel * sizeof(float),

@@ -189,7 +189,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         unsigned char* slab_ptr = base_ptr + S * C::kStageBytes + ew * kSlabBytes;
         const bool out_bf16 = ep.out_mode == kOutBf16;
         const bool out_fp8 = ep.out_mode == kOutFp8;
-        const int slab_cols = out_fp8 ? 128 : (out_bf16 ? 64 : 32);  // 128 bytes per row in every mode
+        const bool glu = ep.act == kActGlu;
+        // accumulator columns per slab: 128 bytes per output row in every mode
+        const int slab_cols = (out_fp8 || glu) ? 128 : (out_bf16 ? 64 : 32);
         const int sw = lane & 7;
         uint32_t lt = 0;
         bool ok = true;
@@ -239,7 +241,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 #pragma unroll
                         for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
                     }
-                    if (out_fp8) {
+                    if (glu) {
+                        // 32 accumulator columns = 16 values and their 16 gates -> 16 outputs = 32 bytes
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            float y[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                y[e] = __fdividef(x[8 * q + e], 1.0f + __expf(-x[16 + 8 * q + e]));
+                            uint4 pk;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(y[4], y[5]), p3 = __floats2bfloat162_rn(y[6], y[7]);
+                            pk.x = *reinterpret_cast<uint32_t*>(&p0);
+                            pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&p2);
+                            pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                            const int ch = 2 * sub + q;
+                            *reinterpret_cast<uint4*>(slab_ptr + lane * 128 + ((ch ^ sw) << 4)) = pk;
+                        }
+                    } else if (out_fp8) {
                         // 32 columns = 32 bytes = chunks 2*sub, 2*sub + 1 of this row
 #pragma unroll
                         for (int q = 0; q < 2; ++q) {
@@ -282,7 +302,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                 __syncwarp();
                 if (lane == 0) {
                     if (ep.out_mode == kOutResidual) tma_reduce_add_2d(&tma_out, slab, n0 + c, m0 + quad * 32);
-                    else tma_store_2d(&tma_out, slab, n0 + c, m0 + quad * 32);
+                    else tma_store_2d(&tma_out, slab, glu ? (n0 + c) >> 1 : n0 + c, m0 + quad * 32);
                     bulk_commit();
                 }
             }
@@ -327,7 +347,7 @@ cudaError_t launch_t(const GemmArgs& g, int sm_count, int* d_error, cudaStream_t
     const CUtensorMapDataType out_dt = o8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                           : (ob ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
     if (!make_map(&ma, g.a, g.M, g.K, g.K, in_dt, eb, kBM) || !make_map(&mb, g.w, g.N, g.K, g.K, in_dt, eb, BN) ||
-        !make_map(&mo, g.out, g.M, g.N, g.ldo, out_dt, o8 ? 1 : (ob ? 2 : 4), 32))
+        !make_map(&mo, g.out, g.M, g.act == kActGlu ? g.N / 2 : g.N, g.ldo, out_dt, o8 ? 1 : (ob ? 2 : 4), 32))
         return cudaErrorInvalidValue;
     EpiParams ep{g.bias, g.row_scale, g.col_scale, g.out_row_scale, g.out, g.M, g.N, g.K, g.ldo, g.act, g.out_mode, g.alpha};
     const int tiles = ((g.M + kBM - 1) / kBM) * (g.N / BN);
@@ -374,7 +394,8 @@ cudaError_t gemm_launch(const GemmArgs& g, int sm_count, int* d_error, cudaStrea
     // BN = 256 when it divides N and still leaves at least one tile per SM; else 128.
     const int m_tiles = (g.M + kBM - 1) / kBM;
     if (g.out_mode == kOutFp8 && (g.N % 256 != 0 || !g.out_row_scale || (g.ldo & 15))) return cudaErrorInvalidValue;
-    const bool wide = (g.N % 256 == 0) && (g.out_mode == kOutFp8 || m_tiles * (g.N / 256) >= sm_count);
+    if (g.act == kActGlu && (g.N % 256 != 0 || g.out_mode != kOutBf16)) return cudaErrorInvalidValue;
+    const bool wide = (g.N % 256 == 0) && (g.out_mode == kOutFp8 || g.act == kActGlu || m_tiles * (g.N / 256) >= sm_count);
     if (g.fp8) return wide ? launch_t<256, true>(g, sm_count, d_error, stream) : launch_t<128, true>(g, sm_count, d_error, stream);
     return wide ? launch_t<256, false>(g, sm_count, d_error, stream) : launch_t<128, false>(g, sm_count, d_error, stream);
 }

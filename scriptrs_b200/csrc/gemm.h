@@ -5,7 +5,9 @@
 
 namespace sb {
 
-enum GemmAct : int { kActNone = 0, kActSilu = 1, kActRelu = 2 };
+// kActGlu: the N accumulator columns are groups of 32 = 16 values followed by their 16 gates; the output has N / 2
+// columns, out[16 g + i] = v[32 g + i] * sigmoid(v[32 g + 16 + i]) (bf16 output, N % 256 == 0).
+enum GemmAct : int { kActNone = 0, kActSilu = 1, kActRelu = 2, kActGlu = 3 };
 enum GemmOut : int {
     kOutBf16 = 0,      // out[M x N] bf16 = act(acc * scales + bias)
     kOutF32 = 1,       // out[M x N] f32  = act(acc * scales + bias) * alpha

@@ -209,7 +209,6 @@ int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensor
                 ld.up_fp8(ld.get(p + "feed_forward1.linear2.weight", d * ff), d, ff, &L.ff1_w2_q, &L.ff1_w2_s);
                 ld.up_fp8(ld.get(p + "feed_forward2.linear1.weight", ff * d), ff, d, &L.ff2_w1_q, &L.ff2_w1_s);
                 ld.up_fp8(ld.get(p + "feed_forward2.linear2.weight", d * ff), d, ff, &L.ff2_w2_q, &L.ff2_w2_s);
-                ld.up_fp8(ld.get(p + "conv.pointwise_conv1.weight", 2 * d * d), 2 * d, d, &L.pw1_w_q, &L.pw1_w_s);
             }
             const float* qw = ld.get(p + "self_attn.q_proj.weight", d * d);
             const float* kw = ld.get(p + "self_attn.k_proj.weight", d * d);
@@ -248,8 +247,25 @@ int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensor
                     if (e != cudaSuccess && ld.err.empty()) ld.err = std::string("position bias failed: ") + cudaGetErrorString(e);
                 }
             }
-            L.pw1_w = ld.b16(p + "conv.pointwise_conv1.weight", 2 * d * d);
-            L.pw1_b = ld.f32(p + "conv.pointwise_conv1.bias", 2 * d);
+            // first pointwise convolution: rows regrouped as [16 value channels | their 16 gate channels] so that the
+            // GEMM epilogue can apply the GLU (value c is row c, its gate row d + c)
+            {
+                const float* w1 = ld.get(p + "conv.pointwise_conv1.weight", 2 * d * d);
+                const float* b1 = ld.get(p + "conv.pointwise_conv1.bias", 2 * d);
+                if (w1 && b1) {
+                    std::vector<float> wp((size_t)2 * d * d), bp((size_t)2 * d);
+                    for (int64_t g16 = 0; g16 < d / 16; ++g16)
+                        for (int64_t i = 0; i < 32; ++i) {
+                            const int64_t src = i < 16 ? 16 * g16 + i : d + 16 * g16 + (i - 16);
+                            const int64_t dst = 32 * g16 + i;
+                            std::memcpy(wp.data() + dst * d, w1 + src * d, sizeof(float) * d);
+                            bp[dst] = b1[src];
+                        }
+                    L.pw1_w = ld.up_bf16(wp.data(), wp.size());
+                    L.pw1_b = ld.up_f32(bp.data(), bp.size());
+                    if (desc->fp8_weights) ld.up_fp8(wp.data(), 2 * d, d, &L.pw1_w_q, &L.pw1_w_s);
+                }
+            }
             L.pw2_w = ld.b16(p + "conv.pointwise_conv2.weight", d * d);
             L.pw2_b = ld.f32(p + "conv.pointwise_conv2.bias", d);
             // fold BatchNorm (eval) into the depthwise taps and bias
