@@ -274,6 +274,7 @@ int32_t sb_ctx_set_option(sb_ctx* c, const char* name, int64_t value) {
     const std::string n(name);
     if (n == "simt_attention") c->simt_attention = value != 0;
     else if (n == "simt_decode") c->simt_decode = value != 0;
+    else if (n == "gemm_pair_tiles") sb::gemm_set_pair_tiles((int)(value < 0 ? 0 : (value > 2 ? 2 : value)));
     else if (n == "fp8") {
         if (value && (!c->model || !c->model->has_fp8))
             return fail(SB_MISSING_MODEL_ASSET, "the model was loaded without fp8 weights");

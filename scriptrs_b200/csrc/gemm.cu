@@ -25,6 +25,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
+
 #include "gemm.h"
 #include "tc_ptx.cuh"
 
@@ -40,21 +42,23 @@ constexpr int kGemmThreads = 320;
 constexpr int kEpiWarps = 8;
 constexpr int kSlabBytes = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes
 
-template <int BN>
+// CTAS = 2: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2); each stages its own 128 rows of A
+// and its own half of the W rows, so a W tile crosses L2 -> SM once per 256 output rows instead of once per 128.
+template <int BN, int CTAS = 1>
 struct Cfg {
-    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kStages = CTAS == 2 ? 6 : (BN == 256 ? 4 : 6);
     static constexpr int kABytes = kBM * kBKBytes;
-    static constexpr int kBBytes = BN * kBKBytes;
+    static constexpr int kBBytes = (BN / CTAS) * kBKBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarBytes = 256;
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiWarps * kSlabBytes + kBarBytes + 1024;  // + alignment slack
 };
 
 // Instruction descriptor: fp32 accumulate, A and B K-major, M = 128, N = BN.
-template <int BN, bool FP8>
+template <int BN, bool FP8, int CTAS = 1>
 __device__ __forceinline__ uint32_t make_idesc() {
     const uint32_t fmt = FP8 ? 0u : 1u;  // kind::f8f6f4: 0 = e4m3; kind::f16: 1 = bf16
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((kBM * CTAS) >> 4) << 24);
 }
 
 __device__ __forceinline__ float apply_act(float x, int act) {
@@ -79,11 +83,13 @@ struct EpiParams {
     float alpha;
 };
 
-template <int BN, bool FP8>
+template <int BN, bool FP8, int CTAS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
             const __grid_constant__ CUtensorMap tma_out, EpiParams ep, int* __restrict__ error) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, CTAS>;
+    // rank of this CTA in its pair (the pair's leader, rank 0, owns the barriers the MMAs wait on)
+    const uint32_t rank = CTAS == 2 ? cluster_ctarank() : 0u;
     constexpr int S = C::kStages;
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -102,10 +108,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m_tiles = (ep.M + kBM - 1) / kBM;
+    constexpr int kTileM = kBM * CTAS;
+    const int m_tiles = (ep.M + kTileM - 1) / kTileM;
     const int n_tiles = ep.N / BN;
     const int num_tiles = m_tiles * n_tiles;
     const int k_tiles = ep.K / (FP8 ? 128 : 64);
+    const int tile0 = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
@@ -114,17 +122,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), kEpiWarps);
+            mbar_init(tempty_bar(a), kEpiWarps * CTAS);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), 2 * BN);
-        tmem_relinquish();
+        if constexpr (CTAS == 2) {
+            tmem_alloc_pair(smem_u32(tmem_slot), 2 * BN);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(tmem_slot), 2 * BN);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync();  // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -133,16 +147,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const int m0 = (t / n_tiles) * kBM, n0 = (t % n_tiles) * BN;
+            for (int t = tile0; t < num_tiles && ok; t += tile_step) {
+                const int m0 = (t / n_tiles) * kTileM + (int)rank * kBM;
+                const int n0 = (t % n_tiles) * BN + (int)rank * (BN / CTAS);
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1;
                     if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(full_bar(s), C::kStageBytes);
                     const int kc = kt * (FP8 ? 128 : 64);
-                    tma_load_2d(a_base + s * C::kABytes, &tma_a, full_bar(s), kc, m0);
-                    tma_load_2d(b_base + s * C::kBBytes, &tma_b, full_bar(s), kc, n0);
+                    if constexpr (CTAS == 2) {
+                        // both CTAs' bytes are counted on the leader's barrier
+                        if (rank == 0) mbar_expect_tx(full_bar(s), 2 * C::kStageBytes);
+                        const uint32_t lead = mapa(full_bar(s), 0);
+                        tma_load_2d_pair(a_base + s * C::kABytes, &tma_a, lead, kc, m0);
+                        tma_load_2d_pair(b_base + s * C::kBBytes, &tma_b, lead, kc, n0);
+                    } else {
+                        mbar_expect_tx(full_bar(s), C::kStageBytes);
+                        tma_load_2d(a_base + s * C::kABytes, &tma_a, full_bar(s), kc, m0);
+                        tma_load_2d(b_base + s * C::kBBytes, &tma_b, full_bar(s), kc, n0);
+                    }
                 }
             }
             if (!ok) {
@@ -153,11 +176,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc<BN, FP8>();
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = make_idesc<BN, FP8, CTAS>();
             uint32_t it = 0, lt = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+            for (int t = tile0; t < num_tiles && ok; t += tile_step, ++lt) {
                 const int acc = lt & 1;
                 const uint32_t acc_ph = (lt >> 1) & 1;
                 if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag)) { ok = false; break; }
@@ -173,11 +196,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         // 32 bytes of K per instruction: +2 in the 16-byte start-address field
-                        tc_mma<FP8>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kt | k) ? 1u : 0u);
+                        if constexpr (CTAS == 2) tc_mma_pair<FP8>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kt | k) ? 1u : 0u);
+                        else tc_mma<FP8>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kt | k) ? 1u : 0u);
                     }
-                    tc_commit(empty_bar(s));
+                    if constexpr (CTAS == 2) {
+                        // the ring slot is free in both CTAs once these MMAs have read it
+                        tc_commit_pair(mapa(empty_bar(s), 0));
+                        tc_commit_pair(mapa(empty_bar(s), 1));
+                    } else {
+                        tc_commit(empty_bar(s));
+                    }
                 }
-                if (ok) tc_commit(tfull_bar(acc));
+                if (ok) {
+                    if constexpr (CTAS == 2) {
+                        tc_commit_pair(mapa(tfull_bar(acc), 0));
+                        tc_commit_pair(mapa(tfull_bar(acc), 1));
+                    } else {
+                        tc_commit(tfull_bar(acc));
+                    }
+                }
             }
         }
     } else {
@@ -195,10 +232,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         const int sw = lane & 7;
         uint32_t lt = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+        for (int t = tile0; t < num_tiles && ok; t += tile_step, ++lt) {
             const int acc = lt & 1;
             const uint32_t acc_ph = (lt >> 1) & 1;
-            const int m0 = (t / n_tiles) * kBM, n0 = (t % n_tiles) * BN;
+            const int m0 = (t / n_tiles) * kTileM + (int)rank * kBM, n0 = (t % n_tiles) * BN;
             if (!mbar_wait(tfull_bar(acc), acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + quad * 32 + lane;
@@ -220,7 +257,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                         // this warp has read its part of the accumulator: hand it back to the MMA warp
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(tempty_bar(acc));
+                        if (lane == 0) {
+                            if constexpr (CTAS == 2) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+                            else mbar_arrive(tempty_bar(acc));
+                        }
                     }
                     const int col0 = n0 + c + 32 * sub;
                     float x[32];
@@ -313,9 +353,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 
     tc_fence_before();
     __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync();  // neither CTA leaves while the other may still touch its memory
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 2 * BN);
+        if constexpr (CTAS == 2) tmem_dealloc_pair(tmem_base, 2 * BN);
+        else tmem_dealloc(tmem_base, 2 * BN);
     }
     if (threadIdx.x == 0 && *abort_flag) atomicExch(error, 1);
 }
@@ -324,6 +366,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
+int g_pair_tiles = 1;  // process-wide: 0 never, 1 where it pays (see gemm_launch), 2 every product large enough
 
 // 2-D row-major tensor [rows x cols] with a row pitch of `pitch_elems`; boxes of 128 bytes x box_rows, 128-byte swizzle.
 bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int pitch_elems, CUtensorMapDataType dt,
@@ -338,7 +381,7 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int pitch_e
     return r == CUDA_SUCCESS;
 }
 
-template <int BN, bool FP8>
+template <int BN, bool FP8, int CTAS>
 cudaError_t launch_t(const GemmArgs& g, int sm_count, int* d_error, cudaStream_t stream) {
     alignas(64) CUtensorMap ma, mb, mo;
     const int eb = FP8 ? 1 : 2;
@@ -346,17 +389,36 @@ cudaError_t launch_t(const GemmArgs& g, int sm_count, int* d_error, cudaStream_t
     const bool ob = g.out_mode == kOutBf16, o8 = g.out_mode == kOutFp8;
     const CUtensorMapDataType out_dt = o8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                           : (ob ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
-    if (!make_map(&ma, g.a, g.M, g.K, g.K, in_dt, eb, kBM) || !make_map(&mb, g.w, g.N, g.K, g.K, in_dt, eb, BN) ||
+    if (!make_map(&ma, g.a, g.M, g.K, g.K, in_dt, eb, kBM) || !make_map(&mb, g.w, g.N, g.K, g.K, in_dt, eb, BN / CTAS) ||
         !make_map(&mo, g.out, g.M, g.act == kActGlu ? g.N / 2 : g.N, g.ldo, out_dt, o8 ? 1 : (ob ? 2 : 4), 32))
         return cudaErrorInvalidValue;
     EpiParams ep{g.bias, g.row_scale, g.col_scale, g.out_row_scale, g.out, g.M, g.N, g.K, g.ldo, g.act, g.out_mode, g.alpha};
-    const int tiles = ((g.M + kBM - 1) / kBM) * (g.N / BN);
-    const int grid = tiles < sm_count ? tiles : sm_count;
-    gemm_kernel<BN, FP8><<<grid, kGemmThreads, Cfg<BN>::kSmemBytes, stream>>>(ma, mb, mo, ep, d_error);
-    return cudaGetLastError();
+    const int tiles = ((g.M + kBM * CTAS - 1) / (kBM * CTAS)) * (g.N / BN);
+    if constexpr (CTAS == 2) {
+        const int pairs = std::min(tiles, sm_count / 2);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * pairs);
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = Cfg<BN, CTAS>::kSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, gemm_kernel<BN, FP8, CTAS>, ma, mb, mo, ep, d_error);
+    } else {
+        const int grid = tiles < sm_count ? tiles : sm_count;
+        gemm_kernel<BN, FP8, CTAS><<<grid, kGemmThreads, Cfg<BN, CTAS>::kSmemBytes, stream>>>(ma, mb, mo, ep, d_error);
+        return cudaGetLastError();
+    }
 }
 
 }  // namespace
+
+void gemm_set_pair_tiles(int mode) { g_pair_tiles = mode; }
 
 cudaError_t gemm_configure(const char** why) {
     if (!g_encode) {
@@ -370,14 +432,15 @@ cudaError_t gemm_configure(const char** why) {
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     cudaError_t e;
-#define SB_SET(BN, F8)                                                                                      \
-    e = cudaFuncSetAttribute(gemm_kernel<BN, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
-                             Cfg<BN>::kSmemBytes);                                                          \
+#define SB_SET(BN, F8, CT)                                                                                  \
+    e = cudaFuncSetAttribute(gemm_kernel<BN, F8, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                             Cfg<BN, CT>::kSmemBytes);                                                      \
     if (e != cudaSuccess) {                                                                                 \
         if (why) *why = "shared-memory opt-in for the GEMM kernel failed";                                  \
         return e;                                                                                           \
     }
-    SB_SET(256, false) SB_SET(128, false) SB_SET(256, true) SB_SET(128, true)
+    SB_SET(256, false, 1) SB_SET(128, false, 1) SB_SET(256, true, 1) SB_SET(128, true, 1)
+    SB_SET(256, false, 2) SB_SET(256, true, 2)
 #undef SB_SET
     return cudaSuccess;
 }
@@ -396,8 +459,18 @@ cudaError_t gemm_launch(const GemmArgs& g, int sm_count, int* d_error, cudaStrea
     if (g.out_mode == kOutFp8 && (g.N % 256 != 0 || !g.out_row_scale || (g.ldo & 15))) return cudaErrorInvalidValue;
     if (g.act == kActGlu && (g.N % 256 != 0 || g.out_mode != kOutBf16)) return cudaErrorInvalidValue;
     const bool wide = (g.N % 256 == 0) && (g.out_mode == kOutFp8 || g.act == kActGlu || m_tiles * (g.N / 256) >= sm_count);
-    if (g.fp8) return wide ? launch_t<256, true>(g, sm_count, d_error, stream) : launch_t<128, true>(g, sm_count, d_error, stream);
-    return wide ? launch_t<256, false>(g, sm_count, d_error, stream) : launch_t<128, false>(g, sm_count, d_error, stream);
+    // Two CTAs per 256 x 256 tile when there is at least one such tile per pair of SMs.  Measured in the 8 h encoder
+    // step against single-CTA tiles: residual-add products -15 % time (their fp32 epilogue leaves L2 little room
+    // for operand traffic), K = 4096 products -9 %, QKV -6 %, the other K = 1024 products unchanged; the K = 256
+    // sub-sampling products are 25 % slower (nothing to amortise), so short K stays on single-CTA tiles.
+    const bool pair = g_pair_tiles && wide && ((g.M + 2 * kBM - 1) / (2 * kBM)) * (g.N / 256) >= sm_count / 2 &&
+                      (g_pair_tiles == 2 || g.K >= 512);
+    if (g.fp8) {
+        if (pair) return launch_t<256, true, 2>(g, sm_count, d_error, stream);
+        return wide ? launch_t<256, true, 1>(g, sm_count, d_error, stream) : launch_t<128, true, 1>(g, sm_count, d_error, stream);
+    }
+    if (pair) return launch_t<256, false, 2>(g, sm_count, d_error, stream);
+    return wide ? launch_t<256, false, 1>(g, sm_count, d_error, stream) : launch_t<128, false, 1>(g, sm_count, d_error, stream);
 }
 
 }  // namespace sb

@@ -31,6 +31,9 @@ struct GemmArgs {
     bool fp8;
 };
 
+// Process-wide switch for two-CTA 256 x 256 tiles: 0 never, 1 for the products that gain from them (default),
+// 2 for every product with at least one such tile per pair of SMs.
+void gemm_set_pair_tiles(int mode);
 // One-time set-up (driver entry point for tensor maps, shared-memory opt-in).
 cudaError_t gemm_configure(const char** why);
 // Launches the tcgen05 GEMM on `stream`.  `d_error` is a device int that the kernel

@@ -17,10 +17,18 @@ def ref_epilogue(acc, bias, act):
     return acc
 
 
+@pytest.fixture(params=["single", "pair"])
+def tile_mode(request, ctx):
+    """Large products run either on one CTA per 128 x 256 tile or on a two-CTA cluster per 256 x 256 tile."""
+    ctx.set_option("gemm_pair_tiles", 2 if request.param == "pair" else 0)
+    yield request.param
+    ctx.set_option("gemm_pair_tiles", 1)
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (200, 256, 256), (4032, 1024, 1024),
                                    (4032, 4096, 1024), (4032, 1024, 4096), (37, 640, 1024), (20000, 256, 256),
-                                   (1, 128, 64)])
-def test_bf16_store_modes(ctx, M, N, K):
+                                   (1, 128, 64), (9500, 2048, 1024), (19000 + 77, 1024, 256)])
+def test_bf16_store_modes(ctx, tile_mode, M, N, K):
     import scriptrs_b200 as sb
 
     g = torch.Generator(device="cuda").manual_seed(M * 7 + N * 3 + K)
@@ -83,8 +91,9 @@ def test_unsupported_shapes_are_rejected(ctx):
     assert e.value.status == 11
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 256, 1024), (4032, 4096, 1024), (4032, 1024, 4096)])
-def test_fp8_e4m3_with_row_and_channel_scales(ctx, M, N, K):
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 256, 1024), (4032, 4096, 1024), (4032, 1024, 4096),
+                                   (9500 + 3, 2048, 1024)])
+def test_fp8_e4m3_with_row_and_channel_scales(ctx, tile_mode, M, N, K):
     """e4m3 operands, fp32 accumulation, per-row and per-output-channel scales applied in the epilogue."""
     import scriptrs_b200 as sb
 
