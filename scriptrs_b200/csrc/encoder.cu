@@ -24,6 +24,7 @@
 #include "attention.h"
 #include "encoder.h"
 #include "gemm.h"
+#include "tc_ptx.cuh"
 
 namespace sb {
 
@@ -500,8 +501,8 @@ dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, const
             a0 = fmaf(w0[k], win[r + k].x, a0);
             a1 = fmaf(w1[k], win[r + k].y, a1);
         }
-        a0 = __fdividef(a0, 1.0f + __expf(-a0));
-        a1 = __fdividef(a1, 1.0f + __expf(-a1));
+        a0 = ptx::silu_fast(a0);
+        a1 = ptx::silu_fast(a1);
         *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(r0 + tb + rh + r) * kDModel + c0 + cp) =
             __floats2bfloat162_rn(a0, a1);
     }

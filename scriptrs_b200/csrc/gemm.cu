@@ -61,12 +61,6 @@ __device__ __forceinline__ uint32_t make_idesc() {
     return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((kBM * CTAS) >> 4) << 24);
 }
 
-__device__ __forceinline__ float apply_act(float x, int act) {
-    if (act == kActSilu) return x / (1.0f + __expf(-x));
-    if (act == kActRelu) return fmaxf(x, 0.0f);
-    return x;
-}
-
 __device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d) {
     const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
     const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
@@ -276,7 +270,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                     }
                     if (ep.act == kActSilu) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j]));
+                        for (int j = 0; j < 32; ++j) x[j] = silu_fast(x[j]);
                     } else if (ep.act == kActRelu) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
@@ -288,7 +282,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                             float y[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e)
-                                y[e] = __fdividef(x[8 * q + e], 1.0f + __expf(-x[16 + 8 * q + e]));
+                                y[e] = gate_fast(x[8 * q + e], x[16 + 8 * q + e]);
                             uint4 pk;
                             __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]);
                             __nv_bfloat162 p2 = __floats2bfloat162_rn(y[4], y[5]), p3 = __floats2bfloat162_rn(y[6], y[7]);
