@@ -106,7 +106,9 @@ int64_t sb_ctx_kernel_launches(const sb_ctx* ctx);
  * Conformer block in FP8 e4m3 (per-row activation scales, per-output-channel weight scales, fp32
  * accumulation); needs a model loaded with fp8_weights.  "simt_attention" (0/1): run the relative-position attention on CUDA cores
  * instead of the tensor-core kernel; "simt_decode" (0/1): run the TDT predictor and joint in plain fp32 on
- * CUDA cores (one persistent kernel) instead of the split-bf16 tensor-core steps; "workspace_budget_mb":
+ * CUDA cores (one persistent kernel) instead of the split-bf16 tensor-core steps; "gemm_pair_tiles" (0/1/2,
+ * process-wide): two-CTA 256 x 256 GEMM tiles never / where they pay (default) / wherever they fit;
+ * "workspace_budget_mb":
  * bytes of encoder intermediates per group of clips (default 12288). */
 int32_t sb_ctx_set_option(sb_ctx* ctx, const char* name, int64_t value);
 
