@@ -139,3 +139,30 @@ def test_fp8_needs_fp8_weights(ctx):
     with pytest.raises(sb.ScriptrsError) as e:
         ctx.set_option("fp8", 1)
     assert e.value.status == 3
+
+
+def test_large_batch_reaches_two_cta_tiles_and_matches_single_cta_and_oracle(ctx):
+    """48 clips x 188 frames = 9024 rows: enough 256 x 256 tiles for the products to run on two-CTA clusters.
+    The two tile shapes add the same products in the same order, so the outputs must be bit-identical; three of
+    the clips are also checked against the oracle."""
+    import scriptrs_b200 as sb
+
+    cfg = eo.EncoderConfig(layers=1)
+    w = eo.seeded_weights(cfg, seed=13, std=0.02, plain_norms=False)
+    sb.load_model(ctx, w, encoder_layers=1)
+    rng = np.random.default_rng(5)
+    feats = [rng.standard_normal((1497 if i % 5 else 1201, 128)).astype(np.float32) for i in range(48)]
+    try:
+        ctx.set_option("gemm_pair_tiles", 0)
+        single = run_gpu(ctx, feats)
+        ctx.set_option("gemm_pair_tiles", 2)
+        pair = run_gpu(ctx, feats)
+    finally:
+        ctx.set_option("gemm_pair_tiles", 1)
+    default = run_gpu(ctx, feats)
+    for a, b, c in zip(single, pair, default):
+        assert np.array_equal(a, b) and np.array_equal(a, c)
+    for i in (0, 5, 47):
+        r = eo.encoder_forward(w, feats[i], cfg)
+        err = np.linalg.norm(pair[i] - r) / np.linalg.norm(r)
+        assert err <= BF16_TOL, (i, err)
