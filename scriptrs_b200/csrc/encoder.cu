@@ -444,68 +444,71 @@ constexpr size_t kAttSmemBytes = ((size_t)(2 * kMaxEncFrames + kPosRows) * kRowS
 
 // ---------------------------------------------------------------- depthwise conv + BN + SiLU
 // in bf16 [rows x 1024] (the GLU is applied by the epilogue of the first pointwise GEMM) -> out bf16 [rows x 1024].
-// grid (time blocks of 32, clips, 4 channel blocks of 256).  Phase 1: 16-byte loads into an fp32 tile
-// [40 rows x 256 channels] in shared memory (zero outside the clip).  Phase 2: each thread convolves two channels
-// over 16 rows.
+// grid (time blocks of 32, clips); a CTA walks the four 256-channel blocks of its rows: the bf16 tile
+// [40 rows x 256 channels] of the next block arrives by cp.async (zero outside the clip) while the current one is
+// convolved; each thread convolves two channels over 16 rows, reading its window straight from the bf16 tile.
 constexpr int kDwRows = 32;
 constexpr int kDwHalo = (kConvK - 1) / 2;
 constexpr int kDwTileRows = kDwRows + kConvK - 1;
 __global__ void __launch_bounds__(256)
 dwconv_kernel(const bf16* __restrict__ in, const int* __restrict__ t3_off, const float* __restrict__ w,
-                  const float* __restrict__ b, bf16* __restrict__ out) {
-    __shared__ __align__(16) float tile[kDwTileRows][256];
+              const float* __restrict__ b, bf16* __restrict__ out) {
+    __shared__ __align__(16) bf16 tile[2][kDwTileRows][256];
     const int clip = blockIdx.y;
     const int r0 = t3_off[clip];
     const int t = t3_off[clip + 1] - r0;
     const int tb = blockIdx.x * kDwRows;
     if (tb >= t) return;
-    const int c0 = blockIdx.z * 256;
-    for (int idx = threadIdx.x; idx < kDwTileRows * 32; idx += 256) {
-        const int r = idx >> 5, v8 = (idx & 31) * 8;
-        const int tt = tb - kDwHalo + r;
-        float g[8];
-        if (tt >= 0 && tt < t) {
-            const uint4 av = *reinterpret_cast<const uint4*>(in + (size_t)(r0 + tt) * kDModel + c0 + v8);
-            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 af = __bfloat1622float2(a2[e]);
-                g[2 * e] = af.x;
-                g[2 * e + 1] = af.y;
-            }
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) g[e] = 0.0f;
+    auto fetch = [&](int zb, int buf) {
+        for (int idx = threadIdx.x; idx < kDwTileRows * 32; idx += 256) {
+            const int r = idx >> 5, v8 = (idx & 31) * 8;
+            const int tt = tb - kDwHalo + r;
+            const bool ok = tt >= 0 && tt < t;
+            const bf16* src = in + (size_t)(r0 + (ok ? tt : 0)) * kDModel + zb * 256 + v8;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&tile[buf][r][v8]);
+            const int bytes = ok ? 16 : 0;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
         }
-        *reinterpret_cast<float4*>(&tile[r][v8]) = make_float4(g[0], g[1], g[2], g[3]);
-        *reinterpret_cast<float4*>(&tile[r][v8 + 4]) = make_float4(g[4], g[5], g[6], g[7]);
-    }
-    __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0, 0);
     const int cp = (threadIdx.x & 127) * 2, rh = (threadIdx.x >> 7) * (kDwRows / 2);
-    float w0[kConvK], w1[kConvK];
-#pragma unroll
-    for (int k = 0; k < kConvK; ++k) {
-        w0[k] = w[k * kDModel + c0 + cp];
-        w1[k] = w[k * kDModel + c0 + cp + 1];
-    }
-    const float b0 = b[c0 + cp], b1 = b[c0 + cp + 1];
-    float2 win[kDwRows / 2 + kConvK - 1];
-#pragma unroll
-    for (int r = 0; r < kDwRows / 2 + kConvK - 1; ++r) win[r] = *reinterpret_cast<const float2*>(&tile[rh + r][cp]);
-#pragma unroll
-    for (int r = 0; r < kDwRows / 2; ++r) {
-        if (tb + rh + r >= t) break;
-        float a0 = b0, a1 = b1;
+    for (int zb = 0; zb < kDModel / 256; ++zb) {
+        const int buf = zb & 1;
+        if (zb + 1 < kDModel / 256) fetch(zb + 1, buf ^ 1);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        const int c0 = zb * 256;
+        float w0[kConvK], w1[kConvK];
 #pragma unroll
         for (int k = 0; k < kConvK; ++k) {
-            a0 = fmaf(w0[k], win[r + k].x, a0);
-            a1 = fmaf(w1[k], win[r + k].y, a1);
+            const float2 wk = *reinterpret_cast<const float2*>(w + k * kDModel + c0 + cp);
+            w0[k] = wk.x;
+            w1[k] = wk.y;
         }
-        a0 = ptx::silu_fast(a0);
-        a1 = ptx::silu_fast(a1);
-        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(r0 + tb + rh + r) * kDModel + c0 + cp) =
-            __floats2bfloat162_rn(a0, a1);
+        const float2 bb = *reinterpret_cast<const float2*>(b + c0 + cp);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();  // this block's tile is complete
+        float2 win[kDwRows / 2 + kConvK - 1];
+#pragma unroll
+        for (int r = 0; r < kDwRows / 2 + kConvK - 1; ++r)
+            win[r] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&tile[buf][rh + r][cp]));
+#pragma unroll
+        for (int r = 0; r < kDwRows / 2; ++r) {
+            if (tb + rh + r >= t) break;
+            float a0 = bb.x, a1 = bb.y;
+#pragma unroll
+            for (int k = 0; k < kConvK; ++k) {
+                a0 = fmaf(w0[k], win[r + k].x, a0);
+                a1 = fmaf(w1[k], win[r + k].y, a1);
+            }
+            a0 = ptx::silu_fast(a0);
+            a1 = ptx::silu_fast(a1);
+            *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(r0 + tb + rh + r) * kDModel + c0 + cp) =
+                __floats2bfloat162_rn(a0, a1);
+        }
+        __syncthreads();  // the buffer is refilled two iterations from now
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 cudaError_t run_gemm(sb_ctx* c, const char* label, const void* a, const bf16* w, const float* bias, void* out, int M, int N,
@@ -706,7 +709,7 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
         // x += Conv(LN x)
         ENC_CUDA(norm_project("gemm_conv_pw1", "gemm_conv_pw1_fp8", L.ln_conv_g, L.ln_conv_b, L.pw1_w, L.pw1_w_q,
                               L.pw1_w_s, L.pw1_b, 2 * kDModel, kActGlu));  // h = GLU(W1 LN(x) + b1), [rows x 1024]
-        PROF("dwconv", (dwconv_kernel<<<dim3((max_t3 + kDwRows - 1) / kDwRows, n, kDModel / 256), 256, 0, st>>>(
+        PROF("dwconv", (dwconv_kernel<<<dim3((max_t3 + kDwRows - 1) / kDwRows, n), 256, 0, st>>>(
                                h, d_t3, L.dw_w, L.dw_b, att)));
         ENC_CUDA(run_gemm(c, "gemm_conv_pw2", att, L.pw2_w, L.pw2_b, x, R3, kDModel, kDModel, kActNone, kOutResidual, 1.0f));
         // x += 0.5 * FF2(LN x)
