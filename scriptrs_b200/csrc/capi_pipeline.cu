@@ -77,13 +77,15 @@ int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const s
     SB_CUDA(c->enc_stage.ensure(sizeof(float) * kDModel * (size_t)enc_rows));
     if (n_tasks > 65535) return fail(SB_INVALID_ARGUMENT, "more than 65535 tasks in one batch");
     // Host PCM goes to the device in pieces on a second stream, so that all but the first piece's copy overlaps the
-    // kernels of the piece before it; frontend and encoder run piece by piece, the decoder once over everything.
+    // kernels of the pieces before it; frontend and encoder run piece by piece, the decoder once over everything.
+    // The first piece is small (1/16 of the tasks: little copy time exposed), the last one large (3/4: the GEMMs
+    // keep their large row counts); at PCIe rates each later copy finishes well inside the earlier pieces' compute.
     const float* d_pcm = pcm + lo;
     int n_pieces = 1;
     if (!pcm_on_device) {
         SB_CUDA(c->pcm_stage.ensure(sizeof(float) * (size_t)(hi - lo)));
         d_pcm = c->pcm_stage.as<float>();
-        if (ordered) n_pieces = (int)std::max<int64_t>(1, std::min<int64_t>(8, n_tasks / 192));
+        if (ordered && n_tasks >= 512) n_pieces = 3;  // below that the extra launches cost more than the copy they hide
         if (!c->copy_stream) SB_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
         while ((int)c->copy_events.size() < n_pieces + 1) {
             cudaEvent_t ev;
@@ -99,7 +101,10 @@ int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const s
     eo[0] = 0;
     int64_t copied_to = lo;
     for (int p = 0; p < n_pieces; ++p) {
-        const int64_t i0 = n_tasks * p / n_pieces, i1 = n_tasks * (p + 1) / n_pieces;
+        // piece boundaries at 0, 1/16, 4/16, 1 of the task list (one piece: everything)
+        static const int kCut[4] = {0, 1, 4, 16};
+        const int64_t i0 = n_pieces == 1 ? 0 : n_tasks * kCut[p] / 16;
+        const int64_t i1 = n_pieces == 1 ? n_tasks : n_tasks * kCut[p + 1] / 16;
         if (i1 <= i0) continue;
         if (!pcm_on_device) {
             const int64_t end = (p == n_pieces - 1) ? hi : tasks[i1 - 1].audio_end;

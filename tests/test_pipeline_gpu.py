@@ -125,12 +125,12 @@ def test_worker_count_does_not_change_the_result(ctx, pipe):
 
 
 def test_pieced_host_copy_equals_resident_path(ctx, pipe):
-    """More than 384 ordered tasks: the host PCM goes up in pieces on a copy stream under the kernels; the token
+    """Many ordered tasks: the host PCM goes up in three pieces on a copy stream under the kernels; the token
     streams must equal those of the same tasks over a device-resident buffer (single piece).  Short tasks keep
     the 2-block encoder cheap."""
     import scriptrs_b200 as sb
 
-    n_tasks, task_len, stride = 400, 4000, 3000
+    n_tasks, task_len, stride = 600, 4000, 3000
     audio = synth.long_audio(stride * (n_tasks - 1) + task_len, 17)
     tasks = [(i * stride, i * stride + task_len, i * stride, 0) for i in range(n_tasks)]
     host = sb.transcribe_chunks(ctx, audio, tasks)
