@@ -179,22 +179,14 @@ def cpu_frontend_baseline(threads: int, budget_s: float = 12.0):
                       f"{threads} thread(s), one clip per thread"}
 
 
-def run_frontend(args, rank, world, local):
-    import torch
-
-    import scriptrs_b200 as sb
+def measure_frontend(ctx, sb, torch, stream, device, rank, world, local, n_clips, steps, warmup, peaks, peak_kind):
+    """Config 1 on this context: `steps` batched frontend passes over n_clips x 30 s resident in HBM.
+    Returns the timing of the whole frontend (all its kernels) and of the log-mel kernel alone, with the clocks
+    sampled while they ran."""
     from scriptrs_b200 import synth
 
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    init_dist(world, local)
-    peaks, peak_kind = measured_peaks()
-    ctx = sb.Context(local)
     fx = sb.ParakeetFeatureExtractor(ctx)
-    stream = torch.cuda.Stream(device=device)
-    ctx.set_stream(stream.cuda_stream)
-
-    n_clips, n = (args.clips or FRONTEND_CLIPS), FRONTEND_SAMPLES
+    n = FRONTEND_SAMPLES
     T = n // 160 + 1
     pcm = synth.clip_batch_torch(n_clips, n, base_seed=1000 + rank, device=device)
     feats = torch.empty(n_clips * T, 128, device=device, dtype=torch.float32)
@@ -207,25 +199,25 @@ def run_frontend(args, rank, world, local):
     sampler = ClockSampler(local)
     sampler.start()
     with torch.cuda.stream(stream):
-        for _ in range(args.warmup):
+        for _ in range(warmup):
             step()
     barrier_sync(world)
     launches0 = ctx.kernel_launches()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     barrier_sync(world)
     with torch.cuda.stream(stream):
         ev[0].record(stream)
-        for i in range(args.steps):
+        for i in range(steps):
             step()
             ev[i + 1].record(stream)
     stream.synchronize()
     barrier_sync(world)
     total_ms = ev[0].elapsed_time(ev[-1])
     launches = ctx.kernel_launches() - launches0
-    # dominant kernel alone (log-mel without the normalisation kernels), live CUDA events
+    # dominant kernel alone (log-mel without the normalisation work), live CUDA events
     k_ms = []
     with torch.cuda.stream(stream):
-        for i in range(max(3, min(args.steps, 10))):
+        for i in range(max(3, min(steps, 10))):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
             step(normalize=False)
@@ -234,7 +226,34 @@ def run_frontend(args, rank, world, local):
             k_ms.append(a.elapsed_time(b))
     clocks = sampler.stop()
     total_ms = max_over_ranks(total_ms, world, device)
-    ms_per_step = total_ms / args.steps
+    ms_per_step = total_ms / steps
+    alg = frontend_algorithmic_bytes(n_clips, n)
+    kern_ms = statistics.mean(k_ms)
+    peak = float(peaks["hbm_gbs"])
+    return {"pcm": pcm, "feats": feats, "offs": offs, "T": T, "n": n, "launches": launches, "ms_per_step": ms_per_step,
+            "kernel_ms": kern_ms, "algorithmic_bytes": alg, "gbs": alg / (ms_per_step * 1e-3) / 1e9,
+            "frac": alg / (ms_per_step * 1e-3) / 1e9 / peak, "kernel_gbs": alg / (kern_ms * 1e-3) / 1e9,
+            "kernel_frac": alg / (kern_ms * 1e-3) / 1e9 / peak, "peak_gbs": peak, "peak_source": peak_kind + " (burst copy)",
+            "clocks": clocks}
+
+
+def run_frontend(args, rank, world, local):
+    import torch
+
+    import scriptrs_b200 as sb
+
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    init_dist(world, local)
+    peaks, peak_kind = measured_peaks()
+    ctx = sb.Context(local)
+    stream = torch.cuda.Stream(device=device)
+    ctx.set_stream(stream.cuda_stream)
+    n_clips = args.clips or FRONTEND_CLIPS
+    m = measure_frontend(ctx, sb, torch, stream, device, rank, world, local, n_clips, args.steps, args.warmup, peaks,
+                         peak_kind)
+    pcm, n, T, offs = m["pcm"], m["n"], m["T"], m["offs"]
+    ms_per_step = m["ms_per_step"]
     audio_s_per_step = n_clips * n / 16000.0
     value = world * audio_s_per_step / (ms_per_step * 1e-3)
 
@@ -265,10 +284,6 @@ def run_frontend(args, rank, world, local):
     e2e_ms = max_over_ranks(e2e_ms, world, device)
     e2e_value = world * audio_s_per_step / (e2e_ms * 1e-3)
 
-    alg = frontend_algorithmic_bytes(n_clips, n)
-    kern_ms = statistics.mean(k_ms)
-    achieved = alg / (kern_ms * 1e-3) / 1e9
-    peak = float(peaks["hbm_gbs"])
     result = {
         "metric": "audio-sec/sec (RTFx), log-mel frontend", "value": value, "unit": "audio-sec/sec",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
@@ -276,14 +291,14 @@ def run_frontend(args, rank, world, local):
         "config": {"workload": f"config 1: batched log-mel frontend, {n_clips} clips x 30 s per GPU, 10% silent",
                    "clips_per_gpu": n_clips, "samples_per_clip": n, "l2": "inputs (1.97 GB) exceed L2",
                    "sharding": f"dp{world}: independent clips per rank, no collective"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "kernel": "logmel_kernel", "peak_source": peak_kind + " (burst copy)",
-                     "algorithmic_bytes_per_launch": alg, "kernel_ms": kern_ms,
-                     "pipeline_gbs": alg / (ms_per_step * 1e-3) / 1e9},
+        "roofline": {"bound": "hbm", "achieved": m["kernel_gbs"], "peak": m["peak_gbs"], "unit": "GB/s",
+                     "frac": m["kernel_frac"], "traffic": None, "kernel": "logmel_kernel",
+                     "peak_source": m["peak_source"], "algorithmic_bytes_per_launch": m["algorithmic_bytes"],
+                     "kernel_ms": m["kernel_ms"], "pipeline_gbs": m["gbs"], "pipeline_frac": m["frac"]},
         "e2e": {"value": e2e_value, "unit": "audio-sec/sec", "h2d_bytes_per_step": int(h_pcm.numel() * 4),
                 "d2h_bytes_per_step": int(h_feats.numel() * 4), "steps": e2e_steps, "ms_per_step": e2e_ms},
-        "gpu_launches": int(launches),
-        "clocks": clocks,
+        "gpu_launches": int(m["launches"]),
+        "clocks": m["clocks"],
     }
     if rank == 0 and not args.skip_cpu_baseline:
         result["cpu_baseline"] = cpu_frontend_baseline(1)
@@ -303,12 +318,9 @@ def bench_vocab_tokens():
 
 def seeded_model(layers):
     """Config-2/3 weights: encoder N(0, 0.02) with identity norms, predictor/joint N(0, 0.05)."""
-    import oracle
-    from oracle import encoder_oracle as eo
+    from scriptrs_b200 import synth
 
-    w = eo.seeded_weights(eo.EncoderConfig(layers=layers), seed=2, std=0.02, plain_norms=True)
-    w.update(oracle.seeded_decoder_weights(3, std=0.05))
-    return w
+    return synth.seeded_model(layers)
 
 
 def cpu_longform_baseline(threads: int, n_chunks: int, layers: int):
@@ -491,8 +503,44 @@ def run_longform(args, rank, world, local):
     prof_wall_ms = (time.perf_counter() - t0) * 1e3
     kernel_ms = {k: {"ms": round(v[0], 3), "launches": v[1]} for k, v in ctx.profile_report().items()}
     kernel_ms["_step_wall_ms"] = round(prof_wall_ms, 3)
+    enc_rows = sum(sb.encoder_num_frames(sb.num_frames(t[1] - t[0])) for t in mine)
+    fp8_report = None
+    if both:
+        # the same profiled step with the Conformer GEMMs in e4m3, and the FP8 tensor peak of this GPU as a yardstick
+        ctx.set_option("fp8", 1)
+        device_step()
+        ctx.profile_report()
+        device_step()
+        k8 = ctx.profile_report()
+        ctx.set_option("fp8", 1 if fp8 else 0)
+        fp8_report = fp8_gemm_report(k8, enc_rows, layers, torch, device, stream)
     ctx.set_profiling(False)
     clocks = sampler.stop()
+    # end to end once more from PAGEABLE host memory (the reference API takes any &[f32]; the headline e2e figure
+    # above assumes the caller pinned its buffer)
+    pageable = None
+    if not args.skip_pageable:
+        p_audio = h_audio.numpy().copy()
+        sb.transcribe_chunks(ctx, None, mine, audio_ptr=p_audio.ctypes.data, n_samples=n)
+        barrier_sync(world)
+        t0 = time.perf_counter()
+        r_p = sb.transcribe_chunks(ctx, None, mine, audio_ptr=p_audio.ctypes.data, n_samples=n)
+        gather_and_finish(r_p)
+        torch.cuda.synchronize()
+        p_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, world, device)
+        pageable = {"value": audio_s / (p_ms * 1e-3), "unit": "audio-sec/sec", "ms_per_step": p_ms, "steps": 1}
+        del p_audio
+    # config 1 (the other half of the metric): batched log-mel frontend, 1024 clips x 30 s, inputs resident
+    frontend = None
+    if not args.no_frontend_line:
+        del d_audio
+        fm = measure_frontend(ctx, sb, torch, stream, device, rank, world, local, FRONTEND_CLIPS, 10, 3, peaks, peak_kind)
+        frontend = {k: fm[k] for k in ("ms_per_step", "kernel_ms", "algorithmic_bytes", "gbs", "frac", "kernel_gbs",
+                                       "kernel_frac", "peak_gbs", "peak_source", "clocks")}
+        frontend.update(workload=f"config 1: {FRONTEND_CLIPS} clips x 30 s per GPU, 10% silent, inputs resident in HBM",
+                        steps=10, warmup=3, unit="GB/s (algorithmic bytes / time; frac = share of the measured HBM peak)",
+                        audio_sec_per_sec=world * FRONTEND_CLIPS * 30.0 / (fm["ms_per_step"] * 1e-3))
+        del fm
 
     enc_flops = sum(ENC_GFLOP_PER_15S_CHUNK * 1e9 * (layers / 24.0) * ((t[1] - t[0]) / 240000.0) for t in tasks)
     result = {
@@ -510,18 +558,21 @@ def run_longform(args, rank, world, local):
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "traffic": int(2 * (m_rows * 1024 + 4096 * 1024 + m_rows * 4096)),
                      "traffic_source": "operand + output bytes per launch; an ncu capture of the same kernel at 13 k rows "
-                                       "reads exactly the operand bytes from DRAM and writes no more than the output "
-                                       "(profiles/gemm_kernel_conformer_shapes_70clips.md); scaled by rows",
+                                       "reads exactly the operand bytes from DRAM and writes no more than the output; "
+                                       "scaled by rows",
                      "kernel": "gemm_kernel<256,bf16> (feed-forward 1024->4096, SiLU epilogue)",
                      "shape": [m_rows, 4096, 1024], "kernel_ms": gemm_ms, "peak_source": peak_kind + " (burst)",
                      "encoder_algorithmic_tflop_per_step": enc_flops / 1e12,
                      "whole_step_tflops_per_gpu": enc_flops / world / (ms_per_step * 1e-3) / 1e12},
         "e2e": {"value": audio_s / (e2e_ms * 1e-3), "unit": "audio-sec/sec", "h2d_bytes_per_step": int(span * 4),
                 "d2h_bytes_per_step": int(n_tokens * 16), "steps": e2e_steps, "ms_per_step": e2e_ms,
+                "host_memory": "pinned", "pageable_host_memory": pageable,
                 "transcript_tokens": (len(res) if res is not None else None), "equals_resident_path_rank0": same,
                 "rank0_phases_ms": {k: v / e2e_steps for k, v in phases.items()}},
         "gpu_launches": int(launches),
         "fp8_variant": variant,
+        "fp8_gemms": fp8_report,
+        "frontend": frontend,
         "stage_ms_rank0": stage_ms,
         "kernel_ms_rank0": kernel_ms,
         "clocks": clocks,
@@ -530,6 +581,70 @@ def run_longform(args, rank, world, local):
         result["cpu_baseline"] = cpu_longform_baseline(os.cpu_count() or 1, 24, layers)
     ctx.close()
     return result
+
+
+FP8_GEMM_SHAPES = {"gemm_ff_up_fp8": (4096, 1024, 2), "gemm_ff_down_fp8": (1024, 4096, 2),
+                   "gemm_qkv_fp8": (3072, 1024, 1), "gemm_conv_pw1_fp8": (2048, 1024, 1)}  # N, K, launches per block
+
+
+def fp8_tensor_peak(torch, device, stream):
+    """FP8 (e4m3 x e4m3 -> bf16, fp32 accumulation) rate of a large square library GEMM on this GPU: best of 10
+    single launches and a 4 s back-to-back loop.  A yardstick only; nothing on the transcription path calls it."""
+    n = 8192
+    try:
+        a = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+        one = torch.ones((), device=device)
+        f = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                f()
+            stream.synchronize()
+            best = 1e9
+            for _ in range(10):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                f()
+                e1.record(stream)
+                stream.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(10, int(4000.0 / best))
+            e0.record(stream)
+            for _ in range(reps):
+                f()
+            e1.record(stream)
+            stream.synchronize()
+            sustained_ms = e0.elapsed_time(e1) / reps
+        fl = 2.0 * n ** 3
+        return {"burst_tflops": fl / (best * 1e-3) / 1e12, "sustained_tflops": fl / (sustained_ms * 1e-3) / 1e12,
+                "how": f"torch._scaled_mm e4m3 {n}^3, best of 10 and {reps} launches back to back"}
+    except Exception as exc:  # the library call is a yardstick; its absence must not fail the bench
+        return {"burst_tflops": None, "sustained_tflops": None, "how": f"unavailable: {type(exc).__name__}: {exc}"[:200]}
+
+
+def fp8_gemm_report(kernel_ms, enc_rows, layers, torch, device, stream):
+    """TFLOP/s of the e4m3 GEMMs inside one profiled step, against the measured FP8 peak."""
+    peak = fp8_tensor_peak(torch, device, stream)
+    out = {"peak": peak, "gemms": {}}
+    tot_fl, tot_ms = 0.0, 0.0
+    for label, (N, K, per_block) in FP8_GEMM_SHAPES.items():
+        if label not in kernel_ms:
+            continue
+        ms = kernel_ms[label][0]
+        fl = 2.0 * enc_rows * N * K * per_block * layers
+        tot_fl += fl
+        tot_ms += ms
+        tf = fl / (ms * 1e-3) / 1e12
+        out["gemms"][label] = {"ms": round(ms, 3), "tflops": round(tf, 1),
+                               "frac_of_burst_peak": (tf / peak["burst_tflops"]) if peak["burst_tflops"] else None,
+                               "frac_of_sustained_peak": (tf / peak["sustained_tflops"]) if peak["sustained_tflops"] else None}
+    if tot_ms > 0:
+        tf = tot_fl / (tot_ms * 1e-3) / 1e12
+        out["all_fp8_gemms"] = {"ms": round(tot_ms, 3), "tflops": round(tf, 1),
+                                "frac_of_burst_peak": (tf / peak["burst_tflops"]) if peak["burst_tflops"] else None,
+                                "frac_of_sustained_peak": (tf / peak["sustained_tflops"]) if peak["sustained_tflops"] else None}
+    return out
 
 
 def stage_breakdown(ctx, sb, torch, stream, d_audio, tasks):
@@ -566,23 +681,44 @@ def stage_breakdown(ctx, sb, torch, stream, d_audio, tasks):
     return out
 
 
+def _percentile(vals, q):
+    v = sorted(vals)
+    if len(v) == 1:
+        return v[0]
+    pos = q * (len(v) - 1)
+    lo = int(pos)
+    hi = min(lo + 1, len(v) - 1)
+    return v[lo] + (v[hi] - v[lo]) * (pos - lo)
+
+
 def run_reference_longform(args):
+    """CPU restatement of the reference path on all host threads.  Protocol as the reference's own timing loops
+    (examples/transcribe_wav.rs:193-214, dev-tools/src/bin/compare_parakeet_rs.rs:392-436): at least one warm-up
+    run, then K timed runs; mean, p50 and p95 reported.  Each step is a bounded sample of config 4 (a few overlap
+    chunks) sized so that K + W steps end within a few minutes."""
     threads = os.cpu_count() or 1
     layers = args.layers
-    vals, last = [], None
-    t0 = time.perf_counter()
-    for _ in range(max(1, min(args.steps, 3))):
-        last = cpu_longform_baseline(threads, 12, layers)
+    steps, warmup = max(1, args.steps), max(1, args.warmup)
+    n_chunks = max(3, min(24, 270 // (steps + warmup)))
+    for _ in range(warmup):
+        cpu_longform_baseline(threads, n_chunks, layers)
+    vals, ms, last = [], [], None
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        last = cpu_longform_baseline(threads, n_chunks, layers)
+        ms.append((time.perf_counter() - t0) * 1e3)
         vals.append(last["value"])
-    dt = time.perf_counter() - t0
     v = statistics.mean(vals)
     last["value"] = v
     return {
         "impl": "reference", "metric": "audio-sec/sec (RTFx), Parakeet-TDT-0.6B long-form transcription", "value": v,
-        "unit": "audio-sec/sec", "n_gpus": args.gpus, "steps": len(vals), "warmup": 0,
-        "ms_per_step": dt / len(vals) * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "unit": "audio-sec/sec", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": statistics.mean(ms), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"config 4 (bounded sample): CPU restatement of the reference path, {layers} blocks"},
+        "config": {"workload": f"config 4 (bounded sample of {n_chunks} overlap chunks per step): CPU restatement of the "
+                               f"reference path, {layers} blocks"},
+        "value_p50": _percentile(vals, 0.5), "value_p95_slowest": _percentile(vals, 0.05),
+        "ms_per_step_p50": _percentile(ms, 0.5), "ms_per_step_p95": _percentile(ms, 0.95),
         "cpu_baseline": last,
         "e2e": {"value": v, "unit": "audio-sec/sec", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -590,24 +726,25 @@ def run_reference_longform(args):
 
 def run_reference_frontend(args):
     threads = os.cpu_count() or 1
-    per_step = 6.0
-    vals = []
-    for _ in range(min(args.warmup, 1)):
-        cpu_frontend_baseline(threads, 2.0)
-    t0 = time.perf_counter()
-    last = None
-    for _ in range(max(1, min(args.steps, 5))):
+    steps, warmup = max(1, args.steps), max(1, args.warmup)
+    per_step = max(1.0, min(6.0, 120.0 / (steps + warmup)))
+    for _ in range(warmup):
+        cpu_frontend_baseline(threads, per_step)
+    vals, ms, last = [], [], None
+    for _ in range(steps):
+        t0 = time.perf_counter()
         last = cpu_frontend_baseline(threads, per_step)
+        ms.append((time.perf_counter() - t0) * 1e3)
         vals.append(last["value"])
-    dt = time.perf_counter() - t0
     v = statistics.mean(vals)
     last["value"] = v
     return {
         "impl": "reference", "metric": "audio-sec/sec (RTFx), log-mel frontend", "value": v,
-        "unit": "audio-sec/sec", "n_gpus": args.gpus, "steps": len(vals), "warmup": min(args.warmup, 1),
-        "ms_per_step": dt / len(vals) * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "unit": "audio-sec/sec", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": statistics.mean(ms), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": "config 1: batched log-mel frontend, 30 s clips, CPU restatement of src/frontend.rs"},
+        "value_p50": _percentile(vals, 0.5), "value_p95_slowest": _percentile(vals, 0.05),
         "cpu_baseline": last,
         "e2e": {"value": v, "unit": "audio-sec/sec", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -627,6 +764,8 @@ def main():
     ap.add_argument("--stage-breakdown", action="store_true", help="longform: also time the three stage entry points")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="profiling runs: leave the CPU leg out")
     ap.add_argument("--no-fp8-variant", action="store_true", help="longform: do not also time the FP8 variant")
+    ap.add_argument("--no-frontend-line", action="store_true", help="longform: do not also time config 1 (frontend)")
+    ap.add_argument("--skip-pageable", action="store_true", help="longform: leave out the pageable-memory e2e step")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":

@@ -104,7 +104,12 @@ int64_t sb_ctx_kernel_launches(const sb_ctx* ctx);
 
 /* Tuning and test switches.  "fp8" (0/1): run the feed-forward, QKV and first pointwise GEMMs of every
  * Conformer block in FP8 e4m3 (per-row activation scales, per-output-channel weight scales, fp32
- * accumulation); needs a model loaded with fp8_weights.  "simt_attention" (0/1): run the relative-position attention on CUDA cores
+ * accumulation); needs a model loaded with fp8_weights.  "fp8_mask" (bits: 1 feed-forward up, 2 feed-forward
+ * down, 4 QKV, 8 first pointwise; default 15): which of those products take the e4m3 path when "fp8" is on.
+ * "fp8_hidden_amax" (0/1): scale the e4m3 hidden row of the feed-forward module by its true maximum (one more
+ * pass over the row) instead of a bound known before the product runs.  "test_raise_device_error" (0/1): sets
+ * the device flag that a kernel raises when a bounded wait runs out (host-side fault injection for tests).
+ * "simt_attention" (0/1): run the relative-position attention on CUDA cores
  * instead of the tensor-core kernel; "simt_decode" (0/1): run the TDT predictor and joint in plain fp32 on
  * CUDA cores (one persistent kernel) instead of the split-bf16 tensor-core steps; "gemm_pair_tiles" (0/1/2,
  * process-wide): two-CTA 256 x 256 GEMM tiles never / where they pay (default) / wherever they fit;
@@ -159,7 +164,9 @@ int32_t sb_frontend_host(sb_ctx* ctx, const float* pcm, const int64_t* clip_offs
  *   - runs on the CURRENT device, on `stream` (a cudaStream_t; NULL = default stream); arguments and
  *     results are those of sb_frontend_device, bit for bit;
  *   - the first call on a device looks up the array's address and fills the tables: make it before
- *     any stream capture;
+ *     any stream capture (first calls from several host threads take turns on a mutex); a call on a
+ *     stream that is capturing is refused with SB_INVALID_ARGUMENT, because the clip metadata is
+ *     copied from the host stack of the call;
  *   - all calls on a device share the array, which keeps the last call's contents (nothing in it has
  *     to be zero); calls whose kernels overlap on the GPU race on it, so serialise them. */
 int32_t sb_frontend_device_noalloc(const float* d_pcm, const int64_t* clip_offsets, int64_t n_clips,
@@ -221,7 +228,10 @@ int32_t sb_encode_device(sb_ctx* ctx, const float* d_feats, const int64_t* frame
 /* Batched ParakeetModel::greedy_decode (src/model.rs:64-95) with the state machine of
  * GreedyDecodeState (src/model.rs:98-214); the predictor (run_decoder, src/model.rs:344-364) and the
  * joint decision (run_joint, src/model.rs:366-384: token arg-max over 1025, duration arg-max over 5,
- * confidence = max softmax) run inside one persistent kernel for the whole batch.
+ * confidence = max softmax) run for the whole batch at once: by default every loop iteration is a short
+ * sequence of tensor-core products and element-wise kernels replayed from a CUDA graph by the host, which
+ * reads an "any sequence alive" word every few iterations; with the option "simt_decode" the whole loop
+ * runs inside one persistent fp32 kernel.
  *   d_enc         device, packed [sum_i T'_i x 1024] f32, time-major per clip
  *   enc_offsets   host, n_clips + 1 prefix sums of T'_i
  *   max_tokens    capacity per clip of the four output arrays (host, [n_clips x max_tokens]);

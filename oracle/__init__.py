@@ -257,27 +257,12 @@ def merge_windows(windows):
     return otok[:n], ofrm[:n], odur[:n], oconf[:n]
 
 
-# -------------------------------------------------- seeded decoder weights (shared by tests and bench)
-DECODER_SHAPES = {
-    "predictor.embedding": (1025, 640),
-    "predictor.lstm.weight_ih": (2, 2560, 640),
-    "predictor.lstm.weight_hh": (2, 2560, 640),
-    "predictor.lstm.bias_ih": (2, 2560),
-    "predictor.lstm.bias_hh": (2, 2560),
-    "joint.enc.weight": (640, 1024),
-    "joint.enc.bias": (640,),
-    "joint.pred.weight": (640, 640),
-    "joint.pred.bias": (640,),
-    "joint.out.weight": (1030, 640),
-    "joint.out.bias": (1030,),
-}
-
-
+# -------------------------------------------------- seeded decoder weights (generated by scriptrs_b200.synth)
 def seeded_decoder_weights(seed: int, std: float = 0.05) -> dict:
     """Config-3 predictor / joint weights: N(0, std) per tensor, named as the library's loader expects."""
     from scriptrs_b200 import synth
 
-    return {k: synth.normal_tensor(k, shp, std, seed) for k, shp in DECODER_SHAPES.items()}
+    return synth.seeded_decoder_weights(seed, std)
 
 
 def tdt_weights_from_named(w: dict) -> dict:

@@ -46,64 +46,18 @@ def subsampled_length(t: int) -> int:
     return t
 
 
+def _shape_kw(cfg: EncoderConfig):
+    return dict(d_model=cfg.d_model, heads=cfg.heads, ff=cfg.ff, conv_kernel=cfg.conv_kernel,
+                sub_channels=cfg.sub_channels, mels=cfg.mels)
+
+
 def weight_shapes(cfg: EncoderConfig):
-    C, d, ff, k = cfg.sub_channels, cfg.d_model, cfg.ff, cfg.conv_kernel
-    f_out = cfg.mels // 8
-    s = {
-        "subsampling.layers.0.weight": (C, 1, 3, 3), "subsampling.layers.0.bias": (C,),
-        "subsampling.layers.2.weight": (C, 1, 3, 3), "subsampling.layers.2.bias": (C,),
-        "subsampling.layers.3.weight": (C, C, 1, 1), "subsampling.layers.3.bias": (C,),
-        "subsampling.layers.5.weight": (C, 1, 3, 3), "subsampling.layers.5.bias": (C,),
-        "subsampling.layers.6.weight": (C, C, 1, 1), "subsampling.layers.6.bias": (C,),
-        "subsampling.linear.weight": (d, C * f_out), "subsampling.linear.bias": (d,),
-    }
-    for i in range(cfg.layers):
-        p = f"layers.{i}."
-        for ffn in ("feed_forward1", "feed_forward2"):
-            s[p + ffn + ".linear1.weight"] = (ff, d)
-            s[p + ffn + ".linear1.bias"] = (ff,)
-            s[p + ffn + ".linear2.weight"] = (d, ff)
-            s[p + ffn + ".linear2.bias"] = (d,)
-        for proj in ("q_proj", "k_proj", "v_proj", "o_proj"):
-            s[p + "self_attn." + proj + ".weight"] = (d, d)
-            s[p + "self_attn." + proj + ".bias"] = (d,)
-        s[p + "self_attn.relative_k_proj.weight"] = (d, d)
-        s[p + "self_attn.bias_u"] = (cfg.heads, d // cfg.heads)
-        s[p + "self_attn.bias_v"] = (cfg.heads, d // cfg.heads)
-        s[p + "conv.pointwise_conv1.weight"] = (2 * d, d, 1)
-        s[p + "conv.pointwise_conv1.bias"] = (2 * d,)
-        s[p + "conv.depthwise_conv.weight"] = (d, 1, k)
-        s[p + "conv.depthwise_conv.bias"] = (d,)
-        for n in ("weight", "bias", "running_mean", "running_var"):
-            s[p + "conv.norm." + n] = (d,)
-        s[p + "conv.pointwise_conv2.weight"] = (d, d, 1)
-        s[p + "conv.pointwise_conv2.bias"] = (d,)
-        for ln in ("norm_feed_forward1", "norm_self_att", "norm_conv", "norm_feed_forward2", "norm_out"):
-            s[p + ln + ".weight"] = (d,)
-            s[p + ln + ".bias"] = (d,)
-    return s
+    return synth.encoder_weight_shapes(cfg.layers, **_shape_kw(cfg))
 
 
 def seeded_weights(cfg: EncoderConfig, seed: int, std: float = 0.02, plain_norms: bool = True):
-    """N(0, std) for every matrix, bias and u/v.  plain_norms=True: LayerNorm gamma 1 / beta 0 and
-    BatchNorm gamma 1, beta 0, mean 0, var 1 (the benchmark configuration); False: seeded
-    non-trivial values so that tests exercise every parameter."""
-    w = {}
-    for name, shape in weight_shapes(cfg).items():
-        is_norm = ".norm" in name or "norm_" in name
-        if is_norm:
-            if plain_norms:
-                v = np.ones(shape, np.float32) if name.endswith(("weight", "running_var")) else np.zeros(shape, np.float32)
-            elif name.endswith("running_var"):
-                v = 0.5 + np.abs(synth.normal_tensor(name, shape, 0.5, seed))
-            elif name.endswith("weight"):
-                v = 1.0 + synth.normal_tensor(name, shape, 0.1, seed)
-            else:
-                v = synth.normal_tensor(name, shape, 0.1, seed)
-        else:
-            v = synth.normal_tensor(name, shape, std, seed)
-        w[name] = v.astype(np.float32)
-    return w
+    """Seeded weights of scriptrs_b200.synth for this configuration (same tensors for oracle and library)."""
+    return synth.seeded_encoder_weights(cfg.layers, seed, std, plain_norms, **_shape_kw(cfg))
 
 
 def rel_positions(t: int, d_model: int) -> torch.Tensor:

@@ -8,10 +8,12 @@ Restates, for small cases, the reference's
   Vocabulary::from_file           src/vocab.rs:15-52
   join_token_text / build_chunk / build_result   src/long_form.rs:602-647
 Pinned by the reference's known-answer tests decode.rs:151-179.
-`str.isalpha()` stands in for Rust's `char::is_alphabetic` (they agree on every
-letter category; Rust additionally counts letter-numbers such as Roman numerals).
+`str.isalpha()` plus the letter-number category Nl stands in for Rust's `char::is_alphabetic`
+(Rust additionally counts the Other_Alphabetic marks, which the standard library does not expose).
 """
 from __future__ import annotations
+
+import unicodedata
 
 SECONDS_PER_FRAME = 1280 / 16000
 
@@ -55,7 +57,7 @@ def needs_digit_spacing(existing: str, display: str) -> bool:
         return False
     trailing = 0
     for ch in reversed(existing):
-        if ch.isalpha():
+        if ch.isalpha() or unicodedata.category(ch) == "Nl":
             trailing += 1
         else:
             break

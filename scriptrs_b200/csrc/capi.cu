@@ -206,22 +206,32 @@ int32_t sb_ctx_create(int32_t device, sb_ctx** out) {
     c->device = device;
     c->sm_count = prop.multiProcessorCount;
     c->pcm_stage.pinned_host = false;
-    SB_CUDA(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
+    // any failure from here on destroys the half-built context (sb_ctx_destroy tolerates null members)
+    auto bail = [&](int32_t st) {
+        sb_ctx_destroy(c);
+        return st;
+    };
+#define SB_CREATE_CUDA(expr)                                            \
+    do {                                                                \
+        cudaError_t _e = (expr);                                        \
+        if (_e != cudaSuccess) return bail(::sb::cuda_fail(_e, #expr)); \
+    } while (0)
+    SB_CREATE_CUDA(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
     c->stream = c->own_stream;
     FrontendTables host_tables;
-    if (!build_frontend_tables(&host_tables, nullptr)) {
-        delete c;
-        return fail(SB_INVALID_MODEL_OUTPUT, "mel filterbank rows exceed the tap budget");
-    }
-    SB_CUDA(cudaMalloc(&c->d_tables, sizeof(FrontendTables)));
-    SB_CUDA(cudaMemcpy(c->d_tables, &host_tables, sizeof(FrontendTables), cudaMemcpyHostToDevice));
-    SB_CUDA(frontend_configure());
-    SB_CUDA(cudaMalloc(&c->d_error, sizeof(int)));
-    SB_CUDA(cudaMemset(c->d_error, 0, sizeof(int)));
+    if (!build_frontend_tables(&host_tables, nullptr))
+        return bail(fail(SB_INVALID_MODEL_OUTPUT, "mel filterbank rows exceed the tap budget"));
+    SB_CREATE_CUDA(cudaMalloc(&c->d_tables, sizeof(FrontendTables)));
+    SB_CREATE_CUDA(cudaMemcpy(c->d_tables, &host_tables, sizeof(FrontendTables), cudaMemcpyHostToDevice));
+    SB_CREATE_CUDA(frontend_configure());
+    SB_CREATE_CUDA(cudaMalloc(&c->d_error, sizeof(int)));
+    SB_CREATE_CUDA(cudaMemset(c->d_error, 0, sizeof(int)));
     const char* why = nullptr;
     cudaError_t ge = gemm_configure(&why);
-    if (ge != cudaSuccess) return fail(SB_CUDA_ERROR, std::string("GEMM set-up failed: ") + (why ? why : cudaGetErrorString(ge)));
-    SB_CUDA(encoder_configure());
+    if (ge != cudaSuccess)
+        return bail(fail(SB_CUDA_ERROR, std::string("GEMM set-up failed: ") + (why ? why : cudaGetErrorString(ge))));
+    SB_CREATE_CUDA(encoder_configure());
+#undef SB_CREATE_CUDA
     c->enc_ws = new EncoderWorkspace();
     *out = c;
     return SB_OK;
@@ -281,6 +291,12 @@ int32_t sb_ctx_set_option(sb_ctx* c, const char* name, int64_t value) {
         c->fp8 = value != 0;
     }
     else if (n == "fp8_mask") c->fp8_mask = (int)(value & 15);
+    else if (n == "fp8_hidden_amax") c->fp8_hidden_amax = value != 0;
+    else if (n == "test_raise_device_error") {
+        // host-side fault injection for tests: sets the flag a kernel would set when a bounded wait runs out
+        SB_CUDA(cudaSetDevice(c->device));
+        SB_CUDA(cudaMemsetAsync(c->d_error, value ? 1 : 0, sizeof(int), c->stream));
+    }
     else if (n == "workspace_budget_mb" && value > 0) c->workspace_budget = (size_t)value << 20;
     else return fail(SB_INVALID_ARGUMENT, "unknown option: " + n);
     return SB_OK;

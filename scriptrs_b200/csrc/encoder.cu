@@ -642,7 +642,7 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
     auto feed_forward = [&](const float* pg, const float* pb, const float* g, const float* b, const bf16* w1, const uint8_t* w1q, const float* w1s,
                             const float* b1, const bf16* w2, const uint8_t* w2q, const float* w2s,
                             const float* b2, float wn, float bmax) -> cudaError_t {
-        if (fp8 && (c->fp8_mask & 3) == 3) {
+        if (fp8 && (c->fp8_mask & 3) == 3 && !c->fp8_hidden_amax) {
             // LayerNorm -> e4m3; up-projection writes the e4m3 hidden row with a scale bounded in advance
             PROF("layernorm_fp8", (layernorm_fp8_kernel<<<ln_grid, 256, 0, st>>>(x, pg, pb, g, b, a8, rs_a, R3, rs_h, wn, bmax)));
             ENC_CUDA(run_gemm_fp8(c, "gemm_ff_up_fp8", a8, rs_a, w1q, w1s, b1, h8, R3, kFF, kDModel, kActSilu, kOutFp8, 1.0f, rs_h));

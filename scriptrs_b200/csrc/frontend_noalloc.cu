@@ -17,7 +17,9 @@
 // Consequences the caller has to know:
 //   * at most kNoAllocMaxClips clips per call; more is refused with SB_INVALID_ARGUMENT;
 //   * the first call on a device resolves the array's device address and fills the tables; make
-//     that first call outside any stream capture;
+//     that first call outside any stream capture.  First calls from several host threads are
+//     serialised by a mutex.  A call made while its stream is capturing is refused with
+//     SB_INVALID_ARGUMENT: the per-call clip metadata is copied from the host stack;
 //   * all calls on a device share the array, and it keeps what the last call left in it.  Nothing in
 //     it has to start at zero (each call rewrites the metadata and the statistics of the clips it
 //     processes before reading them), but two calls whose kernels overlap on the GPU, from
@@ -26,7 +28,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstring>
+#include <mutex>
 #include <string>
 
 #include "context.h"
@@ -50,16 +54,19 @@ constexpr int kMaxDevices = 64;
 // Device address of g_frontend_scratch per device.  The symbol's name is only a host-side handle:
 // kernels must be given the address that cudaGetSymbolAddress returns for the current device.
 unsigned char* g_scratch_ptr[kMaxDevices] = {};
-bool g_ready[kMaxDevices] = {};
+std::atomic<bool> g_ready[kMaxDevices];
+std::mutex g_setup_mutex;  // first calls from several host threads (same or different devices) take turns
 
 int32_t setup_device(int device, cudaStream_t stream) {
-    if (g_ready[device]) return SB_OK;
+    if (g_ready[device].load(std::memory_order_acquire)) return SB_OK;
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    if (g_ready[device].load(std::memory_order_acquire)) return SB_OK;
     unsigned char* ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_frontend_scratch);
     if (e != cudaSuccess || !ptr) return cuda_fail(e != cudaSuccess ? e : cudaErrorInvalidSymbol, "cudaGetSymbolAddress(frontend scratch)");
     e = frontend_configure();  // shared-memory opt-in of the log-mel kernel; not an allocation
     if (e != cudaSuccess) return cuda_fail(e, "frontend_configure");
-    static FrontendTables host_tables;  // static: the copy below may outlive this call
+    static FrontendTables host_tables;  // static: the copy below may outlive this call; guarded by the mutex
     if (!build_frontend_tables(&host_tables, nullptr))
         return fail(SB_INVALID_MODEL_OUTPUT, "mel filterbank rows exceed the tap budget");
     e = cudaMemcpyAsync(ptr, &host_tables, sizeof(FrontendTables), cudaMemcpyHostToDevice, stream);
@@ -67,7 +74,7 @@ int32_t setup_device(int device, cudaStream_t stream) {
     e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return cuda_fail(e, "frontend table set-up");
     g_scratch_ptr[device] = ptr;
-    g_ready[device] = true;
+    g_ready[device].store(true, std::memory_order_release);  // published after the address it guards
     return SB_OK;
 }
 
@@ -90,6 +97,15 @@ extern "C" int32_t sb_frontend_device_noalloc(const float* d_pcm, const int64_t*
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (device < 0 || device >= kMaxDevices) return fail(SB_INVALID_ARGUMENT, "device index out of range");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The clip metadata below is copied from this call's stack frame; a capturing stream would record that host
+    // address and read it again at every replay, long after the frame is gone.  Refuse instead.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    e = cudaStreamIsCapturing(st, &cap);
+    if (e != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        if (e != cudaSuccess) (void)cudaGetLastError();
+        return fail(SB_INVALID_ARGUMENT, "sb_frontend_device_noalloc was called while a stream capture is active; "
+                                         "it copies per-call metadata from the host stack and refuses to be recorded");
+    }
     int32_t s = setup_device(device, st);
     if (s != SB_OK) return s;
 

@@ -5,9 +5,10 @@
 //   is_special_token                src/decode.rs:110-112
 //   needs_digit_spacing             src/decode.rs:114-134
 //   join_token_text / build_chunk / build_result   src/long_form.rs:602-647
-// Strings are UTF-8.  `char::is_alphabetic` is evaluated from a range table of the letter blocks
-// of the scripts a speech vocabulary uses (Latin, Greek, Cyrillic, Armenian, Hebrew, Arabic, Indic
-// letters, kana, Hangul, CJK ideographs); code points outside the table count as non-alphabetic.
+// Strings are UTF-8.  `char::is_alphabetic` is evaluated from a generated table of all code points of the
+// Unicode general categories L* and Nl (unicode_alpha_table.h, written by make_alpha_table.py).  Rust's
+// property also includes Other_Alphabetic (combining vowel signs and the like); those few marks count as
+// non-alphabetic here.
 #include <algorithm>
 #include <cstdio>
 #include <fstream>
@@ -15,6 +16,7 @@
 #include <utility>
 
 #include "longform.h"
+#include "unicode_alpha_table.h"
 
 namespace sb {
 
@@ -22,19 +24,15 @@ namespace {
 
 constexpr double kSecondsPerFrame = 1280.0 / 16000.0;
 
-struct Range { uint32_t lo, hi; };
-const Range kAlpha[] = {
-    {0x41, 0x5A}, {0x61, 0x7A}, {0xAA, 0xAA}, {0xB5, 0xB5}, {0xBA, 0xBA}, {0xC0, 0xD6}, {0xD8, 0xF6}, {0xF8, 0x2C1},
-    {0x2C6, 0x2D1}, {0x2E0, 0x2E4}, {0x370, 0x374}, {0x376, 0x377}, {0x37A, 0x37D}, {0x37F, 0x37F}, {0x386, 0x386},
-    {0x388, 0x3FF}, {0x400, 0x481}, {0x48A, 0x52F}, {0x531, 0x556}, {0x561, 0x587}, {0x5D0, 0x5EA}, {0x620, 0x64A},
-    {0x66E, 0x6D3}, {0x904, 0x939}, {0x958, 0x961}, {0x985, 0x9B9}, {0xE01, 0xE30}, {0x10A0, 0x10FF},
-    {0x1E00, 0x1FFF}, {0x3041, 0x3096}, {0x30A1, 0x30FA}, {0x3400, 0x4DBF}, {0x4E00, 0x9FFF}, {0xAC00, 0xD7A3},
-    {0xFF21, 0xFF3A}, {0xFF41, 0xFF5A},
-};
-
+// binary search in the generated table (sorted, non-overlapping ranges)
 bool is_alphabetic(uint32_t cp) {
-    for (const Range& r : kAlpha)
-        if (cp >= r.lo && cp <= r.hi) return true;
+    int lo = 0, hi = kAlphaRangeCount - 1;
+    while (lo <= hi) {
+        const int mid = (lo + hi) / 2;
+        if (cp < kAlphaRanges[mid].lo) hi = mid - 1;
+        else if (cp > kAlphaRanges[mid].hi) lo = mid + 1;
+        else return true;
+    }
     return false;
 }
 

@@ -149,7 +149,15 @@ int32_t tdt_decode(sb_ctx* c, const float* d_enc, const int64_t* enc_offsets, in
         // read back: counts first, then only the used columns of the output tables
         std::vector<int> cnt((size_t)2 * n + 1);
         SB_CUDA(cudaMemcpyAsync(cnt.data(), s.n_tokens, sizeof(int) * (2 * n + 1), cudaMemcpyDeviceToHost, st));
+        // the flag that a kernel of this stream (GEMM, attention, decoder) raises when one of its bounded waits ran
+        // out: everything computed after that is garbage, so the call must not return tokens
+        int dev_err = 0;
+        SB_CUDA(cudaMemcpyAsync(&dev_err, c->d_error, sizeof(int), cudaMemcpyDeviceToHost, st));
         SB_CUDA(cudaStreamSynchronize(st));
+        if (dev_err) {
+            SB_CUDA(cudaMemsetAsync(c->d_error, 0, sizeof(int), st));
+            return fail(SB_TIMEOUT, "a bounded device-side wait ran out (kernel aborted cleanly); no tokens returned");
+        }
         if (d_timing) {
             long long t[12];
             SB_CUDA(cudaMemcpy(t, d_timing, sizeof(t), cudaMemcpyDeviceToHost));

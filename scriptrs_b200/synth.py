@@ -114,3 +114,93 @@ def normal_tensor(name: str, shape, std: float, seed: int) -> np.ndarray:
     s = (zlib.crc32(name.encode()) ^ (seed * 0x9E3779B1)) & 0xFFFFFFFF
     rng = np.random.default_rng(s)
     return (rng.standard_normal(int(np.prod(shape)), dtype=np.float32) * np.float32(std)).reshape(shape)
+
+
+# ------------------------------------------------------------------ seeded model weights
+def encoder_weight_shapes(layers: int = 24, d_model: int = 1024, heads: int = 8, ff: int = 4096, conv_kernel: int = 9,
+                          sub_channels: int = 256, mels: int = 128) -> dict:
+    """Names and shapes of the FastConformer encoder tensors (the names sb_model_load expects)."""
+    C, d, k = sub_channels, d_model, conv_kernel
+    f_out = mels // 8
+    s = {
+        "subsampling.layers.0.weight": (C, 1, 3, 3), "subsampling.layers.0.bias": (C,),
+        "subsampling.layers.2.weight": (C, 1, 3, 3), "subsampling.layers.2.bias": (C,),
+        "subsampling.layers.3.weight": (C, C, 1, 1), "subsampling.layers.3.bias": (C,),
+        "subsampling.layers.5.weight": (C, 1, 3, 3), "subsampling.layers.5.bias": (C,),
+        "subsampling.layers.6.weight": (C, C, 1, 1), "subsampling.layers.6.bias": (C,),
+        "subsampling.linear.weight": (d, C * f_out), "subsampling.linear.bias": (d,),
+    }
+    for i in range(layers):
+        p = f"layers.{i}."
+        for ffn in ("feed_forward1", "feed_forward2"):
+            s[p + ffn + ".linear1.weight"] = (ff, d)
+            s[p + ffn + ".linear1.bias"] = (ff,)
+            s[p + ffn + ".linear2.weight"] = (d, ff)
+            s[p + ffn + ".linear2.bias"] = (d,)
+        for proj in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            s[p + "self_attn." + proj + ".weight"] = (d, d)
+            s[p + "self_attn." + proj + ".bias"] = (d,)
+        s[p + "self_attn.relative_k_proj.weight"] = (d, d)
+        s[p + "self_attn.bias_u"] = (heads, d // heads)
+        s[p + "self_attn.bias_v"] = (heads, d // heads)
+        s[p + "conv.pointwise_conv1.weight"] = (2 * d, d, 1)
+        s[p + "conv.pointwise_conv1.bias"] = (2 * d,)
+        s[p + "conv.depthwise_conv.weight"] = (d, 1, k)
+        s[p + "conv.depthwise_conv.bias"] = (d,)
+        for n in ("weight", "bias", "running_mean", "running_var"):
+            s[p + "conv.norm." + n] = (d,)
+        s[p + "conv.pointwise_conv2.weight"] = (d, d, 1)
+        s[p + "conv.pointwise_conv2.bias"] = (d,)
+        for ln in ("norm_feed_forward1", "norm_self_att", "norm_conv", "norm_feed_forward2", "norm_out"):
+            s[p + ln + ".weight"] = (d,)
+            s[p + ln + ".bias"] = (d,)
+    return s
+
+
+def seeded_encoder_weights(layers: int, seed: int, std: float = 0.02, plain_norms: bool = True, **shape_kw) -> dict:
+    """N(0, std) for every matrix, bias and u/v.  plain_norms=True: LayerNorm gamma 1 / beta 0 and
+    BatchNorm gamma 1, beta 0, mean 0, var 1 (the benchmark configuration); False: seeded
+    non-trivial values so that tests exercise every parameter."""
+    w = {}
+    for name, shape in encoder_weight_shapes(layers, **shape_kw).items():
+        is_norm = ".norm" in name or "norm_" in name
+        if is_norm:
+            if plain_norms:
+                v = np.ones(shape, np.float32) if name.endswith(("weight", "running_var")) else np.zeros(shape, np.float32)
+            elif name.endswith("running_var"):
+                v = 0.5 + np.abs(normal_tensor(name, shape, 0.5, seed))
+            elif name.endswith("weight"):
+                v = 1.0 + normal_tensor(name, shape, 0.1, seed)
+            else:
+                v = normal_tensor(name, shape, 0.1, seed)
+        else:
+            v = normal_tensor(name, shape, std, seed)
+        w[name] = v.astype(np.float32)
+    return w
+
+
+DECODER_SHAPES = {
+    "predictor.embedding": (1025, 640),
+    "predictor.lstm.weight_ih": (2, 2560, 640),
+    "predictor.lstm.weight_hh": (2, 2560, 640),
+    "predictor.lstm.bias_ih": (2, 2560),
+    "predictor.lstm.bias_hh": (2, 2560),
+    "joint.enc.weight": (640, 1024),
+    "joint.enc.bias": (640,),
+    "joint.pred.weight": (640, 640),
+    "joint.pred.bias": (640,),
+    "joint.out.weight": (1030, 640),
+    "joint.out.bias": (1030,),
+}
+
+
+def seeded_decoder_weights(seed: int, std: float = 0.05) -> dict:
+    """Predictor / joint weights: N(0, std) per tensor, named as sb_model_load expects."""
+    return {k: normal_tensor(k, shp, std, seed) for k, shp in DECODER_SHAPES.items()}
+
+
+def seeded_model(layers: int, encoder_seed: int = 2, decoder_seed: int = 3) -> dict:
+    """The benchmark model: encoder N(0, 0.02) with identity norms, predictor / joint N(0, 0.05)."""
+    w = seeded_encoder_weights(layers, seed=encoder_seed, std=0.02, plain_norms=True)
+    w.update(seeded_decoder_weights(decoder_seed, std=0.05))
+    return w

@@ -140,10 +140,13 @@ def test_text_decode_known_answers():
     assert r.text == "" and r.tokens == [] and r.chunks == [] and r.duration_seconds == 2.5
 
 
-VOCAB = ["▁the", "▁a", "a", "s", "1", "23", "▁", "<unk>", "<pad>", "é", "▁Ünï", "ß", "", "x1", "▁4", "<blk>"]
+# letters from well outside Latin: Thai above U+0E30, a Hebrew presentation form, Latin Extended-D, a Roman numeral
+# (category Nl), Cherokee, a supplementary-plane letter, and a non-letter symbol
+VOCAB = ["▁the", "▁a", "a", "s", "1", "23", "▁", "<unk>", "<pad>", "é", "▁Ünï", "ß", "", "x1", "▁4", "<blk>",
+         "ไ", "\ufb2a", "\ua7b5", "\u2167", "\u13a0", "\U00010400", "\u2603", "7"]
 
 
-@given(st.lists(st.tuples(st.integers(0, 17), st.integers(0, 6)), max_size=25), st.floats(0.0, 40.0))
+@given(st.lists(st.tuples(st.integers(0, 25), st.integers(0, 6)), max_size=25), st.floats(0.0, 40.0))
 @settings(max_examples=120, deadline=None)
 def test_text_decode_matches_oracle(items, duration):
     tok = [t for t, _ in items]

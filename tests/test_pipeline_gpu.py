@@ -18,14 +18,18 @@ LAYERS = 2
 VOCAB = [f"▁w{i}" if i % 3 == 0 else (str(i % 10) if i % 3 == 1 else chr(97 + i % 26)) for i in range(1024)] + ["<blk>"]
 
 
+def model_weights():
+    w = eo.seeded_weights(eo.EncoderConfig(layers=LAYERS), seed=21, std=0.02, plain_norms=False)
+    w.update(oracle.seeded_decoder_weights(22))
+    return w
+
+
 @pytest.fixture(scope="module")
 def pipe(ctx):
     import scriptrs_b200 as sb
 
-    w = eo.seeded_weights(eo.EncoderConfig(layers=LAYERS), seed=21, std=0.02, plain_norms=False)
-    w.update(oracle.seeded_decoder_weights(22))
     vocab = sb.Vocabulary.from_tokens(VOCAB)
-    return sb.TranscriptionPipeline.from_weights(w, vocab, encoder_layers=LAYERS, ctx=ctx)
+    return sb.TranscriptionPipeline.from_weights(model_weights(), vocab, encoder_layers=LAYERS, ctx=ctx)
 
 
 def stages_by_hand(ctx, audio, tasks):
@@ -144,3 +148,72 @@ def test_pieced_host_copy_equals_resident_path(ctx, pipe):
     shuffled = sb.transcribe_chunks(ctx, audio, [tasks[i] for i in perm])
     for k in (0, 57, n_tasks - 1):
         assert np.array_equal(shuffled[k].token_ids, host[perm[k]].token_ids)
+
+
+def test_longform_run_multi_with_two_contexts(ctx, pipe):
+    """sb_longform_run_multi with more than one context: the reference's worker pool (src/long_form.rs:266-342) with
+    one host thread per context.  Two contexts on the same GPU (own stream and workspaces each) must give the
+    single-context result token for token, whatever the worker count says about how the tasks are dealt."""
+    import scriptrs_b200 as sb
+
+    second = sb.Context(0)
+    try:
+        sb.load_model(second, model_weights(), LAYERS, has_encoder=True, has_decoder=True)
+        audio = synth.long_audio(1_100_000, 8)
+        assert len(sb.plan_fast(audio.size)) == 6
+        one = sb.LongFormTranscriptionPipeline(pipe).run(audio)
+        both = sb.LongFormTranscriptionPipeline(pipe, extra_contexts=[second])
+        for workers in (2, 4):
+            two = both.run_with_config(audio, sb.LongFormConfig(worker_count=workers))
+            assert two.text == one.text and two.tokens == one.tokens and two.chunks == one.chunks
+        assert len(one.tokens) > 0
+        # worker_count = 1 leaves the second context idle (long_form.rs:594-600)
+        k0 = second.kernel_launches()
+        solo = both.run_with_config(audio, sb.LongFormConfig(worker_count=1))
+        assert solo.tokens == one.tokens and second.kernel_launches() == k0
+    finally:
+        second.close()
+
+
+def test_failing_shard_fails_the_whole_call(ctx, pipe):
+    """The first error a worker reports aborts the run (src/long_form.rs:328-332).  The fault is made on the host: the
+    second context has no model, so its shard returns SB_MISSING_MODEL_ASSET while the first shard succeeds."""
+    import scriptrs_b200 as sb
+
+    empty = sb.Context(0)
+    try:
+        audio = synth.long_audio(700_000, 6)
+        both = sb.LongFormTranscriptionPipeline(pipe, extra_contexts=[empty])
+        with pytest.raises(sb.ScriptrsError) as e:
+            both.run_with_config(audio, sb.LongFormConfig(worker_count=2))
+        assert e.value.status == 3 and "weights" in e.value.message
+        # nothing was left half-freed: the healthy context still transcribes, and so does the pair with one worker
+        a = sb.LongFormTranscriptionPipeline(pipe).run(audio)
+        b = both.run_with_config(audio, sb.LongFormConfig(worker_count=1))
+        assert a.tokens == b.tokens
+    finally:
+        empty.close()
+
+
+def test_device_side_timeout_flag_fails_the_call(ctx, pipe):
+    """A kernel whose bounded wait ran out raises a flag in device memory and returns; every pipeline entry must then
+    fail with SB_TIMEOUT instead of handing back tokens computed from unfinished tiles.  The flag is raised from the
+    host here (option test_raise_device_error); no kernel waits or faults for this test."""
+    import scriptrs_b200 as sb
+
+    audio = synth.long_audio(500_000, 2)
+    tasks = sb.plan_fast(audio.size)
+    good = sb.transcribe_chunks(ctx, audio, tasks)
+    ctx.set_option("test_raise_device_error", 1)
+    with pytest.raises(sb.ScriptrsError) as e:
+        sb.transcribe_chunks(ctx, audio, tasks)
+    assert e.value.status == 10
+    # the flag was cleared by the failing call
+    again = sb.transcribe_chunks(ctx, audio, tasks)
+    for x, y in zip(good.flat(), again.flat()):
+        assert np.array_equal(x, y)
+    ctx.set_option("test_raise_device_error", 1)
+    with pytest.raises(sb.ScriptrsError) as e:
+        pipe.run(audio[:100_000])
+    assert e.value.status == 10
+    ctx.synchronize()

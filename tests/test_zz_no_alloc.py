@@ -2,8 +2,9 @@
 (an ingest thread that must not trigger cudaMalloc's device-wide synchronisation while other streams
 run, or a host whose own pool owns all device memory).  It keeps its scratch in a fixed device array
 inside the library, so the checks are: same features as the allocating entry point, bit for bit, on
-two calls in a row (the second smaller, so stale scratch from the first must not matter), and a clear
-refusal beyond the fixed capacity.  Collected last on purpose."""
+two calls in a row (the second smaller, so stale scratch from the first must not matter), a batch that
+fills the fixed capacity exactly, free device memory unchanged across calls (the property in the name),
+and clear refusals beyond the capacity and on a capturing stream.  Collected last on purpose."""
 import numpy as np
 import pytest
 
@@ -60,3 +61,57 @@ def test_unnormalised_output_and_capacity_limit(ctx):
     with pytest.raises(sb.ScriptrsError) as e:
         sb.frontend_device_noalloc(pcm.data_ptr(), too_many, b.data_ptr())
     assert e.value.status == 11 and "1024" in e.value.message
+
+
+def test_full_capacity_batch_and_no_device_allocation(ctx):
+    """1024 short clips fill the last rows of the fixed metadata and statistics regions; the result must still
+    equal the allocating entry point bit for bit, and the free device memory that the driver reports must not
+    move across the calls (the first call on the device has already happened in the tests above or happens here
+    before the measurement)."""
+    import scriptrs_b200 as sb
+
+    lens = [300 + (7 * i) % 500 for i in range(1024)]
+    clips = [synth.clip_audio(n, 3000 + i) if i % 9 else np.zeros(n, np.float32) for i, n in enumerate(lens)]
+    offs = np.zeros(1025, np.int64)
+    offs[1:] = np.cumsum(lens)
+    pcm = torch.from_numpy(np.concatenate(clips)).cuda()
+    rows = sum(sb.num_frames(n) for n in lens)
+    ref = torch.full((rows, 128), float("nan"), device="cuda")
+    got = torch.full((rows, 128), float("nan"), device="cuda")
+    sb.ParakeetFeatureExtractor(ctx).extract_device(pcm.data_ptr(), offs, ref.data_ptr())
+    ctx.synchronize()
+    sb.frontend_device_noalloc(pcm.data_ptr(), offs, got.data_ptr())   # first call on the device at the latest
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(2):
+        got.fill_(float("nan"))
+        sb.frontend_device_noalloc(pcm.data_ptr(), offs, got.data_ptr())
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free0
+        assert torch.equal(ref, got)
+
+
+def test_call_on_a_capturing_stream_is_refused(ctx):
+    import scriptrs_b200 as sb
+
+    clip = synth.clip_audio(16000, 6)
+    pcm = torch.from_numpy(clip).cuda()
+    offs = np.array([0, clip.size], np.int64)
+    out = torch.empty(sb.num_frames(clip.size), 128, device="cuda")
+    sb.frontend_device_noalloc(pcm.data_ptr(), offs, out.data_ptr())
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        graph.capture_begin(capture_error_mode="thread_local")
+        try:
+            with pytest.raises(sb.ScriptrsError) as e:
+                sb.frontend_device_noalloc(pcm.data_ptr(), offs, out.data_ptr(), stream=stream.cuda_stream)
+            out.zero_()  # the capture records at least one node
+        finally:
+            graph.capture_end()
+    assert e.value.status == 11 and "capture" in e.value.message
+    # and the entry point still works afterwards
+    sb.frontend_device_noalloc(pcm.data_ptr(), offs, out.data_ptr())
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all()
