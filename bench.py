@@ -50,8 +50,9 @@ class ClockSampler:
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, period_ms: int = 100):
         self.gpu_index = gpu_index
+        self.period_ms = period_ms
         self.proc = None
         self.path = None
 
@@ -61,7 +62,7 @@ class ClockSampler:
             os.close(fd)
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", str(self.period_ms),
                  "-i", str(self.gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -196,7 +197,7 @@ def measure_frontend(ctx, sb, torch, stream, device, rank, world, local, n_clips
     def step(normalize=True):
         fx.extract_device(pcm.data_ptr(), offs, feats.data_ptr(), normalize=normalize)
 
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(local, period_ms=20)
     sampler.start()
     with torch.cuda.stream(stream):
         for _ in range(warmup):
@@ -378,6 +379,7 @@ def run_longform(args, rank, world, local):
     sb.load_model(ctx, seeded_model(layers), encoder_layers=layers, has_encoder=True, has_decoder=True, fp8_weights=both)
     if fp8:
         ctx.set_option("fp8", 1)
+        ctx.set_option("fp8_mask", args.fp8_mask)
     vocab = sb.Vocabulary.from_tokens(bench_vocab_tokens())
 
     n = int(args.hours * 3600 * 16000)
@@ -452,26 +454,38 @@ def run_longform(args, rank, world, local):
 
     # the other precision of the encoder GEMMs, same device-resident step (reported beside the headline, which stays
     # at the precision asked for on the command line)
-    variant = None
-    if both and not fp8:
+    def time_variant(mask, steps_v):
         ctx.set_option("fp8", 1)
+        ctx.set_option("fp8_mask", mask)
         device_step()
         barrier_sync(world)
         va, vb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         va.record(stream)
         t0 = time.perf_counter()
-        v_steps = max(1, min(args.steps, 3))
-        for _ in range(v_steps):
+        for _ in range(steps_v):
             device_step()
         vb.record(stream)
         stream.synchronize()
         v_wall = (time.perf_counter() - t0) * 1e3
         barrier_sync(world)
-        v_ms = max_over_ranks(max(va.elapsed_time(vb), v_wall), world, device) / v_steps
-        ctx.set_option("fp8", 0)
+        v_ms = max_over_ranks(max(va.elapsed_time(vb), v_wall), world, device) / steps_v
+        ctx.set_option("fp8_mask", args.fp8_mask)
+        ctx.set_option("fp8", 1 if fp8 else 0)
+        return v_ms
+
+    variant = None
+    if both and not fp8:
+        v_steps = max(1, min(args.steps, 3))
+        v_ms = time_variant(15, v_steps)
+        g_ms = time_variant(8, v_steps)
         variant = {"dtype": "fp8_e4m3 (ff/qkv/pointwise GEMMs) + bf16", "value": audio_s / (v_ms * 1e-3),
-                   "unit": "audio-sec/sec", "ms_per_step": v_ms, "steps": v_steps,
-                   "note": "same step with the Conformer GEMMs in e4m3 (per-row activation, per-channel weight scales)"}
+                   "unit": "audio-sec/sec", "ms_per_step": v_ms, "steps": v_steps, "fp8_mask": 15,
+                   "parity": "goal missed: 1.0e-1 relative L2 error of the encoder output at 24 blocks against the fp32 "
+                             "oracle (goal 5e-2); a speed figure only",
+                   "note": "same step with the Conformer feed-forward, QKV and first pointwise GEMMs in e4m3 (per-row "
+                           "activation, per-channel weight scales)",
+                   "within_goal_subset": {"fp8_mask": 8, "value": audio_s / (g_ms * 1e-3), "ms_per_step": g_ms,
+                                          "parity": "8.0e-3 at 24 blocks (goal 5e-2): first pointwise GEMM in e4m3 only"}}
 
     # dominant kernel, live: the tcgen05 GEMM at the feed-forward shape of one encoder group
     m_rows = min(sum(sb.encoder_num_frames(sb.num_frames(t[1] - t[0])) for t in mine), 46000)
@@ -508,10 +522,12 @@ def run_longform(args, rank, world, local):
     if both:
         # the same profiled step with the Conformer GEMMs in e4m3, and the FP8 tensor peak of this GPU as a yardstick
         ctx.set_option("fp8", 1)
+        ctx.set_option("fp8_mask", 15)
         device_step()
         ctx.profile_report()
         device_step()
         k8 = ctx.profile_report()
+        ctx.set_option("fp8_mask", args.fp8_mask)
         ctx.set_option("fp8", 1 if fp8 else 0)
         fp8_report = fp8_gemm_report(k8, enc_rows, layers, torch, device, stream)
     ctx.set_profiling(False)
@@ -534,11 +550,11 @@ def run_longform(args, rank, world, local):
     frontend = None
     if not args.no_frontend_line:
         del d_audio
-        fm = measure_frontend(ctx, sb, torch, stream, device, rank, world, local, FRONTEND_CLIPS, 10, 3, peaks, peak_kind)
+        fm = measure_frontend(ctx, sb, torch, stream, device, rank, world, local, FRONTEND_CLIPS, 60, 3, peaks, peak_kind)
         frontend = {k: fm[k] for k in ("ms_per_step", "kernel_ms", "algorithmic_bytes", "gbs", "frac", "kernel_gbs",
                                        "kernel_frac", "peak_gbs", "peak_source", "clocks")}
         frontend.update(workload=f"config 1: {FRONTEND_CLIPS} clips x 30 s per GPU, 10% silent, inputs resident in HBM",
-                        steps=10, warmup=3, unit="GB/s (algorithmic bytes / time; frac = share of the measured HBM peak)",
+                        steps=60, warmup=3, unit="GB/s (algorithmic bytes / time; frac = share of the measured HBM peak)",
                         audio_sec_per_sec=world * FRONTEND_CLIPS * 30.0 / (fm["ms_per_step"] * 1e-3))
         del fm
 
@@ -547,7 +563,7 @@ def run_longform(args, rank, world, local):
         "metric": "audio-sec/sec (RTFx), Parakeet-TDT-0.6B long-form transcription", "value": value,
         "unit": "audio-sec/sec", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": ("fp8_e4m3 (ff/qkv/pointwise GEMMs) + bf16" if fp8 else "bf16"), "data": "synthetic",
+        "dtype": (f"fp8_e4m3 (fp8_mask {args.fp8_mask}) + bf16" if fp8 else "bf16"), "data": "synthetic",
         "config": {"workload": f"config 4: {args.hours:g} h of 16 kHz audio, overlap chunks of 14.88 s + 2 s overlap "
                                f"({len(tasks)} tasks), frontend -> bf16 FastConformer ({layers} blocks) -> TDT greedy "
                                f"decode -> overlap merge", "tasks": len(tasks), "tasks_per_gpu": len(mine),
@@ -759,6 +775,8 @@ def main():
     ap.add_argument("--workload", default="longform", choices=["longform", "frontend"])
     ap.add_argument("--hours", type=float, default=8.0, help="longform workload: hours of audio (default 8)")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8"], help="longform: encoder GEMM precision")
+    ap.add_argument("--fp8-mask", type=int, default=8, help="longform, --precision fp8: GEMM groups in e4m3 (1 ff up, 2 ff "
+                    "down, 4 QKV, 8 first pointwise; 8 keeps the encoder within its 5e-2 accuracy goal, 15 = all)")
     ap.add_argument("--layers", type=int, default=24, help="longform workload: Conformer blocks (default 24)")
     ap.add_argument("--clips", type=int, default=0, help="frontend workload: clips per GPU (default 1024)")
     ap.add_argument("--stage-breakdown", action="store_true", help="longform: also time the three stage entry points")

@@ -69,7 +69,8 @@ struct sb_ctx {
     sb::Model* model = nullptr;
     sb::Profiler prof;
     bool fp8 = false;             // FP8 e4m3 GEMMs in the Conformer blocks (needs fp8 weights)
-    int fp8_mask = 15;            // which GEMMs take the FP8 path: 1 ff up, 2 ff down, 4 QKV, 8 first pointwise
+    int fp8_mask = 8;             // which GEMMs take the FP8 path: 1 ff up, 2 ff down, 4 QKV, 8 first pointwise
+                                  // (default: the subset that keeps the encoder within 5e-2 of the fp32 oracle)
     bool fp8_hidden_amax = false; // FP8 feed-forward: quantise the hidden row by its true maximum (one more pass) instead of a bound
     bool simt_decode = false;     // fp32 CUDA-core decoder (one persistent kernel) instead of the tensor-core steps
     bool simt_attention = false;  // reference implementation of the attention kernel on CUDA cores (tests)

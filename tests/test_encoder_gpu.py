@@ -95,19 +95,14 @@ def test_too_many_feature_frames_is_rejected(ctx):
     assert e.value.status == 6
 
 
-# The stated goal for the FP8 variant is 5e-2.  With seeded random weights it is NOT met: every Conformer
-# branch output is as large as the residual stream (the stream norm is 1 after each block's final
-# LayerNorm, the sub-sampling output it starts from has norm 0.03), so the ~3.6 % rms rounding error of
-# each e4m3 operand (3 mantissa bits) reaches the output undamped; four FP8 GEMM kinds give 9-10 %
-# at any depth, one kind alone 6 %.  The bound below is what the arithmetic can hold; the miss is
-# recorded in the design notes.
+# The stated goal for the FP8 variant is 5e-2 relative L2 error against the fp32 oracle.  With the seeded random
+# weights only the first pointwise convolution of the convolution module can run in e4m3 within that goal (the
+# library's default fp8_mask = 8); each of the other GEMM groups alone already exceeds it at depth, so the all-groups variant is an expected failure below,
+# asserted against the goal itself and not against a loosened bound.
 FP8_GOAL = 5e-2
-FP8_TOL = 1.2e-1
 
 
-@pytest.mark.parametrize("layers", [1, 2, 4])
-def test_fp8_variant_matches_oracle(ctx, layers):
-    """FP8 e4m3 feed-forward / QKV / pointwise GEMMs against the fp32 oracle (see FP8_TOL above)."""
+def fp8_errors(ctx, layers, mask):
     import scriptrs_b200 as sb
 
     cfg = eo.EncoderConfig(layers=layers)
@@ -116,19 +111,36 @@ def test_fp8_variant_matches_oracle(ctx, layers):
     rng = np.random.default_rng(layers)
     feats = [rng.standard_normal((t, 128)).astype(np.float32) for t in (1001, 203, 1497, 9)]
     ctx.set_option("fp8", 1)
+    if mask is not None:
+        ctx.set_option("fp8_mask", mask)
     try:
         got = run_gpu(ctx, feats)
     finally:
+        ctx.set_option("fp8_mask", 8)
         ctx.set_option("fp8", 0)
     bf = run_gpu(ctx, feats)
+    out = []
     for f, g, b in zip(feats, got, bf):
         r = eo.encoder_forward(w, f, cfg)
-        err = np.linalg.norm(g - r) / np.linalg.norm(r)
-        err_bf = np.linalg.norm(b - r) / np.linalg.norm(r)
         assert np.isfinite(g).all()
-        assert err <= FP8_TOL, (layers, f.shape[0], err)
-        assert err_bf <= BF16_TOL
+        assert np.linalg.norm(b - r) / np.linalg.norm(r) <= BF16_TOL
         assert not np.array_equal(g, b)  # the switch really changes the arithmetic
+        out.append(float(np.linalg.norm(g - r) / np.linalg.norm(r)))
+    return out
+
+
+@pytest.mark.parametrize("layers", [1, 2, 4])
+def test_fp8_default_subset_meets_goal(ctx, layers):
+    """The default FP8 configuration (fp8_mask = 8: first pointwise convolution in e4m3) against the fp32 oracle."""
+    errs = fp8_errors(ctx, layers, None)
+    assert max(errs) <= FP8_GOAL, (layers, errs)
+
+
+@pytest.mark.xfail(strict=True, reason="goal missed: feed-forward, QKV and pointwise GEMMs all in e4m3 give 7.2e-2 at 4 "
+                                       "blocks and 1.0e-1 at 24 with N(0, 0.02) random weights (goal 5e-2)")
+def test_fp8_all_gemm_groups_meet_goal(ctx):
+    errs = fp8_errors(ctx, 4, 15)
+    assert max(errs) <= FP8_GOAL, errs
 
 
 def test_fp8_needs_fp8_weights(ctx):
