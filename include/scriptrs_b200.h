@@ -148,6 +148,12 @@ int64_t sb_frontend_num_frames(int64_t n_samples);
 int32_t sb_frontend_device(sb_ctx* ctx, const float* d_pcm, const int64_t* clip_offsets, int64_t n_clips,
                            float preemphasis, int32_t normalize, float* d_feats, int64_t* frame_offsets);
 
+/* The same for 16-bit PCM (d_pcm holds int16 samples): each sample is converted as value / 32767 in f32, the
+ * conversion of the reference's WAV reader for 16-bit files (examples/transcribe_wav.rs:341-347), inside the
+ * kernel's sample read, so the features equal those of sb_frontend_device on the converted buffer bit for bit. */
+int32_t sb_frontend_device_i16(sb_ctx* ctx, const int16_t* d_pcm, const int64_t* clip_offsets, int64_t n_clips,
+                               float preemphasis, int32_t normalize, float* d_feats, int64_t* frame_offsets);
+
 /* Same through host buffers: copies the PCM in, runs, copies the features out. */
 int32_t sb_frontend_host(sb_ctx* ctx, const float* pcm, const int64_t* clip_offsets, int64_t n_clips,
                          float preemphasis, int32_t normalize, float* feats, int64_t* frame_offsets);
@@ -158,9 +164,9 @@ int32_t sb_frontend_host(sb_ctx* ctx, const float* pcm, const int64_t* clip_offs
  * than any before, and cudaMalloc / cudaFree synchronise the whole device.  That is wrong for an
  * ingest thread that extracts features while other streams of the same GPU encode and decode, and
  * impossible for a host that has given all device memory to its own pool.  This variant needs no
- * context and calls no cudaMalloc, cudaFree or allocating library routine: tables, clip metadata
- * and the per-(clip, feature) statistics live in a device array of fixed size (about 1.1 MB) that
- * every GPU loading the library holds until the process exits.
+ * context and calls no cudaMalloc, cudaFree or allocating library routine: tables and clip metadata
+ * live in a device array of fixed size (about 32 KB) that every GPU loading the library holds until the
+ * process exits.
  *   - at most 1024 clips per call; more fails with SB_INVALID_ARGUMENT;
  *   - runs on the CURRENT device, on `stream` (a cudaStream_t; NULL = default stream); arguments and
  *     results are those of sb_frontend_device, bit for bit;
@@ -207,6 +213,21 @@ typedef struct sb_model_desc {
  * "predictor.lstm.{weight_ih,weight_hh,bias_ih,bias_hh}" (layers stacked, gate order i,f,g,o),
  * "joint.{enc,pred,out}.{weight,bias}".  A missing tensor fails with SB_MISSING_MODEL_ASSET. */
 int32_t sb_model_load(sb_ctx* ctx, const sb_model_desc* desc, const sb_tensor* tensors, int64_t n_tensors);
+
+/* The same from a weight file on disk: ModelBundle::from_dir + validate_base (src/models.rs:31-66) with one file in
+ * place of the reference's three compiled CoreML model directories.  The file uses the safetensors layout: 8 bytes
+ * little-endian header length N, N bytes of JSON {"<tensor name>": {"dtype": "F32" | "F16" | "BF16", "shape": [...],
+ * "data_offsets": [begin, end]}, ..., optional "__metadata__": {...}}, then the tensor bytes (offsets count from the
+ * end of the header; row-major, little-endian).  Tensor names are those listed for sb_model_load, optionally behind
+ * `name_prefix` (e.g. "encoder."; NULL for none; tensors without the prefix are ignored).  F16 / BF16 tensors are
+ * widened to f32 on load.  desc->encoder_layers < 0 takes the number of "layers.<i>." blocks found in the file.
+ * A path that does not exist fails with SB_MISSING_MODEL_ASSET (MissingModelAsset { path }), an unreadable or
+ * malformed file with SB_IO, a missing or mis-shaped tensor with SB_MISSING_MODEL_ASSET. */
+int32_t sb_model_load_file(sb_ctx* ctx, const sb_model_desc* desc, const char* path, const char* name_prefix);
+
+/* Host only (no GPU needed): the tensors of a weight file as text lines "name dtype d0xd1x...", written into buf
+ * (NUL terminated, truncated to cap).  Returns the full length, or minus an sb_status on failure. */
+int64_t sb_weights_file_list(const char* path, char* buf, int64_t cap);
 
 /* ---------------------------------------------------------------- encoder */
 
@@ -336,6 +357,13 @@ void sb_raw_batch_free(sb_raw_batch* b);
  * cfg->max_audio_samples with SB_AUDIO_TOO_LONG.  cfg may be NULL for the defaults. */
 int32_t sb_transcribe_chunks(sb_ctx* ctx, const float* audio, int64_t n_samples, const sb_chunk_task* tasks,
                              int64_t n_tasks, const sb_transcription_config* cfg, sb_raw_batch** out);
+
+/* The same for a 16-bit PCM recording in host memory: half the bytes cross to the GPU, and the conversion to
+ * f32 (value / 32767, examples/transcribe_wav.rs:341-347, which the reference's caller does per sample on the
+ * CPU before run()) happens inside the frontend kernel.  Token streams equal those of sb_transcribe_chunks on
+ * the converted recording. */
+int32_t sb_transcribe_chunks_i16(sb_ctx* ctx, const int16_t* audio, int64_t n_samples, const sb_chunk_task* tasks,
+                                 int64_t n_tasks, const sb_transcription_config* cfg, sb_raw_batch** out);
 
 /* The same with the recording already in device memory (d_audio is a device pointer). */
 int32_t sb_transcribe_chunks_device(sb_ctx* ctx, const float* d_audio, int64_t n_samples, const sb_chunk_task* tasks,

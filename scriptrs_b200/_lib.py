@@ -72,9 +72,12 @@ SIGNATURES = {
     "sb_frontend_tables": (_I32, [_VP, _VP]),
     "sb_frontend_num_frames": (_I64, [_I64]),
     "sb_frontend_device": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
+    "sb_frontend_device_i16": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
     "sb_frontend_host": (_I32, [_VP, _VP, _VP, _I64, C.c_float, _I32, _VP, _VP]),
     "sb_frontend_device_noalloc": (_I32, [_VP, _VP, _I64, C.c_float, _I32, _VP, _VP, _VP]),
     "sb_model_load": (_I32, [_VP, C.POINTER(ModelDescC), C.POINTER(TensorC), _I64]),
+    "sb_model_load_file": (_I32, [_VP, C.POINTER(ModelDescC), C.c_char_p, C.c_char_p]),
+    "sb_weights_file_list": (_I64, [C.c_char_p, C.c_char_p, _I64]),
     "sb_encoder_num_frames": (_I64, [_I64]),
     "sb_encode_device": (_I32, [_VP, _VP, _VP, _I64, _VP, _VP]),
     "sb_tdt_decode_device": (_I32, [_VP, _VP, _VP, _I64, _I64, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _VP]),
@@ -107,6 +110,7 @@ SIGNATURES = {
     "sb_raw_batch_flatten": (_I32, [_VP, _VP, _VP, _VP, _VP, _VP]),
     "sb_raw_batch_free": (None, [_VP]),
     "sb_transcribe_chunks": (_I32, [_VP, _VP, _I64, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),
+    "sb_transcribe_chunks_i16": (_I32, [_VP, _VP, _I64, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),
     "sb_transcribe_chunks_device": (_I32, [_VP, _VP, _I64, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),
     "sb_pipeline_run": (_I32, [_VP, _VP, _VP, _I64, C.POINTER(TranscriptionConfigC), C.POINTER(_VP)]),
     "sb_longform_run": (_I32, [_VP, _VP, _VP, _I64, C.POINTER(LongFormConfigC), C.POINTER(_VP)]),

@@ -146,14 +146,16 @@ class ParakeetFeatureExtractor:
                                           float(self.config.preemphasis), int(normalize), _ptr(feats), _ptr(fo)))
         return [feats[fo[i]:fo[i + 1]] for i in range(len(clips))]
 
-    def extract_device(self, d_pcm: int, clip_offsets: np.ndarray, d_feats: int, normalize: bool = True):
-        """Device pointers in and out; asynchronous on the context's stream.  Returns frame offsets."""
+    def extract_device(self, d_pcm: int, clip_offsets: np.ndarray, d_feats: int, normalize: bool = True,
+                       int16: bool = False):
+        """Device pointers in and out; asynchronous on the context's stream.  Returns frame offsets.
+        int16=True: d_pcm holds 16-bit PCM (converted as value / 32767 inside the kernel)."""
         clip_offsets = np.ascontiguousarray(clip_offsets, np.int64)
         n = clip_offsets.size - 1
         fo = np.zeros(n + 1, np.int64)
-        check(_lib.lib().sb_frontend_device(self.ctx.handle, C.c_void_p(d_pcm), _ptr(clip_offsets), n,
-                                            float(self.config.preemphasis), int(normalize), C.c_void_p(d_feats),
-                                            _ptr(fo)))
+        fn = _lib.lib().sb_frontend_device_i16 if int16 else _lib.lib().sb_frontend_device
+        check(fn(self.ctx.handle, C.c_void_p(d_pcm), _ptr(clip_offsets), n, float(self.config.preemphasis),
+                 int(normalize), C.c_void_p(d_feats), _ptr(fo)))
         return fo
 
 

@@ -2,6 +2,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <string>
@@ -11,6 +12,7 @@
 #include "context.h"
 #include "encoder.h"
 #include "gemm.h"
+#include "host/weights_file.h"
 #include "model.h"
 #include "pipeline.h"
 
@@ -107,37 +109,35 @@ void sb_model_free_internal(sb_ctx*);
 namespace sb {
 
 // Shared by the public frontend entry points and the chunk pipeline.  Asynchronous on the stream.
-int32_t frontend_run(sb_ctx* c, const float* d_pcm, const int64_t* clip_start, const int64_t* clip_len,
+int32_t frontend_run(sb_ctx* c, const void* d_pcm, SampleFormat fmt, const int64_t* clip_start, const int64_t* clip_len,
                      int64_t n_clips, float preemphasis, bool normalize, float* d_feats, int64_t* frame_offsets) {
-    if (n_clips > 65535) return fail(SB_INVALID_ARGUMENT, "at most 65535 clips per call");
+    if (n_clips > (int64_t)1 << 30) return fail(SB_INVALID_ARGUMENT, "too many clips in one call");
     const size_t n1 = static_cast<size_t>(n_clips) + 1;
     std::vector<int64_t> meta(3 * n1);  // starts | lens | frame prefix sums
     int64_t* fo = meta.data() + 2 * n1;
     fo[0] = 0;
-    int64_t max_frames = 0;
     for (int64_t i = 0; i < n_clips; ++i) {
         if (clip_len[i] <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // frontend.rs:105
         meta[i] = clip_start[i];
         meta[n1 + i] = clip_len[i];
         const int64_t t = frames_for_samples(clip_len[i]);
+        if (t > INT32_MAX / 2) return fail(SB_INVALID_ARGUMENT, "clip too long");
         fo[i + 1] = fo[i] + t;
-        if (t > max_frames) max_frames = t;
     }
-    if (max_frames > (int64_t)65535 * 32) return fail(SB_INVALID_ARGUMENT, "clip too long for one launch");
     if (frame_offsets) std::memcpy(frame_offsets, fo, sizeof(int64_t) * n1);
     SB_CUDA(cudaSetDevice(c->device));
     SB_CUDA(c->clip_off.ensure(sizeof(int64_t) * 3 * n1));
-    SB_CUDA(c->col_mean.ensure(sizeof(float) * kMels * static_cast<size_t>(n_clips)));
-    SB_CUDA(c->col_std.ensure(sizeof(float) * kMels * static_cast<size_t>(n_clips)));
     // pageable source: the copy is staged before the call returns, so the vector may go out of scope
     SB_CUDA(cudaMemcpyAsync(c->clip_off.p, meta.data(), sizeof(int64_t) * 3 * n1, cudaMemcpyHostToDevice, c->stream));
     const int64_t* d_meta = c->clip_off.as<int64_t>();
-    c->prof.begin("frontend(3 kernels)", c->stream);
-    SB_CUDA(frontend_launch(d_pcm, d_meta, d_meta + n1, d_meta + 2 * n1, (int)n_clips, (int)max_frames, preemphasis,
-                            c->d_tables, d_feats, c->col_mean.as<float>(), c->col_std.as<float>(), normalize,
-                            c->stream));
+    c->prof.begin("frontend", c->stream);
+    cudaError_t e = frontend_launch(d_pcm, fmt, d_meta, d_meta + n1, d_meta + 2 * n1, (int)n_clips, preemphasis,
+                                    c->d_tables, d_feats, normalize, c->stream);
     c->prof.end(c->stream);
-    c->launches += normalize ? 3 : 1;
+    if (e == cudaErrorMisalignedAddress)
+        return fail(SB_INVALID_ARGUMENT, "the feature buffer must be 16-byte aligned and the PCM buffer aligned to its sample type");
+    SB_CUDA(e);
+    c->launches += 1;
     return SB_OK;
 }
 
@@ -244,8 +244,6 @@ void sb_ctx_destroy(sb_ctx* c) {
     sb_model_free_internal(c);
     c->clip_off.release();
     c->frame_off.release();
-    c->col_mean.release();
-    c->col_std.release();
     c->pcm_stage.release();
     c->feat_stage.release();
     c->enc_stage.release();
@@ -328,8 +326,9 @@ int32_t sb_frontend_tables(float* window, float* filterbank) {
 
 int64_t sb_frontend_num_frames(int64_t n_samples) { return n_samples <= 0 ? 0 : frames_for_samples(n_samples); }
 
-int32_t sb_frontend_device(sb_ctx* c, const float* d_pcm, const int64_t* clip_offsets, int64_t n_clips,
-                           float preemphasis, int32_t normalize, float* d_feats, int64_t* frame_offsets) {
+static int32_t frontend_device_any(sb_ctx* c, const void* d_pcm, SampleFormat fmt, const int64_t* clip_offsets,
+                                   int64_t n_clips, float preemphasis, int32_t normalize, float* d_feats,
+                                   int64_t* frame_offsets) {
     if (!c || !clip_offsets || !d_pcm || !d_feats) return fail(SB_INVALID_ARGUMENT, "null argument");
     if (n_clips <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");
     std::vector<int64_t> start(static_cast<size_t>(n_clips)), len(static_cast<size_t>(n_clips));
@@ -337,8 +336,18 @@ int32_t sb_frontend_device(sb_ctx* c, const float* d_pcm, const int64_t* clip_of
         start[i] = clip_offsets[i];
         len[i] = clip_offsets[i + 1] - clip_offsets[i];
     }
-    return frontend_run(c, d_pcm, start.data(), len.data(), n_clips, preemphasis, normalize != 0, d_feats,
+    return frontend_run(c, d_pcm, fmt, start.data(), len.data(), n_clips, preemphasis, normalize != 0, d_feats,
                         frame_offsets);
+}
+
+int32_t sb_frontend_device(sb_ctx* c, const float* d_pcm, const int64_t* clip_offsets, int64_t n_clips,
+                           float preemphasis, int32_t normalize, float* d_feats, int64_t* frame_offsets) {
+    return frontend_device_any(c, d_pcm, kSampleF32, clip_offsets, n_clips, preemphasis, normalize, d_feats, frame_offsets);
+}
+
+int32_t sb_frontend_device_i16(sb_ctx* c, const int16_t* d_pcm, const int64_t* clip_offsets, int64_t n_clips,
+                               float preemphasis, int32_t normalize, float* d_feats, int64_t* frame_offsets) {
+    return frontend_device_any(c, d_pcm, kSampleI16, clip_offsets, n_clips, preemphasis, normalize, d_feats, frame_offsets);
 }
 
 int32_t sb_frontend_host(sb_ctx* c, const float* pcm, const int64_t* clip_offsets, int64_t n_clips,
@@ -372,6 +381,56 @@ int32_t sb_frontend_host(sb_ctx* c, const float* pcm, const int64_t* clip_offset
 
 int32_t sb_model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensors, int64_t n_tensors) {
     return model_load(c, desc, tensors, n_tensors);
+}
+
+int32_t sb_model_load_file(sb_ctx* c, const sb_model_desc* desc, const char* path, const char* name_prefix) {
+    if (!c || !desc || !path) return fail(SB_INVALID_ARGUMENT, "null argument");
+    WeightFile wf;
+    bool missing = false;
+    const std::string err = weight_file_open(path, &wf, &missing);
+    if (!err.empty()) return fail(missing ? SB_MISSING_MODEL_ASSET : SB_IO, err);  // models.rs:53-66
+    const std::string prefix = name_prefix ? name_prefix : "";
+    std::vector<std::string> names;
+    std::vector<sb_tensor> tensors;
+    names.reserve(wf.entries.size());
+    int max_layer = -1;
+    for (auto& kv : wf.entries) {
+        if (kv.first.compare(0, prefix.size(), prefix) != 0) continue;
+        names.push_back(kv.first.substr(prefix.size()));
+        const std::string& n = names.back();
+        if (n.compare(0, 7, "layers.") == 0) max_layer = std::max(max_layer, std::atoi(n.c_str() + 7));
+    }
+    size_t k = 0;
+    for (auto& kv : wf.entries) {
+        if (kv.first.compare(0, prefix.size(), prefix) != 0) continue;
+        const float* data = wf.as_f32(kv.first);
+        tensors.push_back(sb_tensor{names[k].c_str(), data, kv.second.numel()});
+        ++k;
+    }
+    sb_model_desc d = *desc;
+    if (d.encoder_layers < 0) d.encoder_layers = max_layer + 1;  // as many Conformer blocks as the file holds
+    return model_load(c, &d, tensors.data(), (int64_t)tensors.size());
+}
+
+int64_t sb_weights_file_list(const char* path, char* buf, int64_t cap) {
+    if (!path) return -(int64_t)fail(SB_INVALID_ARGUMENT, "null argument");
+    WeightFile wf;
+    bool missing = false;
+    const std::string err = weight_file_open(path, &wf, &missing);
+    if (!err.empty()) return -(int64_t)fail(missing ? SB_MISSING_MODEL_ASSET : SB_IO, err);
+    std::string out;
+    for (auto& kv : wf.entries) {
+        out += kv.first + " " + kv.second.dtype + " ";
+        for (size_t i = 0; i < kv.second.shape.size(); ++i) out += (i ? "x" : "") + std::to_string(kv.second.shape[i]);
+        if (kv.second.shape.empty()) out += "scalar";
+        out += "\n";
+    }
+    if (buf && cap > 0) {
+        const size_t n = std::min<size_t>(out.size(), (size_t)cap - 1);
+        std::memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    return (int64_t)out.size();
 }
 
 int64_t sb_encoder_num_frames(int64_t feature_frames) {

@@ -35,8 +35,11 @@ RawTokens raw_from_arrays(const uint32_t* tok, const int64_t* frm, const int64_t
 
 // Frontend -> encoder -> decoder for a set of tasks over one host PCM buffer; the reference's
 // transcribe_task (src/long_form.rs:584-592) for a whole batch at once.
-int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const sb_chunk_task* tasks, int64_t n_tasks,
-                         const sb_transcription_config& cfg, std::vector<RawTokens>* out, bool pcm_on_device = false) {
+int32_t transcribe_tasks(sb_ctx* c, const void* pcm_any, int64_t n_samples, const sb_chunk_task* tasks, int64_t n_tasks,
+                         const sb_transcription_config& cfg, std::vector<RawTokens>* out, bool pcm_on_device = false,
+                         SampleFormat fmt = kSampleF32) {
+    const size_t esz = fmt == kSampleI16 ? sizeof(int16_t) : sizeof(float);
+    const char* pcm = static_cast<const char*>(pcm_any);
     out->clear();
     if (n_tasks == 0) return SB_OK;
     if (!c->model || !c->model->has_encoder || !c->model->has_decoder)
@@ -78,14 +81,18 @@ int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const s
     if (n_tasks > 65535) return fail(SB_INVALID_ARGUMENT, "more than 65535 tasks in one batch");
     // Host PCM goes to the device in pieces on a second stream, so that all but the first piece's copy overlaps the
     // kernels of the pieces before it; frontend and encoder run piece by piece, the decoder once over everything.
-    // The first piece is small (1/16 of the tasks: little copy time exposed), the last one large (3/4: the GEMMs
-    // keep their large row counts); at PCIe rates each later copy finishes well inside the earlier pieces' compute.
-    const float* d_pcm = pcm + lo;
+    // The first piece is small (1/16 or 1/8 of the tasks: little copy time exposed), the last one large (3/4 or 7/8:
+    // the GEMMs keep their large row counts); at PCIe rates each later copy finishes well inside the earlier pieces'
+    // compute.
+    const void* d_pcm = pcm + (size_t)lo * esz;
     int n_pieces = 1;
     if (!pcm_on_device) {
-        SB_CUDA(c->pcm_stage.ensure(sizeof(float) * (size_t)(hi - lo)));
-        d_pcm = c->pcm_stage.as<float>();
-        if (ordered && n_tasks >= 512) n_pieces = 3;  // below that the extra launches cost more than the copy they hide
+        SB_CUDA(c->pcm_stage.ensure(esz * (size_t)(hi - lo)));
+        d_pcm = c->pcm_stage.p;
+        // three pieces for large batches, two (1/8 + 7/8) for medium ones: at 280 tasks the single copy of 230 MB is
+        // 4-5 ms of exposed time, the second set of launches costs about 1 ms
+        if (ordered && n_tasks >= 512) n_pieces = 3;
+        else if (ordered && n_tasks >= 64) n_pieces = 2;
         if (!c->copy_stream) SB_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
         while ((int)c->copy_events.size() < n_pieces + 1) {
             cudaEvent_t ev;
@@ -102,21 +109,22 @@ int32_t transcribe_tasks(sb_ctx* c, const float* pcm, int64_t n_samples, const s
     int64_t copied_to = lo;
     for (int p = 0; p < n_pieces; ++p) {
         // piece boundaries at 0, 1/16, 4/16, 1 of the task list (one piece: everything)
-        static const int kCut[4] = {0, 1, 4, 16};
-        const int64_t i0 = n_pieces == 1 ? 0 : n_tasks * kCut[p] / 16;
-        const int64_t i1 = n_pieces == 1 ? n_tasks : n_tasks * kCut[p + 1] / 16;
+        static const int kCut3[4] = {0, 1, 4, 16}, kCut2[3] = {0, 2, 16}, kCut1[2] = {0, 16};
+        const int* cut = n_pieces == 3 ? kCut3 : (n_pieces == 2 ? kCut2 : kCut1);
+        const int64_t i0 = n_tasks * cut[p] / 16;
+        const int64_t i1 = n_tasks * cut[p + 1] / 16;
         if (i1 <= i0) continue;
         if (!pcm_on_device) {
             const int64_t end = (p == n_pieces - 1) ? hi : tasks[i1 - 1].audio_end;
             if (end > copied_to)
-                SB_CUDA(cudaMemcpyAsync(c->pcm_stage.as<float>() + (copied_to - lo), pcm + copied_to,
-                                        sizeof(float) * (size_t)(end - copied_to), cudaMemcpyHostToDevice, c->copy_stream));
+                SB_CUDA(cudaMemcpyAsync(c->pcm_stage.as<char>() + (size_t)(copied_to - lo) * esz, pcm + (size_t)copied_to * esz,
+                                        esz * (size_t)(end - copied_to), cudaMemcpyHostToDevice, c->copy_stream));
             copied_to = std::max(copied_to, end);
             SB_CUDA(cudaEventRecord(c->copy_events[p], c->copy_stream));
             SB_CUDA(cudaStreamWaitEvent(st, c->copy_events[p], 0));
         }
         std::vector<int64_t> rel(i1 - i0 + 1);
-        int32_t s = frontend_run(c, d_pcm, start.data() + i0, len.data() + i0, i1 - i0, cfg.preemphasis, true,
+        int32_t s = frontend_run(c, d_pcm, fmt, start.data() + i0, len.data() + i0, i1 - i0, cfg.preemphasis, true,
                                  c->feat_stage.as<float>() + (size_t)fo[i0] * kMels, rel.data());
         if (s != SB_OK) return s;
         for (int64_t k = 1; k <= i1 - i0; ++k) fo[i0 + k] = fo[i0] + rel[k];
@@ -361,6 +369,23 @@ int32_t sb_transcribe_chunks(sb_ctx* c, const float* pcm, int64_t n_samples, con
     if (s != SB_OK) return s;
     sb_raw_batch* b = new sb_raw_batch();
     s = transcribe_tasks(c, pcm, n_samples, tasks, n_tasks, t, &b->items);
+    if (s != SB_OK) {
+        delete b;
+        return s;
+    }
+    *out = b;
+    return SB_OK;
+}
+
+int32_t sb_transcribe_chunks_i16(sb_ctx* c, const int16_t* pcm, int64_t n_samples, const sb_chunk_task* tasks,
+                                 int64_t n_tasks, const sb_transcription_config* cfg, sb_raw_batch** out) {
+    if (!c || !pcm || !out || (n_tasks > 0 && !tasks) || n_tasks < 0) return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_transcription_config t;
+    if (cfg) t = *cfg; else sb_default_transcription_config(&t);
+    int32_t s = check_config(t);
+    if (s != SB_OK) return s;
+    sb_raw_batch* b = new sb_raw_batch();
+    s = transcribe_tasks(c, pcm, n_samples, tasks, n_tasks, t, &b->items, false, kSampleI16);
     if (s != SB_OK) {
         delete b;
         return s;

@@ -65,7 +65,7 @@ struct sb_ctx {
     sb::FrontendTables* d_tables = nullptr;
     int* d_error = nullptr;  // set by a kernel whose bounded wait ran out
     // frontend workspaces
-    sb::Buffer clip_off, frame_off, col_mean, col_std, pcm_stage, feat_stage, enc_stage;
+    sb::Buffer clip_off, frame_off, pcm_stage, feat_stage, enc_stage;
     sb::Model* model = nullptr;
     sb::Profiler prof;
     bool fp8 = false;             // FP8 e4m3 GEMMs in the Conformer blocks (needs fp8 weights)

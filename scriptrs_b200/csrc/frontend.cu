@@ -1,4 +1,4 @@
-// Log-mel frontend for sm_100a: PCM f32 -> normalised log-mel [T x 128] per clip.
+// Log-mel frontend for sm_100a: PCM (f32 or 16-bit) -> normalised log-mel [T x 128] per clip, one kernel.
 //
 // Replaces the reference's CPU feature extractor (src/frontend.rs:104-241):
 // pre-emphasis 0.97, 256-sample zero padding on both sides, Hann window of 400
@@ -6,312 +6,302 @@
 // filterbank, ln(x + 2^-24), per-feature mean / variance normalisation over
 // all frames of the clip.
 //
-// Three kernels:
-//   logmel_kernel     a CTA walks four consecutive 32-frame tiles of a clip (tables and twiddles set up once, the
-//                     next tile's raw samples arriving by cp.async while the current one is transformed);
-//                     one warp per frame: pre-emphasised samples staged in shared
-//                     memory, 256-point complex FFT of the even/odd-packed frame
-//                     (8 x 8 x 4 decomposition: two register radix-8 passes with
-//                     one shared-memory transpose, then a radix-4 across four
-//                     adjacent lanes with shuffles), real-FFT untangling + power,
-//                     sparse mel filterbank (504 non-zero taps), ln.
-//   colstats_kernel   one thread per (clip, feature) walks the clip's frames in
-//                     order and accumulates the mean and the variance exactly as
-//                     the reference does (strictly sequential f32 sums, left to
-//                     right): for a constant column (an all-zero clip) the result
-//                     is made of the rounding residue of that sum alone, so any
-//                     other summation order gives a different answer.
-//   normalize_kernel  (v - mean) / std, elementwise, float4.
+// frontend_clip_kernel: one CTA (8 warps) per clip, two CTAs per SM.
+//   rows      The clip is walked 16 frames at a time.  The raw samples of the next 16 frames arrive by cp.async
+//             (16-byte pieces where the clip's placement allows it) while the current ones are transformed; one
+//             pass turns them into pre-emphasised, zero-padded samples (16-bit input is converted here).  Each
+//             warp then transforms two frames, sixteen lanes per frame (frontend_core.cuh: two register radix-16
+//             passes around one shared-memory transpose, untangling + power, sparse mel filterbank, ln), and leaves
+//             the two log-mel rows in a 16-row stage in shared memory.  At the top of the next step the stage is
+//             written out with 16-byte stores, and threads 0..127 add its rows to their column sums.
+//   statistics The reference sums every column strictly left to right in f32 (frontend.rs:225-236); for a constant
+//             column (an all-zero clip) the result consists of the rounding residue of exactly that order, so the
+//             order is kept: thread c owns column c.  The first sum comes from the stage (no re-read); the second
+//             pass (squared deviations) streams the clip's rows back through a cp.async ring per warp.
+//   normalise (v - mean) / std over the clip's rows, 16-byte loads and stores, all threads.
+// While one CTA of an SM is in its two bandwidth-bound tail passes the other one keeps the SM's issue slots busy
+// with transforms, so the passes cost little wall time although they re-read the clip's rows.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "frontend.h"
+#include "frontend_core.cuh"
 
 namespace sb {
 
 namespace {
 
-constexpr int kWarpsPerCta = 8;
-constexpr int kThreads = kWarpsPerCta * 32;
-constexpr int kFramesPerTile = 32;
-constexpr int kTilesPerCta = 4;                                    // consecutive tiles of one clip per CTA
-constexpr int kTileSamples = (kFramesPerTile - 1) * kHop + kWin;  // 5360
-constexpr int kRawSamples = kTileSamples + 8 + 1;                  // the tile plus the sample before it
-constexpr int kS1Stride = 36;                                      // float2 per k1 row, conflict-free
-constexpr int kWarpScratchF2 = 8 * kS1Stride;                      // 288 float2 (>= 272 for the Z layout)
-constexpr int kPowerPad = 272;                                     // 257 bins + slack for padded mel taps
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStepFrames = 2 * kWarps;                           // 16 frames per step
+constexpr int kStepSamples = (kStepFrames - 1) * kHop + kWin;    // 2800
+constexpr int kRawElems = 2816;  // the step's samples + the one before them + up to 7 of alignment shift, in 16-byte pieces
+constexpr int kRingRows = 16;    // rows per ring slot of the second statistics pass
+constexpr int kRingSlots = 4;
 
 struct __align__(16) SmemLayout {
-    float xs[2][kRawSamples + 3];          // raw samples of the current and the next tile (cp.async ring)
-    float ys[kTileSamples + 8];            // pre-emphasised, zero-padded samples of the tile
-    float window[kWin];                    // Hann window
-    float2 tw_post[132];                   // 0.5 * exp(-2*pi*i*k/512), k = 0..128
-    float melw[kMaxTaps * kMels];          // tap-major: melw[j * 128 + m]
+    float2 scratch[kWarps][2][fe::kFrameScratch];  // transpose buffer / Z per frame; the statistics ring later
+    float pw[kWarps][2][fe::kPowPad];              // power bins per frame
+    float raw[2][kRawElems];                       // raw samples of this and the next step (16-bit input: first half)
+    float ys[kRawElems];                           // pre-emphasised samples, indexed like raw
+    float stage[kStepFrames][kMels];               // log-mel rows of one step
+    float window[kWin];
+    float2 tw_post[132];
+    float2 twid[256];
+    float melw[kMelTapRows * 16];
+    float mean[kMels];
+    float stdv[kMels];
     int16_t mel_start[kMels];
-    int16_t mel_cnt[kMels];
-    float2 scratch[kWarpsPerCta][kWarpScratchF2];
-    float power[kWarpsPerCta][kPowerPad];
+};
+static_assert(sizeof(float2) * kWarps * 2 * fe::kFrameScratch >= sizeof(float) * 4 * kRingSlots * kRingRows * 32,
+              "the statistics ring must fit in the transform scratch");
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename TIn>
+struct Sample;
+template <>
+struct Sample<float> {
+    static constexpr int kPerPiece = 4;  // samples per 16 bytes
+    static __device__ __forceinline__ float get(const void* raw, int j) { return static_cast<const float*>(raw)[j]; }
+};
+template <>
+struct Sample<int16_t> {
+    static constexpr int kPerPiece = 8;
+    static __device__ __forceinline__ float get(const void* raw, int j) {
+        return fe::pcm16_to_f32(static_cast<const int16_t*>(raw)[j]);
+    }
 };
 
-__device__ __forceinline__ float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
-__device__ __forceinline__ float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
-__device__ __forceinline__ float2 cmul(float2 a, float2 b) {
-    return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
-}
-// multiply by -i
-__device__ __forceinline__ float2 mul_mi(float2 a) { return make_float2(a.y, -a.x); }
-
-// Forward 8-point DFT, natural order in and out.
-__device__ __forceinline__ void fft8(float2 (&a)[8]) {
-    const float h = 0.70710678118654752440f;
-    float2 b0 = cadd(a[0], a[4]), b1 = csub(a[0], a[4]);
-    float2 b2 = cadd(a[2], a[6]), b3 = mul_mi(csub(a[2], a[6]));
-    float2 b4 = cadd(a[1], a[5]), b5 = csub(a[1], a[5]);
-    float2 b6 = cadd(a[3], a[7]), b7 = mul_mi(csub(a[3], a[7]));
-    float2 e0 = cadd(b0, b2), e2 = csub(b0, b2), e1 = cadd(b1, b3), e3 = csub(b1, b3);
-    float2 o0 = cadd(b4, b6), o2 = csub(b4, b6), o1 = cadd(b5, b7), o3 = csub(b5, b7);
-    // W8^1 = (1 - i)/sqrt2, W8^2 = -i, W8^3 = (-1 - i)/sqrt2
-    float2 t1 = make_float2((o1.x + o1.y) * h, (o1.y - o1.x) * h);
-    float2 t2 = mul_mi(o2);
-    float2 t3 = make_float2((o3.y - o3.x) * h, -(o3.x + o3.y) * h);
-    a[0] = cadd(e0, o0); a[4] = csub(e0, o0);
-    a[1] = cadd(e1, t1); a[5] = csub(e1, t1);
-    a[2] = cadd(e2, t2); a[6] = csub(e2, t2);
-    a[3] = cadd(e3, t3); a[7] = csub(e3, t3);
-}
-
-__device__ __forceinline__ float2 twiddle(int num, int den) {
-    // exp(-2*pi*i*num/den)
-    float s, c;
-    sincospif(-2.0f * (float)num / (float)den, &s, &c);
-    return make_float2(c, s);
-}
-
+template <typename TIn>
 __global__ void __launch_bounds__(kThreads, 2)
-logmel_kernel(const float* __restrict__ pcm, const int64_t* __restrict__ clip_start,
-              const int64_t* __restrict__ clip_len, const int64_t* __restrict__ frame_off, float* __restrict__ out, float preemph,
-              const FrontendTables* __restrict__ tables) {
+frontend_clip_kernel(const TIn* __restrict__ pcm, const int64_t* __restrict__ clip_start,
+                     const int64_t* __restrict__ clip_len, const int64_t* __restrict__ frame_off,
+                     float* __restrict__ out, float preemph, const FrontendTables* __restrict__ tables, int normalize) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     SmemLayout& sm = *reinterpret_cast<SmemLayout*>(smem_raw);
+    constexpr int PP = Sample<TIn>::kPerPiece;
 
-    const int clip = blockIdx.y;
+    const int clip = blockIdx.x;
     const int64_t c0 = clip_start[clip];
     const int64_t n = clip_len[clip];
     const int64_t fo = frame_off[clip];
     const int T = (int)(frame_off[clip + 1] - fo);
-    const int tile0 = blockIdx.x * kTilesPerCta;
-    if (tile0 * kFramesPerTile >= T) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const TIn* x = pcm + c0;
+    // Placement of the clip in memory: shared-memory index j of a step's buffers holds clip sample gbase + j, with
+    // gbase chosen so that index 0 sits on a 16-byte boundary of the PCM buffer.  `shift` (0 .. PP-1) is how far the
+    // sample before the step lies above that boundary; it is the same for every step (a step is 2560 samples).
+    const int64_t elem0 = (int64_t)(reinterpret_cast<uintptr_t>(pcm) / sizeof(TIn)) + c0;   // absolute element index
+    const int shift = (int)(((elem0 - kPad - 1) % PP + PP) % PP);
+    const bool aligned8 = ((shift + 1) & 1) == 0;  // a frame's first sample sits at the even index shift + 1 + 160 fl
+    const int n_steps = (T + kStepFrames - 1) / kStepFrames;
 
-    const int tid = threadIdx.x;
-    const float* x = pcm + c0;
-    // Raw samples of a tile -> shared memory, asynchronously; sample g of the clip sits at index g - s0 + 1, so
-    // that the sample before the tile is there too; zero outside the clip (frontend.rs:59-65).
-    auto fetch = [&](int tile, int buf) {
-        const int64_t s0 = (int64_t)tile * kFramesPerTile * kHop - kPad;
-        for (int i = tid; i < kRawSamples; i += kThreads) {
-            const int64_t g = s0 - 1 + i;
-            const bool in = g >= 0 && g < n && tile * kFramesPerTile < T;
-            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&sm.xs[buf][i]);
-            const int bytes = in ? 4 : 0;
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(x + (in ? g : 0)), "r"(bytes) : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    fetch(tile0, 0);
-    // Tables -> shared memory.
-    for (int i = tid; i < kWin; i += kThreads) sm.window[i] = tables->window[i];
-    for (int i = tid; i < kMaxTaps * kMels; i += kThreads) sm.melw[i] = tables->melw[i];
-    for (int i = tid; i < kMels; i += kThreads) {
-        sm.mel_start[i] = tables->mel_start[i];
-        sm.mel_cnt[i] = tables->mel_cnt[i];
-    }
-    for (int i = tid; i <= 128; i += kThreads) sm.tw_post[i] = tables->tw_post[i];
-
-    const int warp = tid >> 5, lane = tid & 31;
-    float2* sc = sm.scratch[warp];
-    float* pw = sm.power[warp];
-    if (lane < kPowerPad - 257) pw[257 + lane] = 0.0f;
-
-    // Lane-constant twiddles.
-    float2 tw1[8], tw2[8];
-    const int k1s = lane >> 2, r2 = lane & 3;
+    // Raw samples of a step -> shared memory, asynchronously; zero outside the clip (frontend.rs:59-65).
+    auto fetch = [&](int step, int buf) {
+        const int64_t gbase = (int64_t)step * kStepFrames * kHop - kPad - 1 - shift;
+        TIn* dst = reinterpret_cast<TIn*>(sm.raw[buf]);
+        for (int q = tid; q < kRawElems / PP; q += kThreads) {
+            const int64_t g = gbase + (int64_t)q * PP;
+            const uint32_t d = smem_addr(dst + q * PP);
+            if (g >= 0 && g + PP <= n) {
+                cp_async16(d, x + g, 16);
+            } else if (g + PP <= 0 || g >= n) {
+                *reinterpret_cast<uint4*>(dst + q * PP) = make_uint4(0u, 0u, 0u, 0u);
+            } else if constexpr (sizeof(TIn) == 4) {
 #pragma unroll
-    for (int k = 1; k < 8; ++k) {
-        tw1[k] = twiddle(lane * k, 256);
-        tw2[k] = twiddle(r2 * k, 32);
-    }
-
-    for (int tt = 0; tt < kTilesPerCta; ++tt) {
-        const int f0 = (tile0 + tt) * kFramesPerTile;
-        if (f0 >= T) break;
-        const int buf = tt & 1;
-        if (tt + 1 < kTilesPerCta) fetch(tile0 + tt + 1, buf ^ 1);  // lands while this tile is transformed
-        else asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-        __syncthreads();  // this tile's raw samples are visible; the previous tile's frames are done with ys
-        // Pre-emphasis (frontend.rs:150-159): y[0] = x[0]; y[i] = x[i] - c * x[i-1], product rounded first.
-        {
-            const int64_t s0 = (int64_t)f0 * kHop - kPad;
-            const float* xr = sm.xs[buf];
-            for (int i = tid; i < kTileSamples + 8; i += kThreads) {
-                const int64_t g = s0 + i;
-                sm.ys[i] = (g >= 0 && g < n) ? __fsub_rn(xr[i + 1], __fmul_rn(preemph, xr[i])) : 0.0f;
-            }
-        }
-        __syncthreads();
-        for (int fl = warp; fl < kFramesPerTile; fl += kWarpsPerCta) {
-            const int f = f0 + fl;
-            if (f >= T) break;
-            const float* ys = sm.ys + fl * kHop;
-
-            // ---- stage 1: z[n] = (x[2n], x[2n+1]) windowed; DFT-8 over n1 with n = 32*n1 + lane
-            float2 a[8];
+                for (int e = 0; e < PP; ++e) {
+                    const bool in = g + e >= 0 && g + e < n;
+                    cp_async4(d + 4 * e, x + (in ? g + e : 0), in ? 4 : 0);
+                }
+            } else {
+                // 16-bit samples at a clip edge: plain loads (cp.async moves at least four bytes)
 #pragma unroll
-            for (int n1 = 0; n1 < 8; ++n1) {
-                const int nn = 32 * n1 + lane;
-                if (nn < kWin / 2) {
-                    const float2 v = *reinterpret_cast<const float2*>(ys + 2 * nn);
-                    const float2 w = *reinterpret_cast<const float2*>(sm.window + 2 * nn);
-                    a[n1] = make_float2(__fmul_rn(v.x, w.x), __fmul_rn(v.y, w.y));
-                } else {
-                    a[n1] = make_float2(0.0f, 0.0f);
+                for (int e = 0; e < PP; ++e) {
+                    const bool in = g + e >= 0 && g + e < n;
+                    dst[q * PP + e] = in ? x[g + e] : TIn(0);
                 }
             }
-            fft8(a);
-            sc[lane] = a[0];
-#pragma unroll
-            for (int k = 1; k < 8; ++k) sc[k * kS1Stride + lane] = cmul(a[k], tw1[k]);
-            __syncwarp();
+        }
+        cp_async_commit();
+    };
+    if (n_steps > 0) fetch(0, 0);
 
-            // ---- stage 2: for (k1, r2): DFT-8 over r1 of B[4*r1 + r2]
-#pragma unroll
-            for (int r1 = 0; r1 < 8; ++r1) a[r1] = sc[k1s * kS1Stride + 4 * r1 + r2];
-            __syncwarp();
-            fft8(a);
-#pragma unroll
-            for (int k = 1; k < 8; ++k) a[k] = cmul(a[k], tw2[k]);
+    // Tables -> shared memory.
+    for (int i = tid; i < kWin; i += kThreads) sm.window[i] = tables->window[i];
+    for (int i = tid; i < 132; i += kThreads) sm.tw_post[i] = tables->tw_post[i];
+    for (int i = tid; i < 256; i += kThreads) sm.twid[i] = tables->twid[i];
+    for (int i = tid; i < kMelTapRows * 16; i += kThreads) sm.melw[i] = tables->melw[i];
+    for (int i = tid; i < kMels; i += kThreads) sm.mel_start[i] = tables->mel_start[i];
+    const float log_floor = tables->log_floor;
+    for (int i = tid; i < kWarps * 2 * (fe::kPowPad - 257); i += kThreads) {
+        const int f = i / (fe::kPowPad - 257), k = i % (fe::kPowPad - 257);
+        (&sm.pw[0][0][0])[f * fe::kPowPad + 257 + k] = 0.0f;  // taps past a run multiply these
+    }
 
-            // ---- stage 3: DFT-4 over r2 across the four adjacent lanes, by shuffles.
-            // After it lane r2 holds k3 = bitrev2(r2).
+    float sum = 0.0f;  // threads 0..127: running sum of column tid, frontend.rs:230
+    // Rows of a finished step: out to memory (16-byte stores), and into the column sums in frame order.
+    auto flush = [&](int step) {
+        const int f0 = step * kStepFrames;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                float2 v = a[k];
-                float2 p = make_float2(__shfl_xor_sync(0xffffffffu, v.x, 2), __shfl_xor_sync(0xffffffffu, v.y, 2));
-                v = (r2 & 2) ? csub(p, v) : cadd(v, p);
-                if (r2 == 3) v = mul_mi(v);
-                p = make_float2(__shfl_xor_sync(0xffffffffu, v.x, 1), __shfl_xor_sync(0xffffffffu, v.y, 1));
-                v = (r2 & 1) ? csub(p, v) : cadd(v, p);
-                a[k] = v;
+        for (int k = 0; k < 2; ++k) {
+            const int idx = tid + kThreads * k, row = idx >> 5, c4 = idx & 31;
+            if (f0 + row < T)
+                reinterpret_cast<float4*>(out + (fo + f0 + row) * kMels)[c4] = reinterpret_cast<const float4*>(sm.stage[row])[c4];
+        }
+        if (tid < kMels) {
+            const int rows = min(kStepFrames, T - f0);
+            if (rows == kStepFrames) {
+#pragma unroll
+                for (int r = 0; r < kStepFrames; ++r) sum = __fadd_rn(sum, sm.stage[r][tid]);
+            } else {
+                for (int r = 0; r < rows; ++r) sum = __fadd_rn(sum, sm.stage[r][tid]);
             }
-            const int k3 = ((r2 & 1) << 1) | (r2 >> 1);
-            // Z[k], k = k1 + 8*k2 + 64*k3, stored at k + 4*(k >> 6) (bank-conflict-free).
-#pragma unroll
-            for (int k2 = 0; k2 < 8; ++k2) sc[k1s + 8 * k2 + 68 * k3] = a[k2];
-            __syncwarp();
+        }
+    };
 
-            // ---- real-FFT untangling and power for bins k and 256 - k, k = 1..128.
-            //   E = (Z[k] + conj(Z[256-k])) / 2,  O = -i (Z[k] - conj(Z[256-k])) / 2
-            //   X[k] = E + W512^k O,  X[256-k] = conj(E - W512^k O)
+    const int half = lane >> 4, p = lane & 15;
+    for (int step = 0; step < n_steps; ++step) {
+        const int buf = step & 1;
+        if (step + 1 < n_steps) fetch(step + 1, buf ^ 1);  // lands while this step is transformed
+        else cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();  // this step's raw samples are in; the previous step's rows are all in the stage
+        if (step > 0) flush(step - 1);
+        // Pre-emphasis (frontend.rs:150-159): y[0] = x[0]; y[i] = x[i] - c * x[i-1], product rounded first; zero outside
+        // the clip (the padding is added after the pre-emphasis, frontend.rs:59-65).
+        {
+            const int64_t gbase = (int64_t)step * kStepFrames * kHop - kPad - 1 - shift;
+            const void* raw = sm.raw[buf];
+            for (int q = tid; q < kRawElems / 4; q += kThreads) {
+                const int j = 4 * q;
+                float xs[5];
+                xs[0] = j > 0 ? Sample<TIn>::get(raw, j - 1) : 0.0f;
 #pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                const int k = 1 + lane + 32 * m;
-                const int kc = 256 - k;
-                const float2 zk = sc[k + 4 * (k >> 6)];
-                const float2 zc = sc[kc + 4 * (kc >> 6)];
-                const float2 e = make_float2(0.5f * (zk.x + zc.x), 0.5f * (zk.y - zc.y));
-                const float2 d = make_float2(zk.x - zc.x, zk.y + zc.y);       // Z[k] - conj(Z[256-k])
-                const float2 o = make_float2(d.y, -d.x);                       // -i * d
-                const float2 t = cmul(o, sm.tw_post[k]);                       // includes the 1/2
-                const float2 xp = cadd(e, t), xm = csub(e, t);
-                pw[k] = __fadd_rn(__fmul_rn(xp.x, xp.x), __fmul_rn(xp.y, xp.y));
-                pw[kc] = __fadd_rn(__fmul_rn(xm.x, xm.x), __fmul_rn(xm.y, xm.y));
-            }
-            if (lane == 0) {
-                const float2 z0 = sc[0];
-                const float dc = z0.x + z0.y, ny = z0.x - z0.y;
-                pw[0] = dc * dc;
-                pw[256] = ny * ny;
-            }
-            __syncwarp();
-
-            // ---- sparse mel filterbank + ln(mel + 2^-24), frontend.rs:110-115
-            float* orow = out + (fo + f) * (int64_t)kMels;
+                for (int e = 0; e < 4; ++e) xs[e + 1] = Sample<TIn>::get(raw, j + e);
+                float4 y;
+                float* yv = reinterpret_cast<float*>(&y);
+                const int64_t g = gbase + j;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int m = lane + 32 * i;
-                const int st = sm.mel_start[m], cnt = sm.mel_cnt[m];
-                float acc = 0.0f;
-                for (int j = 0; j < cnt; ++j) acc = fmaf(sm.melw[j * kMels + m], pw[st + j], acc);
-                orow[m] = logf(__fadd_rn(acc, 5.9604644775390625e-08f));
+                for (int e = 0; e < 4; ++e) {
+                    const float v = __fsub_rn(xs[e + 1], __fmul_rn(preemph, xs[e]));
+                    yv[e] = (g + e >= 0 && g + e < n) ? v : 0.0f;
+                }
+                *reinterpret_cast<float4*>(sm.ys + j) = y;
             }
+        }
+        __syncthreads();  // samples ready; the stage is free again
+        {
+            const int fl = 2 * warp + half;                      // frame of the step this half-warp transforms
+            const float* ysf = sm.ys + shift + 1 + fl * kHop;     // its 400 samples
+            float2* B = sm.scratch[warp][half];
+            float* pwf = sm.pw[warp][half];
+            if (aligned8) fe::pass1<true>(p, ysf, sm.window, sm.twid, B);
+            else fe::pass1<false>(p, ysf, sm.window, sm.twid, B);
             __syncwarp();
+            float2 z[16];
+            fe::pass2(p, B, z);
+            __syncwarp();
+            fe::store_z(p, z, B);
+            __syncwarp();
+            fe::untangle(p, B, sm.tw_post, pwf);
+            __syncwarp();
+            fe::mel_rows(p, pwf, sm.melw, sm.mel_start, log_floor, sm.stage[fl]);
         }
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
-}
+    cp_async_wait<0>();
+    __syncthreads();
+    if (n_steps > 0) flush(n_steps - 1);
+    if (!normalize) return;
 
-// frontend.rs:225-236: strictly sequential f32 accumulation per (clip, feature).
-__global__ void __launch_bounds__(kMels)
-colstats_kernel(const float* __restrict__ feat, const int64_t* __restrict__ frame_off,
-                float* __restrict__ mean_out, float* __restrict__ std_out) {
-    const int clip = blockIdx.x, f = threadIdx.x;
-    const int64_t fo = frame_off[clip];
-    const int T = (int)(frame_off[clip + 1] - fo);
-    const float* col = feat + fo * kMels + f;
-    float sum = 0.0f;
-    int t = 0;
-    for (; t + 8 <= T; t += 8) {
-        float v[8];
+    // ---- statistics, frontend.rs:225-236.  Thread c (< 128) owns column c; warp w streams rows of columns
+    // 32 w .. 32 w + 31 through its own ring of kRingSlots x kRingRows rows.
+    __syncthreads();  // every row of the clip has been stored by this CTA
+    const float* rows = out + fo * kMels;
+    if (warp < kMels / 32) {
+        const float mean = __fdiv_rn(sum, (float)T);
+        float* ring = reinterpret_cast<float*>(&sm.scratch[0][0][0]) + warp * (kRingSlots * kRingRows * 32);
+        const int n_blk = (T + kRingRows - 1) / kRingRows;
+        auto issue = [&](int blk) {
+            if (blk < n_blk) {
+                float* slot = ring + (blk % kRingSlots) * (kRingRows * 32);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = col[(int64_t)(t + u) * kMels];
+                for (int k = 0; k < kRingRows * 8 / 32; ++k) {
+                    const int q = lane + 32 * k, r = q >> 3, ch = q & 7;
+                    const int row = blk * kRingRows + r;
+                    const bool in = row < T;
+                    cp_async16(smem_addr(slot + r * 32 + 4 * ch), rows + (int64_t)(in ? row : 0) * kMels + 32 * warp + 4 * ch,
+                               in ? 16 : 0);
+                }
+            }
+            cp_async_commit();
+        };
 #pragma unroll
-        for (int u = 0; u < 8; ++u) sum = __fadd_rn(sum, v[u]);
-    }
-    for (; t < T; ++t) sum = __fadd_rn(sum, col[(int64_t)t * kMels]);
-    const float mean = __fdiv_rn(sum, (float)T);
-    float acc = 0.0f;
-    t = 0;
-    for (; t + 8 <= T; t += 8) {
-        float v[8];
+        for (int s = 0; s < kRingSlots - 1; ++s) issue(s);
+        float acc = 0.0f;
+        for (int blk = 0; blk < n_blk; ++blk) {
+            issue(blk + kRingSlots - 1);  // refills the slot that was read one iteration ago
+            cp_async_wait<kRingSlots - 1>();
+            __syncwarp();
+            const float* slot = ring + (blk % kRingSlots) * (kRingRows * 32);
+            const int nr = min(kRingRows, T - blk * kRingRows);
+            if (nr == kRingRows) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = col[(int64_t)(t + u) * kMels];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const float d = __fsub_rn(v[u], mean);
-            acc = __fadd_rn(acc, __fmul_rn(d, d));
+                for (int r = 0; r < kRingRows; ++r) {
+                    const float d = __fsub_rn(slot[r * 32 + lane], mean);
+                    acc = __fadd_rn(acc, __fmul_rn(d, d));
+                }
+            } else {
+                for (int r = 0; r < nr; ++r) {
+                    const float d = __fsub_rn(slot[r * 32 + lane], mean);
+                    acc = __fadd_rn(acc, __fmul_rn(d, d));
+                }
+            }
+            __syncwarp();  // all lanes are done with the slot before the next issue overwrites it
         }
+        cp_async_wait<0>();
+        // variance / (T - 1); T == 1 divides 0 by 0 and yields NaN exactly as the reference does.
+        const float variance = __fdiv_rn(acc, __fsub_rn((float)T, 1.0f));
+        sm.mean[tid] = mean;
+        sm.stdv[tid] = __fadd_rn(__fsqrt_rn(variance), 1e-5f);
     }
-    for (; t < T; ++t) {
-        const float d = __fsub_rn(col[(int64_t)t * kMels], mean);
-        acc = __fadd_rn(acc, __fmul_rn(d, d));
-    }
-    // variance / (T - 1); T == 1 divides 0 by 0 and yields NaN exactly as the reference does.
-    const float variance = __fdiv_rn(acc, __fsub_rn((float)T, 1.0f));
-    mean_out[clip * kMels + f] = mean;
-    std_out[clip * kMels + f] = __fadd_rn(__fsqrt_rn(variance), 1e-5f);
-}
-
-// frontend.rs:237-239
-__global__ void __launch_bounds__(256)
-normalize_kernel(float* __restrict__ feat, const int64_t* __restrict__ frame_off,
-                 const float* __restrict__ mean, const float* __restrict__ stdv, int rows_per_cta) {
-    const int clip = blockIdx.y;
-    const int64_t fo = frame_off[clip];
-    const int T = (int)(frame_off[clip + 1] - fo);
-    const int r0 = blockIdx.x * rows_per_cta;
-    if (r0 >= T) return;
-    const int r1 = min(T, r0 + rows_per_cta);
-    const int c4 = (threadIdx.x & 31) * 4;
-    const float4 mu = *reinterpret_cast<const float4*>(mean + clip * kMels + c4);
-    const float4 sd = *reinterpret_cast<const float4*>(stdv + clip * kMels + c4);
-    for (int r = r0 + (threadIdx.x >> 5); r < r1; r += 8) {
-        float4* p = reinterpret_cast<float4*>(feat + (fo + r) * kMels + c4);
-        float4 v = *p;
-        v.x = __fdiv_rn(__fsub_rn(v.x, mu.x), sd.x);
-        v.y = __fdiv_rn(__fsub_rn(v.y, mu.y), sd.y);
-        v.z = __fdiv_rn(__fsub_rn(v.z, mu.z), sd.z);
-        v.w = __fdiv_rn(__fsub_rn(v.w, mu.w), sd.w);
-        *p = v;
+    __syncthreads();
+    // ---- normalise, frontend.rs:237-239
+    {
+        const int c4 = tid & 31;
+        const float4 mu = reinterpret_cast<const float4*>(sm.mean)[c4];
+        const float4 sd = reinterpret_cast<const float4*>(sm.stdv)[c4];
+        float4* rows4 = reinterpret_cast<float4*>(out + fo * kMels);
+        constexpr int U = 8;
+        for (int r0 = tid >> 5; r0 < T; r0 += 8 * U) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int r = r0 + 8 * u;
+                if (r < T) v[u] = __ldcg(rows4 + (int64_t)r * 32 + c4);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int r = r0 + 8 * u;
+                if (r < T) {
+                    float4 o;
+                    o.x = __fdiv_rn(__fsub_rn(v[u].x, mu.x), sd.x);
+                    o.y = __fdiv_rn(__fsub_rn(v[u].y, mu.y), sd.y);
+                    o.z = __fdiv_rn(__fsub_rn(v[u].z, mu.z), sd.z);
+                    o.w = __fdiv_rn(__fsub_rn(v[u].w, mu.w), sd.w);
+                    rows4[(int64_t)r * 32 + c4] = o;
+                }
+            }
+        }
     }
 }
 
@@ -320,25 +310,26 @@ normalize_kernel(float* __restrict__ feat, const int64_t* __restrict__ frame_off
 size_t frontend_smem_bytes() { return sizeof(SmemLayout); }
 
 cudaError_t frontend_configure() {
-    return cudaFuncSetAttribute(logmel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(frontend_clip_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)sizeof(SmemLayout));
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(frontend_clip_kernel<int16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)sizeof(SmemLayout));
 }
 
-cudaError_t frontend_launch(const float* pcm, const int64_t* d_clip_start, const int64_t* d_clip_len,
-                            const int64_t* d_frame_off, int n_clips,
-                            int max_frames, float preemph, const FrontendTables* d_tables, float* feats,
-                            float* d_mean, float* d_std, bool normalize, cudaStream_t stream) {
+cudaError_t frontend_launch(const void* pcm, SampleFormat fmt, const int64_t* d_clip_start, const int64_t* d_clip_len,
+                            const int64_t* d_frame_off, int n_clips, float preemph, const FrontendTables* d_tables,
+                            float* feats, bool normalize, cudaStream_t stream) {
     if (n_clips <= 0) return cudaSuccess;
-    const int tiles = (max_frames + kFramesPerTile - 1) / kFramesPerTile;
-    dim3 grid((tiles + kTilesPerCta - 1) / kTilesPerCta, n_clips);
-    logmel_kernel<<<grid, kThreads, sizeof(SmemLayout), stream>>>(pcm, d_clip_start, d_clip_len, d_frame_off, feats,
-                                                                 preemph, d_tables);
-    if (normalize) {
-        colstats_kernel<<<n_clips, kMels, 0, stream>>>(feats, d_frame_off, d_mean, d_std);
-        const int rows_per_cta = 64;
-        dim3 g2((max_frames + rows_per_cta - 1) / rows_per_cta, n_clips);
-        normalize_kernel<<<g2, 256, 0, stream>>>(feats, d_frame_off, d_mean, d_std, rows_per_cta);
-    }
+    // 16-byte row accesses of the feature matrix and 4- / 2-byte aligned samples
+    if ((reinterpret_cast<uintptr_t>(feats) & 15) || (reinterpret_cast<uintptr_t>(pcm) & (fmt == kSampleI16 ? 1 : 3)))
+        return cudaErrorMisalignedAddress;
+    if (fmt == kSampleI16)
+        frontend_clip_kernel<int16_t><<<n_clips, kThreads, sizeof(SmemLayout), stream>>>(
+            static_cast<const int16_t*>(pcm), d_clip_start, d_clip_len, d_frame_off, feats, preemph, d_tables, normalize ? 1 : 0);
+    else
+        frontend_clip_kernel<float><<<n_clips, kThreads, sizeof(SmemLayout), stream>>>(
+            static_cast<const float*>(pcm), d_clip_start, d_clip_len, d_frame_off, feats, preemph, d_tables, normalize ? 1 : 0);
     return cudaGetLastError();
 }
 

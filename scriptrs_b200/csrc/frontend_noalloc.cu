@@ -9,10 +9,10 @@
 //   * a host program that has handed all device memory to its own pool (an inference server, a
 //     framework allocator) and gives a library nothing but the input and output buffers it names.
 // For them this file holds everything the frontend needs besides its input and output in ONE
-// file-scope device array of fixed size: the constant tables (Hann window, mel taps, twiddles), the
-// per-clip metadata (start, length, first output row) and the per-(clip, feature) mean and standard
-// deviation that the normalisation pass reads.  Every GPU that loads the library carries this array
-// (about 1.1 MB) until the process exits.
+// file-scope device array of fixed size: the constant tables (Hann window, mel taps, twiddles) and the
+// per-clip metadata (start, length, first output row) that the kernel reads; the per-feature statistics
+// stay inside the kernel's CTAs.  Every GPU that loads the library carries this array (about 32 KB)
+// until the process exits.
 //
 // Consequences the caller has to know:
 //   * at most kNoAllocMaxClips clips per call; more is refused with SB_INVALID_ARGUMENT;
@@ -21,14 +21,15 @@
 //     serialised by a mutex.  A call made while its stream is capturing is refused with
 //     SB_INVALID_ARGUMENT: the per-call clip metadata is copied from the host stack;
 //   * all calls on a device share the array, and it keeps what the last call left in it.  Nothing in
-//     it has to start at zero (each call rewrites the metadata and the statistics of the clips it
-//     processes before reading them), but two calls whose kernels overlap on the GPU, from
-//     different streams or threads, race on it: serialise them;
+//     it has to start at zero (each call rewrites the metadata of the clips it processes before its
+//     kernel reads them), but two calls whose kernels overlap on the GPU, from different streams or
+//     threads, race on it: serialise them;
 //   * no cudaMalloc, cudaFree or allocating library routine is called, on the first call or later.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include <atomic>
+#include <climits>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -45,8 +46,7 @@ namespace {
 // Layout of the scratch array (all offsets multiples of 256 bytes).
 constexpr size_t kTablesBytes = (sizeof(FrontendTables) + 255) / 256 * 256;
 constexpr size_t kMetaBytes = (3 * (size_t)(kNoAllocMaxClips + 1) * sizeof(int64_t) + 255) / 256 * 256;
-constexpr size_t kStatBytes = (size_t)kNoAllocMaxClips * kMels * sizeof(float);
-constexpr size_t kScratchBytes = kTablesBytes + kMetaBytes + 2 * kStatBytes;
+constexpr size_t kScratchBytes = kTablesBytes + kMetaBytes;
 
 static __device__ __align__(256) unsigned char g_frontend_scratch[kScratchBytes];
 
@@ -114,29 +114,26 @@ extern "C" int32_t sb_frontend_device_noalloc(const float* d_pcm, const int64_t*
     int64_t meta[3 * (kNoAllocMaxClips + 1)] = {};
     int64_t* fo = meta + 2 * n1;
     fo[0] = 0;
-    int64_t max_frames = 0;
     for (int64_t i = 0; i < n_clips; ++i) {
         const int64_t len = clip_offsets[i + 1] - clip_offsets[i];
         if (len <= 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");
         meta[i] = clip_offsets[i];
         meta[n1 + i] = len;
         const int64_t t = frames_for_samples(len);
+        if (t > INT32_MAX / 2) return fail(SB_INVALID_ARGUMENT, "clip too long");
         fo[i + 1] = fo[i] + t;
-        if (t > max_frames) max_frames = t;
     }
-    if (max_frames > (int64_t)65535 * 32) return fail(SB_INVALID_ARGUMENT, "clip too long for one launch");
     if (frame_offsets) std::memcpy(frame_offsets, fo, sizeof(int64_t) * ((size_t)n_clips + 1));
 
     unsigned char* base = g_scratch_ptr[device];
     const FrontendTables* d_tables = reinterpret_cast<const FrontendTables*>(base);
     int64_t* d_meta = reinterpret_cast<int64_t*>(base + kTablesBytes);
-    float* d_mean = reinterpret_cast<float*>(base + kTablesBytes + kMetaBytes);
-    float* d_std = reinterpret_cast<float*>(base + kTablesBytes + kMetaBytes + kStatBytes);
     // pageable source: the runtime has staged the bytes by the time the call returns
     e = cudaMemcpyAsync(d_meta, meta, sizeof(meta), cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return cuda_fail(e, "copy of the clip metadata");
-    e = frontend_launch(d_pcm, d_meta, d_meta + n1, d_meta + 2 * n1, (int)n_clips, (int)max_frames, preemphasis,
-                        d_tables, d_feats, d_mean, d_std, normalize != 0, st);
+    e = frontend_launch(d_pcm, kSampleF32, d_meta, d_meta + n1, d_meta + 2 * n1, (int)n_clips, preemphasis, d_tables,
+                        d_feats, normalize != 0, st);
+    if (e == cudaErrorMisalignedAddress) return fail(SB_INVALID_ARGUMENT, "the feature buffer must be 16-byte aligned");
     if (e != cudaSuccess) return cuda_fail(e, "frontend launch");
     return SB_OK;
 }

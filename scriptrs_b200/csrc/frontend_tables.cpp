@@ -3,6 +3,7 @@
 // Follows the table construction of the reference's feature extractor
 // (src/frontend.rs:161-223): window in f32, filterbank triangles in f64 cast to
 // f32 and scaled in f32.  Compiled with floating-point contraction off.
+#include <algorithm>
 #include <cmath>
 #include <vector>
 
@@ -48,28 +49,36 @@ void mel_filterbank_host(float* fb, int n_fft, int n_mels, int sample_rate) {
 }
 
 bool build_frontend_tables(FrontendTables* t, float* dense_fb) {
+    const double pi = 3.14159265358979323846;
     hann_window_host(t->window, kWin);
     for (int k = 0; k < 132; ++k) {
-        const double ang = -2.0 * 3.14159265358979323846 * k / 512.0;
+        const double ang = -2.0 * pi * k / 512.0;
         t->tw_post[k] = make_float2(static_cast<float>(0.5 * std::cos(ang)), static_cast<float>(0.5 * std::sin(ang)));
     }
+    for (int k1 = 0; k1 < 16; ++k1)
+        for (int n2 = 0; n2 < 16; ++n2) {
+            const double ang = -2.0 * pi * (n2 * k1) / 256.0;
+            t->twid[k1 * 16 + n2] = make_float2(static_cast<float>(std::cos(ang)), static_cast<float>(std::sin(ang)));
+        }
+    t->log_floor = std::log(5.9604644775390625e-08f);  // f32 logarithm of 2^-24, frontend.rs:111
     std::vector<float> fb(static_cast<size_t>(kMels) * kBins);
     mel_filterbank_host(fb.data(), kNfft, kMels, kSampleRate);
     if (dense_fb) std::copy(fb.begin(), fb.end(), dense_fb);
-    for (int i = 0; i < kMaxTaps * kMels; ++i) t->melw[i] = 0.0f;
+    for (int i = 0; i < kMelTapRows * 16; ++i) t->melw[i] = 0.0f;
     for (int m = 0; m < kMels; ++m) {
-        int first = -1, last = -1;
+        int first = -1, last = -1, nonzero = 0;
         for (int k = 0; k < kBins; ++k)
             if (fb[m * kBins + k] != 0.0f) {
                 if (first < 0) first = k;
                 last = k;
+                ++nonzero;
             }
         if (first < 0) { first = 0; last = -1; }
         const int cnt = last - first + 1;
-        if (cnt > kMaxTaps) return false;
-        for (int j = 0; j < cnt; ++j) t->melw[j * kMels + m] = fb[m * kBins + first + j];
+        const int g = m / 16, lane = m % 16;
+        if (cnt > kGroupTaps[g] || cnt > kMaxTaps || nonzero != cnt) return false;
+        for (int j = 0; j < cnt; ++j) t->melw[(kGroupTapOffset[g] + j) * 16 + lane] = fb[m * kBins + first + j];
         t->mel_start[m] = static_cast<int16_t>(first);
-        t->mel_cnt[m] = static_cast<int16_t>(cnt);
     }
     return true;
 }

@@ -18,7 +18,7 @@ struct RawTokens {
 
 void decode_workspace_free(sb_ctx* c);
 
-int32_t frontend_run(sb_ctx* c, const float* d_pcm, const int64_t* clip_start, const int64_t* clip_len,
+int32_t frontend_run(sb_ctx* c, const void* d_pcm, SampleFormat fmt, const int64_t* clip_start, const int64_t* clip_len,
                      int64_t n_clips, float preemphasis, bool normalize, float* d_feats, int64_t* frame_offsets);
 
 // Runs the TDT decoder over packed encoder output already on the device.  Blocking.

@@ -273,19 +273,31 @@ def _audio(a) -> np.ndarray:
 
 
 def transcribe_chunks(ctx: Context, audio: np.ndarray, tasks, config: TranscriptionConfig | None = None,
-                      audio_ptr: int | None = None, n_samples: int | None = None, on_device: bool = False):
+                      audio_ptr: int | None = None, n_samples: int | None = None, on_device: bool = False,
+                      sample_format: str = "float32"):
     """Batched transcribe_task for a list of (audio_start, audio_end, global_sample_offset, context_samples).
     Returns a RawBatch (a list-like of RawTranscription).  `audio_ptr`/`n_samples` let a caller pass pinned host memory, or,
-    with on_device=True, a device pointer."""
+    with on_device=True, a device pointer.  An int16 array (or sample_format="int16" with audio_ptr) is 16-bit PCM: it
+    crosses to the GPU as it is and is converted (value / 32767) inside the frontend kernel."""
+    int16 = False
     if audio_ptr is None:
-        audio = _audio(audio)
+        if isinstance(audio, np.ndarray) and audio.dtype == np.int16:
+            audio = np.ascontiguousarray(audio).reshape(-1)   # 16-bit PCM goes to the GPU as it is
+            int16 = True
+        else:
+            audio = _audio(audio)
         audio_ptr, n_samples = audio.ctypes.data, audio.size
+    elif sample_format == "int16":
+        int16 = True
     arr = (_lib.ChunkTaskC * max(len(tasks), 1))()
     for i, t in enumerate(tasks):
         arr[i] = _lib.ChunkTaskC(*[int(x) for x in t])
     cfg = (config or TranscriptionConfig()).to_c()
     h = C.c_void_p()
-    fn = _lib.lib().sb_transcribe_chunks_device if on_device else _lib.lib().sb_transcribe_chunks
+    if int16 and on_device:
+        raise ScriptrsError(11, "16-bit PCM is taken from host memory")
+    fn = (_lib.lib().sb_transcribe_chunks_device if on_device else
+          (_lib.lib().sb_transcribe_chunks_i16 if int16 else _lib.lib().sb_transcribe_chunks))
     check(fn(ctx.handle, C.c_void_p(audio_ptr), n_samples, arr, len(tasks), C.byref(cfg), C.byref(h)))
     L = _lib.lib()
     try:
@@ -323,6 +335,20 @@ class TranscriptionPipeline:
         over named float32 tensors instead of a CoreML bundle directory."""
         ctx = ctx or Context(device)
         load_model(ctx, weights, encoder_layers, scale_input, has_encoder=True, has_decoder=True)
+        return cls(ctx, vocab)
+
+    @classmethod
+    def from_dir(cls, models_dir: str, device: int = 0, ctx: Context | None = None,
+                 fp8_weights: bool = False) -> "TranscriptionPipeline":
+        """src/pipeline.rs:35-46: builds the pipeline from a local bundle directory, here
+        `<models_dir>/parakeet-v2/model.safetensors` + `<models_dir>/parakeet-v2/vocab.txt`.  A missing file raises
+        MissingModelAsset with its path (src/models.rs:53-66)."""
+        from . import weights
+
+        model_path, vocab_path = weights.validate_bundle(models_dir)
+        vocab = Vocabulary.from_file(vocab_path)
+        ctx = ctx or Context(device)
+        weights.load_model_file(ctx, model_path, fp8_weights=fp8_weights)
         return cls(ctx, vocab)
 
     def config(self) -> TranscriptionConfig:

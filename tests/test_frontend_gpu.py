@@ -110,3 +110,55 @@ def test_empty_audio_is_rejected(fx):
     with pytest.raises(sb.ScriptrsError) as e:
         fx.extract(np.zeros(0, np.float32))
     assert e.value.status == 1
+
+
+def _device_features(ctx, fx, pcm_np, offsets, int16=False):
+    import torch
+
+    import scriptrs_b200 as sb
+
+    d_pcm = torch.from_numpy(pcm_np).cuda()
+    rows = sum(sb.num_frames(int(offsets[i + 1] - offsets[i])) for i in range(len(offsets) - 1))
+    d_out = torch.full((rows, 128), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    fo = fx.extract_device(d_pcm.data_ptr(), np.asarray(offsets, np.int64), d_out.data_ptr(), int16=int16)
+    ctx.synchronize()
+    out = d_out.cpu().numpy()
+    return [out[fo[i]:fo[i + 1]] for i in range(len(offsets) - 1)]
+
+
+def test_clip_placement_does_not_change_the_result(ctx, fx):
+    """Clips that start at odd sample offsets of the PCM buffer take the 4-byte copy and unaligned load paths of the
+    kernel; the features must equal, bit for bit, those of the same clips placed at the start of a buffer."""
+    rng = np.random.default_rng(3)
+    lens = [16001, 4999, 48002, 1, 161, 23998]
+    offs = np.zeros(len(lens) + 1, np.int64)
+    offs[1:] = np.cumsum(lens)
+    assert {int(o) % 4 for o in offs[:-1]} == {0, 1, 2, 3}
+    pcm = np.clip(rng.normal(0, 0.2, int(offs[-1])), -1, 1).astype(np.float32)
+    packed = _device_features(ctx, fx, pcm, offs)
+    for i, n in enumerate(lens):
+        alone = _device_features(ctx, fx, pcm[offs[i]:offs[i + 1]].copy(), [0, n])[0]
+        assert np.array_equal(packed[i], alone, equal_nan=True), (i, n)
+
+
+def test_int16_pcm_equals_the_converted_f32_buffer(ctx, fx):
+    """16-bit PCM in: the kernel converts each sample as value / 32767 in f32 (the reference's WAV reader,
+    examples/transcribe_wav.rs:341-347); the features must equal those of the f32 path on the buffer converted on the
+    host, bit for bit, for every clip placement (offsets 0 .. 7 modulo the 16-byte copy granule)."""
+    rng = np.random.default_rng(4)
+    lens = [16000, 4001, 48003, 239360, 7, 161, 23998, 5, 1602]
+    offs = np.zeros(len(lens) + 1, np.int64)
+    offs[1:] = np.cumsum(lens)
+    assert len({int(o) % 8 for o in offs[:-1]}) >= 5
+    pcm16 = rng.integers(-32768, 32768, int(offs[-1]), dtype=np.int16)
+    pcm16[offs[3]:offs[3] + 120000] = 0                        # a long silent stretch
+    pcm16[offs[0]], pcm16[offs[0] + 1] = -32768, 32767         # both extremes
+    pcm32 = pcm16.astype(np.float32) / np.float32(32767.0)
+    a = _device_features(ctx, fx, pcm16, offs, int16=True)
+    b = _device_features(ctx, fx, pcm32, offs)
+    for i in range(len(lens)):
+        assert np.array_equal(a[i], b[i], equal_nan=True), i
+    r = oracle.frontend_extract(pcm32[offs[2]:offs[3]])
+    nrm, peak = rel_errors(a[2], r)
+    assert nrm <= REL_TOL and peak <= REL_TOL, (nrm, peak)

@@ -217,3 +217,28 @@ def test_device_side_timeout_flag_fails_the_call(ctx, pipe):
         pipe.run(audio[:100_000])
     assert e.value.status == 10
     ctx.synchronize()
+
+
+def test_int16_recording_gives_the_f32_token_streams(ctx, pipe):
+    """sb_transcribe_chunks_i16: the 16-bit recording crosses to the GPU as it is (half the bytes) and is converted
+    inside the frontend kernel; the token streams must equal those of the f32 entry on the recording converted on the
+    host as the reference's WAV reader does (value / 32767, examples/transcribe_wav.rs:341-347)."""
+    import scriptrs_b200 as sb
+
+    audio = synth.long_audio(700_000, 12)
+    pcm16 = np.round(audio * 32767.0).astype(np.int16)
+    pcm32 = pcm16.astype(np.float32) / np.float32(32767.0)
+    tasks = sb.plan_fast(pcm16.size)
+    a = sb.transcribe_chunks(ctx, pcm16, tasks)
+    b = sb.transcribe_chunks(ctx, pcm32, tasks)
+    assert sum(len(r.token_ids) for r in b) > 0
+    for x, y in zip(a.flat(), b.flat()):
+        assert np.array_equal(x, y)
+    # many ordered tasks: the pieced copy path with 2-byte samples
+    n_tasks, task_len, stride = 200, 4000, 3000
+    long16 = np.round(synth.long_audio(stride * (n_tasks - 1) + task_len, 18) * 32767.0).astype(np.int16)
+    many = [(i * stride, i * stride + task_len, i * stride, 0) for i in range(n_tasks)]
+    a = sb.transcribe_chunks(ctx, long16, many)
+    b = sb.transcribe_chunks(ctx, long16.astype(np.float32) / np.float32(32767.0), many)
+    for x, y in zip(a.flat(), b.flat()):
+        assert np.array_equal(x, y)
