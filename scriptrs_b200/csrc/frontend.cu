@@ -20,7 +20,10 @@
 //             pass (squared deviations) streams the clip's rows back through a cp.async ring per warp.
 //   normalise (v - mean) / std over the clip's rows, 16-byte loads and stores, all threads.
 // While one CTA of an SM is in its two bandwidth-bound tail passes the other one keeps the SM's issue slots busy
-// with transforms, so the passes cost little wall time although they re-read the clip's rows.
+// with transforms, so the passes cost little wall time although they re-read the clip's rows.  The kernel is bound by
+// shared-memory wavefronts and issue slots, not by DRAM: the filterbank taps and as much state as fits live in
+// registers (128 per thread, two CTAs per SM), and buffers are laid out so that the two frames of a warp use
+// different banks.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -34,21 +37,21 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kStepFrames = 2 * kWarps;                           // 16 frames per step
-constexpr int kStepSamples = (kStepFrames - 1) * kHop + kWin;    // 2800
 constexpr int kRawElems = 2816;  // the step's samples + the one before them + up to 7 of alignment shift, in 16-byte pieces
 constexpr int kRingRows = 16;    // rows per ring slot of the second statistics pass
 constexpr int kRingSlots = 4;
 
+constexpr int kStageStride = kMels + 16;  // floats per stage row: the two frames of a warp write different banks
+
 struct __align__(16) SmemLayout {
-    float2 scratch[kWarps][2][fe::kFrameScratch];  // transpose buffer / Z per frame; the statistics ring later
-    float pw[kWarps][2][fe::kPowPad];              // power bins per frame
-    float raw[2][kRawElems];                       // raw samples of this and the next step (16-bit input: first half)
-    float ys[kRawElems];                           // pre-emphasised samples, indexed like raw
-    float stage[kStepFrames][kMels];               // log-mel rows of one step
+    float2 scratch[kWarps][2][fe::kFrameScratch];  // per frame: transpose buffer, then Z, then the power bins; the
+                                                   // statistics ring after the last step
+    float raw[kRawElems];                          // raw samples of the next step (16-bit input: first half)
+    float ys[kRawElems + 8];                       // pre-emphasised samples of this step, indexed like raw (+ ys_off)
+    float stage[kStepFrames][kStageStride];        // log-mel rows of one step
     float window[kWin];
     float2 tw_post[132];
     float2 twid[256];
-    float melw[kMelTapRows * 16];
     float mean[kMels];
     float stdv[kMels];
     int16_t mel_start[kMels];
@@ -103,50 +106,53 @@ frontend_clip_kernel(const TIn* __restrict__ pcm, const int64_t* __restrict__ cl
     // sample before the step lies above that boundary; it is the same for every step (a step is 2560 samples).
     const int64_t elem0 = (int64_t)(reinterpret_cast<uintptr_t>(pcm) / sizeof(TIn)) + c0;   // absolute element index
     const int shift = (int)(((elem0 - kPad - 1) % PP + PP) % PP);
-    const bool aligned8 = ((shift + 1) & 1) == 0;  // a frame's first sample sits at the even index shift + 1 + 160 fl
+    // A frame's first sample sits at index shift + 1 + 160 fl of the pre-emphasised buffer; the transform reads sample
+    // pairs with 8-byte loads, so an odd shift + 1 (a clip that starts on an odd sample of the PCM buffer) moves the
+    // whole buffer up by one element.
+    const int ys_off = (shift + 1) & 1;
     const int n_steps = (T + kStepFrames - 1) / kStepFrames;
 
     // Raw samples of a step -> shared memory, asynchronously; zero outside the clip (frontend.rs:59-65).
-    auto fetch = [&](int step, int buf) {
+    auto fetch = [&](int step) {
         const int64_t gbase = (int64_t)step * kStepFrames * kHop - kPad - 1 - shift;
-        TIn* dst = reinterpret_cast<TIn*>(sm.raw[buf]);
-        for (int q = tid; q < kRawElems / PP; q += kThreads) {
-            const int64_t g = gbase + (int64_t)q * PP;
-            const uint32_t d = smem_addr(dst + q * PP);
-            if (g >= 0 && g + PP <= n) {
-                cp_async16(d, x + g, 16);
-            } else if (g + PP <= 0 || g >= n) {
-                *reinterpret_cast<uint4*>(dst + q * PP) = make_uint4(0u, 0u, 0u, 0u);
-            } else if constexpr (sizeof(TIn) == 4) {
+        TIn* dst = reinterpret_cast<TIn*>(sm.raw);
+        if (gbase >= 0 && gbase + kRawElems <= n) {  // the whole step lies inside the clip
+            const TIn* src = x + gbase;
+            for (int q = tid; q < kRawElems / PP; q += kThreads) cp_async16(smem_addr(dst + q * PP), src + q * PP, 16);
+        } else {
+            for (int q = tid; q < kRawElems / PP; q += kThreads) {
+                const int64_t g = gbase + (int64_t)q * PP;
+                const uint32_t d = smem_addr(dst + q * PP);
+                if (g >= 0 && g + PP <= n) {
+                    cp_async16(d, x + g, 16);
+                } else if (g + PP <= 0 || g >= n) {
+                    *reinterpret_cast<uint4*>(dst + q * PP) = make_uint4(0u, 0u, 0u, 0u);
+                } else if constexpr (sizeof(TIn) == 4) {
 #pragma unroll
-                for (int e = 0; e < PP; ++e) {
-                    const bool in = g + e >= 0 && g + e < n;
-                    cp_async4(d + 4 * e, x + (in ? g + e : 0), in ? 4 : 0);
-                }
-            } else {
-                // 16-bit samples at a clip edge: plain loads (cp.async moves at least four bytes)
+                    for (int e = 0; e < PP; ++e) {
+                        const bool in = g + e >= 0 && g + e < n;
+                        cp_async4(d + 4 * e, x + (in ? g + e : 0), in ? 4 : 0);
+                    }
+                } else {
+                    // 16-bit samples at a clip edge: plain loads (cp.async moves at least four bytes)
 #pragma unroll
-                for (int e = 0; e < PP; ++e) {
-                    const bool in = g + e >= 0 && g + e < n;
-                    dst[q * PP + e] = in ? x[g + e] : TIn(0);
+                    for (int e = 0; e < PP; ++e) {
+                        const bool in = g + e >= 0 && g + e < n;
+                        dst[q * PP + e] = in ? x[g + e] : TIn(0);
+                    }
                 }
             }
         }
         cp_async_commit();
     };
-    if (n_steps > 0) fetch(0, 0);
+    fetch(0);
 
     // Tables -> shared memory.
     for (int i = tid; i < kWin; i += kThreads) sm.window[i] = tables->window[i];
     for (int i = tid; i < 132; i += kThreads) sm.tw_post[i] = tables->tw_post[i];
     for (int i = tid; i < 256; i += kThreads) sm.twid[i] = tables->twid[i];
-    for (int i = tid; i < kMelTapRows * 16; i += kThreads) sm.melw[i] = tables->melw[i];
     for (int i = tid; i < kMels; i += kThreads) sm.mel_start[i] = tables->mel_start[i];
     const float log_floor = tables->log_floor;
-    for (int i = tid; i < kWarps * 2 * (fe::kPowPad - 257); i += kThreads) {
-        const int f = i / (fe::kPowPad - 257), k = i % (fe::kPowPad - 257);
-        (&sm.pw[0][0][0])[f * fe::kPowPad + 257 + k] = 0.0f;  // taps past a run multiply these
-    }
 
     float sum = 0.0f;  // threads 0..127: running sum of column tid, frontend.rs:230
     // Rows of a finished step: out to memory (16-byte stores), and into the column sums in frame order.
@@ -170,18 +176,18 @@ frontend_clip_kernel(const TIn* __restrict__ pcm, const int64_t* __restrict__ cl
     };
 
     const int half = lane >> 4, p = lane & 15;
+    float taps[kMelTapRows];  // this lane's filterbank taps (rows 16 g + p)
+    fe::load_mel_taps(p, tables->melw, taps);
     for (int step = 0; step < n_steps; ++step) {
-        const int buf = step & 1;
-        if (step + 1 < n_steps) fetch(step + 1, buf ^ 1);  // lands while this step is transformed
-        else cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<0>();
         __syncthreads();  // this step's raw samples are in; the previous step's rows are all in the stage
         if (step > 0) flush(step - 1);
         // Pre-emphasis (frontend.rs:150-159): y[0] = x[0]; y[i] = x[i] - c * x[i-1], product rounded first; zero outside
         // the clip (the padding is added after the pre-emphasis, frontend.rs:59-65).
         {
             const int64_t gbase = (int64_t)step * kStepFrames * kHop - kPad - 1 - shift;
-            const void* raw = sm.raw[buf];
+            const void* raw = sm.raw;
+            const bool inside = gbase >= 0 && gbase + kRawElems <= n;
             for (int q = tid; q < kRawElems / 4; q += kThreads) {
                 const int j = 4 * q;
                 float xs[5];
@@ -194,33 +200,44 @@ frontend_clip_kernel(const TIn* __restrict__ pcm, const int64_t* __restrict__ cl
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float v = __fsub_rn(xs[e + 1], __fmul_rn(preemph, xs[e]));
-                    yv[e] = (g + e >= 0 && g + e < n) ? v : 0.0f;
+                    yv[e] = (inside || (g + e >= 0 && g + e < n)) ? v : 0.0f;
                 }
-                *reinterpret_cast<float4*>(sm.ys + j) = y;
+                if (ys_off == 0) {
+                    *reinterpret_cast<float4*>(sm.ys + j) = y;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sm.ys[j + 1 + e] = yv[e];
+                }
             }
         }
-        __syncthreads();  // samples ready; the stage is free again
+        __syncthreads();  // samples ready; the stage and the raw buffer are free again
+        if (step + 1 < n_steps) fetch(step + 1);  // lands while this step is transformed
         {
-            const int fl = 2 * warp + half;                      // frame of the step this half-warp transforms
-            const float* ysf = sm.ys + shift + 1 + fl * kHop;     // its 400 samples
+            const int fl = 2 * warp + half;                                // frame of the step this half-warp transforms
+            const float* ysf = sm.ys + shift + 1 + ys_off + fl * kHop;     // its 400 samples
             float2* B = sm.scratch[warp][half];
-            float* pwf = sm.pw[warp][half];
-            if (aligned8) fe::pass1<true>(p, ysf, sm.window, sm.twid, B);
-            else fe::pass1<false>(p, ysf, sm.window, sm.twid, B);
+            fe::pass1(p, ysf, sm.window, sm.twid, B);
             __syncwarp();
-            float2 z[16];
-            fe::pass2(p, B, z);
+            {
+                float2 z[16];
+                fe::pass2(p, B, z);
+                __syncwarp();
+                fe::store_z(p, z, B);
+            }
             __syncwarp();
-            fe::store_z(p, z, B);
+            float* pwf = reinterpret_cast<float*>(B);  // the power bins take Z's place once every lane holds its Z values
+            {
+                float2 zk[8], zc[8], z0;
+                fe::untangle_load(p, B, zk, zc, z0);
+                __syncwarp();
+                fe::untangle_store(p, zk, zc, z0, sm.tw_post, pwf);
+            }
             __syncwarp();
-            fe::untangle(p, B, sm.tw_post, pwf);
-            __syncwarp();
-            fe::mel_rows(p, pwf, sm.melw, sm.mel_start, log_floor, sm.stage[fl]);
+            fe::mel_rows(p, pwf, taps, sm.mel_start, log_floor, sm.stage[fl]);
         }
     }
-    cp_async_wait<0>();
     __syncthreads();
-    if (n_steps > 0) flush(n_steps - 1);
+    flush(n_steps - 1);
     if (!normalize) return;
 
     // ---- statistics, frontend.rs:225-236.  Thread c (< 128) owns column c; warp w streams rows of columns
@@ -275,11 +292,24 @@ frontend_clip_kernel(const TIn* __restrict__ pcm, const int64_t* __restrict__ cl
         sm.stdv[tid] = __fadd_rn(__fsqrt_rn(variance), 1e-5f);
     }
     __syncthreads();
-    // ---- normalise, frontend.rs:237-239
+    // ---- normalise, frontend.rs:237-239: (v - mean) / std with the IEEE quotient.  For a divisor in the range below
+    // the quotient is formed from the correctly rounded reciprocal and one exact-remainder correction, three
+    // instructions, which gives the correctly rounded result (Markstein's correction step; checked against the
+    // hardware division on 4e8 operand pairs, all-ones significands included); any other divisor takes __fdiv_rn.
     {
         const int c4 = tid & 31;
         const float4 mu = reinterpret_cast<const float4*>(sm.mean)[c4];
         const float4 sd = reinterpret_cast<const float4*>(sm.stdv)[c4];
+        auto plain = [](float d) {
+            const uint32_t b = __float_as_uint(d);
+            return d >= 7.62939453125e-06f && d < 128.0f && (b & 0x7FFFFFu) != 0x7FFFFFu;  // 2^-17 <= d < 2^7
+        };
+        const bool fast = plain(sd.x) && plain(sd.y) && plain(sd.z) && plain(sd.w);
+        const float4 rc = make_float4(__frcp_rn(sd.x), __frcp_rn(sd.y), __frcp_rn(sd.z), __frcp_rn(sd.w));
+        auto quot = [](float x, float d, float r) {
+            const float q = __fmul_rn(x, r);
+            return fmaf(fmaf(-q, d, x), r, q);
+        };
         float4* rows4 = reinterpret_cast<float4*>(out + fo * kMels);
         constexpr int U = 8;
         for (int r0 = tid >> 5; r0 < T; r0 += 8 * U) {
@@ -294,10 +324,19 @@ frontend_clip_kernel(const TIn* __restrict__ pcm, const int64_t* __restrict__ cl
                 const int r = r0 + 8 * u;
                 if (r < T) {
                     float4 o;
-                    o.x = __fdiv_rn(__fsub_rn(v[u].x, mu.x), sd.x);
-                    o.y = __fdiv_rn(__fsub_rn(v[u].y, mu.y), sd.y);
-                    o.z = __fdiv_rn(__fsub_rn(v[u].z, mu.z), sd.z);
-                    o.w = __fdiv_rn(__fsub_rn(v[u].w, mu.w), sd.w);
+                    const float a = __fsub_rn(v[u].x, mu.x), b = __fsub_rn(v[u].y, mu.y);
+                    const float c = __fsub_rn(v[u].z, mu.z), d = __fsub_rn(v[u].w, mu.w);
+                    if (fast) {
+                        o.x = quot(a, sd.x, rc.x);
+                        o.y = quot(b, sd.y, rc.y);
+                        o.z = quot(c, sd.z, rc.z);
+                        o.w = quot(d, sd.w, rc.w);
+                    } else {
+                        o.x = __fdiv_rn(a, sd.x);
+                        o.y = __fdiv_rn(b, sd.y);
+                        o.z = __fdiv_rn(c, sd.z);
+                        o.w = __fdiv_rn(d, sd.w);
+                    }
                     rows4[(int64_t)r * 32 + c4] = o;
                 }
             }

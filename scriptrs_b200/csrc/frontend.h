@@ -26,9 +26,9 @@ constexpr int kMelTapRows = 40;  // sum of kGroupTaps
 // Device-resident constant tables, built once on the host.
 struct FrontendTables {
     float window[kWin];               // Hann, frontend.rs:161-165
-    float2 tw_post[132];              // 0.5 * exp(-2*pi*i*k/512), k = 0..128
+    float2 tw_post[132];              // exp(-2*pi*i*k/512), k = 0..128
     float2 twid[256];                 // exp(-2*pi*i*n2*k1/256) at [k1 * 16 + n2]: twiddles between the two radix-16 passes
-    float melw[kMelTapRows * 16];     // filterbank taps: [kGroupTapOffset[g] + t][lane] = tap t of row 16 g + lane (0 past its run)
+    float melw[kMelTapRows * 16];     // [kGroupTapOffset[g] + t][lane] = tap t of row 16 g + lane, times 1/4 (0 past its run)
     int16_t mel_start[kMels];         // first non-zero bin of each row
     float log_floor;                  // ln(2^-24) as the host's logf rounds it: the log-mel value of an empty mel cell
 };

@@ -27,8 +27,9 @@ namespace sb {
 namespace fe {
 
 constexpr int kRow = 17;                    // float2 per row of the 16 x 16 transpose buffer
-constexpr int kFrameScratch = 16 * kRow;    // 272 float2 per frame; also holds Z[0..255]
-constexpr int kPowPad = 272;                // 257 power bins + slack for zero-weight taps past a run
+constexpr int kFrameScratch = 280;          // float2 per frame (>= 16 * kRow = 272): transpose buffer, then Z[0..255], then
+                                            // the power bins.  560 words = 16 (mod 32), so that the 4-byte accesses of the
+                                            // two frames of a warp fall into different banks
 
 SB_HD float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
 SB_HD float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
@@ -93,16 +94,15 @@ SB_HD void dft16(float2 (&a)[16]) {
 #define SB_ADD_RN(a, b) ((a) + (b))
 #endif
 
-// Pass 1 of one frame for lane p (0..15).  ys: the frame's 400 pre-emphasised samples (8-byte aligned if ALIGNED8);
+// Pass 1 of one frame for lane p (0..15).  ys: the frame's 400 pre-emphasised samples (8-byte aligned);
 // window: Hann[400]; twid: the 256 inter-pass twiddles; B: this frame's transpose buffer.
-template <bool ALIGNED8 = true>
 SB_HD void pass1(int p, const float* ys, const float* window, const float2* twid, float2* B) {
     float2 a[16];
 #pragma unroll
     for (int n1 = 0; n1 < 13; ++n1) {
         const int n = 16 * n1 + p;
         if (n1 < 12 || p < 8) {  // n < 200
-            const float2 v = ALIGNED8 ? *reinterpret_cast<const float2*>(ys + 2 * n) : make_float2(ys[2 * n], ys[2 * n + 1]);
+            const float2 v = *reinterpret_cast<const float2*>(ys + 2 * n);
             const float2 w = *reinterpret_cast<const float2*>(window + 2 * n);
             a[n1] = make_float2(SB_MUL_RN(v.x, w.x), SB_MUL_RN(v.y, w.y));  // frontend.rs:74-77
         } else {
@@ -131,22 +131,32 @@ SB_HD void store_z(int p, const float2 (&z)[16], float2* Z) {
 
 // Real-FFT untangling and power for bins k and 256 - k, k = 1 + p + 16 m (m = 0..7), plus DC / Nyquist (lane 0).
 //   E = (Z[k] + conj(Z[256-k])) / 2,  O = -i (Z[k] - conj(Z[256-k])) / 2,  X[k] = E + W512^k O,  X[256-k] = conj(E - W512^k O)
-// tw_post[k] = 0.5 * W512^k; power = re^2 + im^2 (frontend.rs:142, norm_sqr).
-SB_HD void untangle(int p, const float2* Z, const float2* tw_post, float* pw) {
+// The halves are left out: with tw_post[k] = W512^k the code forms 2 X, so the stored value is 4 |X|^2 (an exact
+// scaling), and the filterbank taps carry the factor 1/4 (frontend.rs:142, norm_sqr, then :110).
+// Two steps so that the power bins may overwrite the buffer Z was read from: every lane first loads its sixteen Z
+// values (untangle_load), the warp synchronises, then the bins are written (untangle_store).
+SB_HD void untangle_load(int p, const float2* Z, float2 (&zk)[8], float2 (&zc)[8], float2& z0) {
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+        const int k = 1 + p + 16 * m;
+        zk[m] = Z[k];
+        zc[m] = Z[256 - k];
+    }
+    z0 = Z[0];
+}
+SB_HD void untangle_store(int p, const float2 (&zk)[8], const float2 (&zc)[8], float2 z0, const float2* tw_post, float* pw) {
 #pragma unroll
     for (int m = 0; m < 8; ++m) {
         const int k = 1 + p + 16 * m, kc = 256 - k;
-        const float2 zk = Z[k], zc = Z[kc];
-        const float2 e = make_float2(0.5f * (zk.x + zc.x), 0.5f * (zk.y - zc.y));
-        const float2 d = make_float2(zk.x - zc.x, zk.y + zc.y);  // Z[k] - conj(Z[256-k])
-        const float2 t = cmul(make_float2(d.y, -d.x), tw_post[k]);  // (-i d) * W / 2
+        const float2 e = make_float2(zk[m].x + zc[m].x, zk[m].y - zc[m].y);
+        const float2 d = make_float2(zk[m].x - zc[m].x, zk[m].y + zc[m].y);  // Z[k] - conj(Z[256-k])
+        const float2 t = cmul(make_float2(d.y, -d.x), tw_post[k]);            // (-i d) * W
         const float2 xp = cadd(e, t), xm = csub(e, t);
-        pw[k] = SB_ADD_RN(SB_MUL_RN(xp.x, xp.x), SB_MUL_RN(xp.y, xp.y));
-        pw[kc] = SB_ADD_RN(SB_MUL_RN(xm.x, xm.x), SB_MUL_RN(xm.y, xm.y));
+        pw[k] = fmaf(xp.x, xp.x, xp.y * xp.y);
+        pw[kc] = fmaf(xm.x, xm.x, xm.y * xm.y);
     }
     if (p == 0) {
-        const float2 z0 = Z[0];
-        const float dc = z0.x + z0.y, ny = z0.x - z0.y;
+        const float dc = 2.0f * (z0.x + z0.y), ny = 2.0f * (z0.x - z0.y);
         pw[0] = dc * dc;
         pw[256] = ny * ny;
     }
@@ -172,15 +182,23 @@ SB_HD float log_mel(float acc, float log_floor) {
 #endif
 }
 
-// Mel rows 16 g + p, g = 0..7, of one frame: out[16 g + p] = ln(sum_t w[t] * pw[start + t] + 2^-24).
-SB_HD void mel_rows(int p, const float* pw, const float* melw, const int16_t* mel_start, float log_floor, float* out) {
+// Mel rows 16 g + p, g = 0..7, of one frame: out[16 g + p] = ln(sum_t w[t] * pw[start + t] + 2^-24); pw holds four
+// times the power and the taps a quarter of the filterbank value (both exact).  Taps past a row's run are zero and
+// meet power bins of index <= 255, which always hold finite values.  The lane's 40 taps live in registers
+// (load_mel_taps, once per kernel).
+SB_HD void load_mel_taps(int p, const float* melw, float (&w)[kMelTapRows]) {
+#pragma unroll
+    for (int i = 0; i < kMelTapRows; ++i) w[i] = melw[i * 16 + p];
+}
+SB_HD void mel_rows(int p, const float* pw, const float (&w)[kMelTapRows], const int16_t* mel_start, float log_floor,
+                    float* out) {
 #pragma unroll
     for (int g = 0; g < kMelGroups; ++g) {
         const int m = 16 * g + p;
         const int st = mel_start[m];
         float acc = 0.0f;
 #pragma unroll
-        for (int t = 0; t < group_taps(g); ++t) acc = fmaf(melw[(group_tap_offset(g) + t) * 16 + p], pw[st + t], acc);
+        for (int t = 0; t < group_taps(g); ++t) acc = fmaf(w[group_tap_offset(g) + t], pw[st + t], acc);
         out[m] = log_mel(acc, log_floor);
     }
 }

@@ -53,7 +53,7 @@ bool build_frontend_tables(FrontendTables* t, float* dense_fb) {
     hann_window_host(t->window, kWin);
     for (int k = 0; k < 132; ++k) {
         const double ang = -2.0 * pi * k / 512.0;
-        t->tw_post[k] = make_float2(static_cast<float>(0.5 * std::cos(ang)), static_cast<float>(0.5 * std::sin(ang)));
+        t->tw_post[k] = make_float2(static_cast<float>(std::cos(ang)), static_cast<float>(std::sin(ang)));
     }
     for (int k1 = 0; k1 < 16; ++k1)
         for (int n2 = 0; n2 < 16; ++n2) {
@@ -77,7 +77,8 @@ bool build_frontend_tables(FrontendTables* t, float* dense_fb) {
         const int cnt = last - first + 1;
         const int g = m / 16, lane = m % 16;
         if (cnt > kGroupTaps[g] || cnt > kMaxTaps || nonzero != cnt) return false;
-        for (int j = 0; j < cnt; ++j) t->melw[(kGroupTapOffset[g] + j) * 16 + lane] = fb[m * kBins + first + j];
+        // a quarter of the tap: the kernel's power bins are 4 |X|^2 (scaling by a power of two is exact)
+        for (int j = 0; j < cnt; ++j) t->melw[(kGroupTapOffset[g] + j) * 16 + lane] = 0.25f * fb[m * kBins + first + j];
         t->mel_start[m] = static_cast<int16_t>(first);
     }
     return true;
