@@ -110,7 +110,8 @@ int64_t sb_ctx_kernel_launches(const sb_ctx* ctx);
  * "fp8_hidden_amax" (0/1): scale the e4m3 hidden row of the feed-forward module by its true maximum (one more
  * pass over the row) instead of a bound known before the product runs.  "test_raise_device_error" (0/1): sets
  * the device flag that a kernel raises when a bounded wait runs out (host-side fault injection for tests).
- * "simt_attention" (0/1): run the relative-position attention on CUDA cores
+ * "simt_subsample" (0/1): run the first two sub-sampling stages in fp32 on CUDA cores instead of the fp16
+ * tensor-core kernel.  "simt_attention" (0/1): run the relative-position attention on CUDA cores
  * instead of the tensor-core kernel; "simt_decode" (0/1): run the TDT predictor and joint in plain fp32 on
  * CUDA cores (one persistent kernel) instead of the split-bf16 tensor-core steps; "gemm_pair_tiles" (0/1/2,
  * process-wide): two-CTA 256 x 256 GEMM tiles never / where they pay (default) / wherever they fit;

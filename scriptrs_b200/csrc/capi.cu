@@ -281,6 +281,7 @@ int32_t sb_ctx_set_option(sb_ctx* c, const char* name, int64_t value) {
     if (!c || !name) return fail(SB_INVALID_ARGUMENT, "null argument");
     const std::string n(name);
     if (n == "simt_attention") c->simt_attention = value != 0;
+    else if (n == "simt_subsample") c->simt_subsample = value != 0;
     else if (n == "simt_decode") c->simt_decode = value != 0;
     else if (n == "gemm_pair_tiles") sb::gemm_set_pair_tiles((int)(value < 0 ? 0 : (value > 2 ? 2 : value)));
     else if (n == "fp8") {

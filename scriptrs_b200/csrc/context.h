@@ -74,6 +74,7 @@ struct sb_ctx {
     bool fp8_hidden_amax = false; // FP8 feed-forward: quantise the hidden row by its true maximum (one more pass) instead of a bound
     bool simt_decode = false;     // fp32 CUDA-core decoder (one persistent kernel) instead of the tensor-core steps
     bool simt_attention = false;  // reference implementation of the attention kernel on CUDA cores (tests)
+    bool simt_subsample = false;  // fp32 CUDA-core version of the first two sub-sampling stages (tests)
     sb::EncoderWorkspace* enc_ws = nullptr;
     sb::DecodeWorkspace* dec_ws = nullptr;
     size_t workspace_budget = (size_t)12 << 30;  // bytes of encoder intermediates per group of clips

@@ -7,7 +7,9 @@
 // projections run as tcgen05 GEMMs over the packed rows (gemm.cu); the kernels in this file
 // cover what is not a GEMM and respect clip boundaries.
 //
-//   sub_conv0_dw1_kernel conv2d(1 -> 256, k3, s2, p1) + ReLU fused with the first depthwise conv2d(k3, s2, p1)
+//   sub_conv0_dw1_kernel conv2d(1 -> 256, k3, s2, p1) + ReLU fused with the first depthwise conv2d(k3, s2, p1), in fp32 on
+//                        CUDA cores: the in-library cross-check (option "simt_subsample") of the tensor-core kernel
+//                        in subsample.cu, which is the one the encoder runs
 //   sub_dw_kernel        second depthwise conv2d(k3, s2, p1) + bias (feeds the pointwise GEMM)
 //   layernorm_kernel     one warp per 1024-wide row, fp32 statistics, bf16 or f32 output
 //   relpos_attention_kernel  per (clip, head): scores = ((q + u) k^T + (q + v) p^T[i - j]) / sqrt(128),
@@ -24,6 +26,7 @@
 #include "attention.h"
 #include "encoder.h"
 #include "gemm.h"
+#include "subsample.h"
 #include "tc_ptx.cuh"
 
 namespace sb {
@@ -554,6 +557,8 @@ cudaError_t run_gemm_fp8(sb_ctx* c, const char* label, const uint8_t* a, const f
 cudaError_t encoder_configure() {
     cudaError_t e = attention_configure();
     if (e != cudaSuccess) return e;
+    e = subsample_configure();
+    if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(relpos_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)kAttSmemBytes);
 }
@@ -617,8 +622,14 @@ static cudaError_t encode_group(sb_ctx* c, const Model& m, const float* d_feats,
         int max_t2 = 0;
         for (int i = 0; i < n; ++i) max_t2 = std::max(max_t2, t2[i + 1] - t2[i]);
         const dim3 grid((max_t2 + kTO - 1) / kTO, n);
-        PROF("sub_conv0_dw1", (sub_conv0_dw1_kernel<kTO><<<grid, 256, 0, st>>>(d_feats, d_t0, d_t1, d_t2, m.sub0_w, m.sub0_b,
-                                                                              m.dw1_w, m.dw1_b, ws.y1.as<bf16>())));
+        if (c->simt_subsample) {
+            PROF("sub_conv0_dw1_simt", (sub_conv0_dw1_kernel<kTO><<<grid, 256, 0, st>>>(d_feats, d_t0, d_t1, d_t2, m.sub0_w, m.sub0_b,
+                                                                                       m.dw1_w, m.dw1_b, ws.y1.as<bf16>())));
+        } else {
+            c->prof.begin("sub_conv0_dw1", st);
+            ENC_CUDA(subsample_conv0_dw1_launch(d_feats, d_t0, d_t1, d_t2, n, max_t2, m.sub0_frag, m.dw1_pairs, ws.y1.p, st));
+            c->prof.end(st);
+        }
         c->launches += 1;
     }
     ENC_CUDA(run_gemm(c, "gemm_sub_pw", ws.y1.p, m.pw1_w, m.pw1_b, ws.y2.p, R2 * 32, kSubC, kSubC, kActRelu, kOutBf16, 1.0f));

@@ -19,6 +19,7 @@
 #include "decode.h"
 #include "model.h"
 #include "pipeline.h"
+#include "subsample.h"
 
 namespace sb {
 
@@ -154,6 +155,28 @@ int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensor
         m->sub0_b = ld.f32("subsampling.layers.0.bias", C);
         m->dw1_w = ld.tap_major(ld.get("subsampling.layers.2.weight", C * 9), C, 9, nullptr);
         m->dw1_b = ld.f32("subsampling.layers.2.bias", C);
+        {
+            // the same two stages as fp16 tensor-core operands (subsample.cu)
+            const float* w0 = ld.get("subsampling.layers.0.weight", C * 9);
+            const float* b0 = ld.get("subsampling.layers.0.bias", C);
+            const float* w1 = ld.get("subsampling.layers.2.weight", C * 9);
+            const float* b1 = ld.get("subsampling.layers.2.bias", C);
+            if (w0 && b0 && w1 && b1) {
+                std::vector<uint2> frags(subsample_frag_count());
+                subsample_build_frags(w0, b0, frags.data());
+                m->sub0_frag = ld.dalloc(frags.size() * sizeof(uint2));
+                if (m->sub0_frag && cudaMemcpy(m->sub0_frag, frags.data(), frags.size() * sizeof(uint2), cudaMemcpyHostToDevice) != cudaSuccess && ld.err.empty())
+                    ld.err = "cudaMemcpy failed while loading the model";
+                std::vector<float> tapm((size_t)9 * C);
+                for (int ch = 0; ch < C; ++ch)
+                    for (int k = 0; k < 9; ++k) tapm[(size_t)k * C + ch] = w1[(size_t)ch * 9 + k];
+                std::vector<uint32_t> pairs((size_t)10 * C / 2);
+                subsample_build_dw(tapm.data(), b1, pairs.data());
+                m->dw1_pairs = ld.dalloc(pairs.size() * sizeof(uint32_t));
+                if (m->dw1_pairs && cudaMemcpy(m->dw1_pairs, pairs.data(), pairs.size() * sizeof(uint32_t), cudaMemcpyHostToDevice) != cudaSuccess && ld.err.empty())
+                    ld.err = "cudaMemcpy failed while loading the model";
+            }
+        }
         m->pw1_w = ld.b16("subsampling.layers.3.weight", C * C);
         m->pw1_b = ld.f32("subsampling.layers.3.bias", C);
         m->dw2_w = ld.tap_major(ld.get("subsampling.layers.5.weight", C * 9), C, 9, nullptr);

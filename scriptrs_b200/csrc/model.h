@@ -71,6 +71,7 @@ struct Model {
     // sub-sampling
     float *sub0_w = nullptr, *sub0_b = nullptr;  // [256 x 9], [256]
     float *dw1_w = nullptr, *dw1_b = nullptr;    // [9 x 256] tap-major, [256]
+    void *sub0_frag = nullptr, *dw1_pairs = nullptr;  // fp16 operands of the tensor-core kernel for these two stages (subsample.h)
     float *dw2_w = nullptr, *dw2_b = nullptr;
     bf16 *pw1_w = nullptr, *pw2_w = nullptr;     // [256 x 256]
     float *pw1_b = nullptr, *pw2_b = nullptr;

@@ -178,3 +178,29 @@ def test_large_batch_reaches_two_cta_tiles_and_matches_single_cta_and_oracle(ctx
         r = eo.encoder_forward(w, feats[i], cfg)
         err = np.linalg.norm(pair[i] - r) / np.linalg.norm(r)
         assert err <= BF16_TOL, (i, err)
+
+
+def test_subsampling_tensor_core_kernel_against_cuda_core_kernel_and_oracle(ctx):
+    """The first two sub-sampling stages run as an fp16 tensor-core product + packed-fp16 depthwise stage; the fp32
+    CUDA-core kernel of the same stages (option simt_subsample) and the fp32 oracle are the checks.  0-block stack:
+    the encoder output is the sub-sampling output."""
+    import scriptrs_b200 as sb
+
+    cfg = eo.EncoderConfig(layers=0)
+    w = eo.seeded_weights(cfg, seed=17, std=0.05, plain_norms=False)
+    sb.load_model(ctx, w, encoder_layers=0)
+    rng = np.random.default_rng(9)
+    feats = [(rng.standard_normal((t, 128)) * s).astype(np.float32) for t, s in
+             ((1497, 1.0), (1, 1.0), (2, 3.0), (5, 1.0), (9, 0.1), (1001, 2.0), (333, 1.0), (8, 1.0), (1329, 1.0))]
+    tc = run_gpu(ctx, feats)
+    ctx.set_option("simt_subsample", 1)
+    try:
+        simt = run_gpu(ctx, feats)
+    finally:
+        ctx.set_option("simt_subsample", 0)
+    for f, a, b in zip(feats, tc, simt):
+        r = eo.encoder_forward(w, f, cfg)
+        assert np.isfinite(a).all()
+        assert np.linalg.norm(a - r) / np.linalg.norm(r) <= BF16_TOL, f.shape
+        assert np.linalg.norm(b - r) / np.linalg.norm(r) <= BF16_TOL, f.shape
+        assert np.linalg.norm(a - b) / np.linalg.norm(b) <= 1e-2, (f.shape, np.linalg.norm(a - b) / np.linalg.norm(b))
