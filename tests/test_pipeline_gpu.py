@@ -242,3 +242,23 @@ def test_int16_recording_gives_the_f32_token_streams(ctx, pipe):
     b = sb.transcribe_chunks(ctx, long16.astype(np.float32) / np.float32(32767.0), many)
     for x, y in zip(a.flat(), b.flat()):
         assert np.array_equal(x, y)
+
+
+def test_longform_run_multi_on_two_gpus(ctx, pipe):
+    """The same entry with one context per GPU (what a host crate binds for a multi-GPU box); skipped on a
+    single-GPU machine."""
+    import scriptrs_b200 as sb
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    second = sb.Context(1)
+    try:
+        sb.load_model(second, model_weights(), LAYERS, has_encoder=True, has_decoder=True)
+        audio = synth.long_audio(1_100_000, 8)
+        one = sb.LongFormTranscriptionPipeline(pipe).run(audio)
+        two = sb.LongFormTranscriptionPipeline(pipe, extra_contexts=[second]).run_with_config(
+            audio, sb.LongFormConfig(worker_count=2))
+        assert two.text == one.text and two.tokens == one.tokens and two.chunks == one.chunks
+        assert second.kernel_launches() > 0
+    finally:
+        second.close()
