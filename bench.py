@@ -380,6 +380,8 @@ def run_longform(args, rank, world, local):
     if fp8:
         ctx.set_option("fp8", 1)
         ctx.set_option("fp8_mask", args.fp8_mask)
+    if args.workspace_mb:
+        ctx.set_option("workspace_budget_mb", args.workspace_mb)
     vocab = sb.Vocabulary.from_tokens(bench_vocab_tokens())
 
     n = int(args.hours * 3600 * 16000)
@@ -777,6 +779,8 @@ def main():
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8"], help="longform: encoder GEMM precision")
     ap.add_argument("--fp8-mask", type=int, default=8, help="longform, --precision fp8: GEMM groups in e4m3 (1 ff up, 2 ff "
                     "down, 4 QKV, 8 first pointwise; 8 keeps the encoder within its 5e-2 accuracy goal, 15 = all)")
+    ap.add_argument("--workspace-mb", type=int, default=0, help="longform: encoder workspace budget per group of clips in MB "
+                    "(0 = the library's default)")
     ap.add_argument("--layers", type=int, default=24, help="longform workload: Conformer blocks (default 24)")
     ap.add_argument("--clips", type=int, default=0, help="frontend workload: clips per GPU (default 1024)")
     ap.add_argument("--stage-breakdown", action="store_true", help="longform: also time the three stage entry points")

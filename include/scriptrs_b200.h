@@ -116,7 +116,8 @@ int64_t sb_ctx_kernel_launches(const sb_ctx* ctx);
  * CUDA cores (one persistent kernel) instead of the split-bf16 tensor-core steps; "gemm_pair_tiles" (0/1/2,
  * process-wide): two-CTA 256 x 256 GEMM tiles never / where they pay (default) / wherever they fit;
  * "workspace_budget_mb":
- * bytes of encoder intermediates per group of clips (default 12288). */
+ * MB of encoder intermediates per group of clips (default 49152: the 2236 chunks of an 8 h recording form one group; a
+ * batch allocates only what it needs). */
 int32_t sb_ctx_set_option(sb_ctx* ctx, const char* name, int64_t value);
 
 /* In-situ timing (off by default): CUDA events around every kernel launch, summed per kernel label.

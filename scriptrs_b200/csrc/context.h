@@ -77,5 +77,5 @@ struct sb_ctx {
     bool simt_subsample = false;  // fp32 CUDA-core version of the first two sub-sampling stages (tests)
     sb::EncoderWorkspace* enc_ws = nullptr;
     sb::DecodeWorkspace* dec_ws = nullptr;
-    size_t workspace_budget = (size_t)12 << 30;  // bytes of encoder intermediates per group of clips
+    size_t workspace_budget = (size_t)48 << 30;  // bytes of encoder intermediates per group of clips (8 h of chunks fit one group)
 };
