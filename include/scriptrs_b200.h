@@ -61,15 +61,52 @@ typedef struct sb_overlap_config {
     int64_t max_model_samples; /* 240000 */
 } sb_overlap_config;
 
-/* LongFormConfig (src/long_form.rs:56-87).  mode 0 = Fast (the only mode built).
- * worker_count keeps the reference's meaning of "parallel chunk workers"; here a
- * worker is a GPU shard. */
+/* VadConfig (src/long_form/planner.rs:11-27). */
+typedef struct sb_vad_config {
+    float default_threshold; /* 0.85: positive speech threshold on the per-window probabilities */
+} sb_vad_config;
+
+/* VadSegmentationConfig (src/long_form/planner.rs:29-68), field for field; the Option<f32>
+ * negative_threshold is the pair (has_negative_threshold, negative_threshold). */
+typedef struct sb_vad_segmentation_config {
+    double min_speech_duration;        /* 0.15 */
+    double min_silence_duration;       /* 0.75 */
+    double max_speech_duration;        /* 14.0 (carried; the reference's planner does not read it) */
+    double speech_padding;             /* 0.1 */
+    float silence_threshold_for_split; /* 0.3 */
+    int32_t has_negative_threshold;    /* 0 = None */
+    float negative_threshold;
+    float negative_threshold_offset;   /* 0.15 */
+    double min_silence_at_max_speech;  /* 0.098 */
+    int32_t use_max_possible_silence_at_max_speech; /* 1 (carried; the reference's planner does not read it) */
+} sb_vad_segmentation_config;
+
+/* LongFormConfig (src/long_form.rs:56-87), field for field.  mode 0 = Fast (overlap chunks over the whole
+ * recording, the default), 1 = Vad (speech regions from per-window probabilities first).  worker_count keeps
+ * the reference's meaning of "parallel chunk workers"; here a worker is a GPU shard. */
 typedef struct sb_longform_config {
     int32_t mode;
     int64_t worker_count; /* 4 */
     sb_transcription_config transcription;
+    sb_vad_config vad;
+    sb_vad_segmentation_config segmentation;
     sb_overlap_config overlap;
 } sb_longform_config;
+
+/* SampleRange (src/long_form/planner.rs:5-9). */
+typedef struct sb_sample_range {
+    int64_t start;
+    int64_t end;
+} sb_sample_range;
+
+/* RegionTask (src/long_form.rs:488-499): a run of consecutive tasks and how their token streams are joined.
+ * kind 0 = Overlap (windows merged by merge_overlapping_windows), 1 = Segments (each task decoded on its
+ * own and shifted to its place in the recording). */
+typedef struct sb_region_task {
+    int32_t kind;
+    int64_t first_task;
+    int64_t n_tasks;
+} sb_region_task;
 
 /* ChunkTask (src/long_form.rs:468-476). */
 typedef struct sb_chunk_task {
@@ -89,6 +126,8 @@ const char* sb_status_string(int32_t status);
 void sb_default_transcription_config(sb_transcription_config* cfg);
 void sb_default_overlap_config(sb_overlap_config* cfg);
 void sb_default_longform_config(sb_longform_config* cfg);
+void sb_default_vad_config(sb_vad_config* cfg);                           /* planner.rs:19-27 */
+void sb_default_vad_segmentation_config(sb_vad_segmentation_config* cfg); /* planner.rs:52-68 */
 
 /* Creates a context on CUDA device `device` (frontend tables, stream, workspaces).
  * Replaces ParakeetFeatureExtractor::new (src/frontend.rs:88-102) and the
@@ -115,6 +154,9 @@ int64_t sb_ctx_kernel_launches(const sb_ctx* ctx);
  * instead of the tensor-core kernel; "simt_decode" (0/1): run the TDT predictor and joint in plain fp32 on
  * CUDA cores (one persistent kernel) instead of the split-bf16 tensor-core steps; "gemm_pair_tiles" (0/1/2,
  * process-wide): two-CTA 256 x 256 GEMM tiles never / where they pay (default) / wherever they fit;
+ * "vad_cluster" (4 or 8, default 8): thread blocks in the cluster that runs the VAD network's recurrence;
+ * "vad_segment_windows" (default 131072): windows the VAD network processes per pass (its work buffers hold 2560 bytes
+ * per window; the recurrent state is carried from pass to pass);
  * "workspace_budget_mb":
  * MB of encoder intermediates per group of clips (default 49152: the 2236 chunks of an 8 h recording form one group; a
  * batch allocates only what it needs). */
@@ -302,6 +344,33 @@ int32_t sb_merge_windows(const uint32_t* token_ids, const int64_t* frame_indices
                          int64_t* out_frame_indices, int64_t* out_durations, float* out_confidences, int64_t out_cap,
                          int64_t* n_out);
 
+/* ------------------------------------------------ VAD planning (LongFormMode::Vad) host logic */
+
+/* Windows process_coreml_vad walks over n_samples (src/long_form/vad.rs:72,78): ceil(n / 512). */
+int64_t sb_vad_num_windows(int64_t n_samples);
+
+/* detect_speech_regions (src/long_form/planner.rs:139-233): hysteresis over the per-window speech
+ * probabilities (window w covers samples [512 w, 512 w + 512)), minimum speech and silence spans, then padding
+ * shared between neighbouring regions.  *n_regions receives the count; regions may be NULL to size the buffer. */
+int32_t sb_vad_detect_speech_regions(const float* probabilities, int64_t n_probabilities, int64_t audio_len,
+                                     float threshold, const sb_vad_segmentation_config* cfg, sb_sample_range* regions,
+                                     int64_t cap, int64_t* n_regions);
+
+/* plan_region_subsegments (src/long_form/planner.rs:242-284) over the probabilities of the region's windows
+ * (region_probability_slice, planner.rs:235-240): cuts a region longer than max_chunk_samples at its longest
+ * silences.  *n_segments is -1 where the reference returns None (no usable silence: overlap fallback). */
+int32_t sb_vad_plan_region_subsegments(const sb_sample_range* region, const float* region_probabilities,
+                                       int64_t n_probabilities, const sb_vad_segmentation_config* cfg,
+                                       int64_t max_chunk_samples, sb_sample_range* segments, int64_t cap,
+                                       int64_t* n_segments);
+
+/* build_execution_plan + build_region_plan (src/long_form.rs:421-437,508-548): one region task per speech
+ * region — a single segment if it fits max_audio_samples, else silence-split segments, else overlap windows
+ * over the region.  `probabilities` covers the whole recording.  tasks / region_tasks may be NULL to size. */
+int32_t sb_plan_vad(const sb_longform_config* cfg, const sb_sample_range* regions, int64_t n_regions,
+                    const float* probabilities, int64_t n_probabilities, sb_chunk_task* tasks, int64_t task_cap,
+                    int64_t* n_tasks, sb_region_task* region_tasks, int64_t region_cap);
+
 /* ----------------------------------------------------------- vocabulary and text */
 
 typedef struct sb_vocab sb_vocab;
@@ -376,9 +445,11 @@ int32_t sb_transcribe_chunks_device(sb_ctx* ctx, const float* d_audio, int64_t n
 int32_t sb_pipeline_run(sb_ctx* ctx, const sb_vocab* vocab, const float* audio, int64_t n_samples,
                         const sb_transcription_config* cfg, sb_result** out);
 
-/* LongFormTranscriptionPipeline::run_with_config (src/long_form.rs:153-166), Fast mode: audio of at
- * most max_audio_samples goes through the single-chunk path, longer audio is planned into overlap
- * chunks, transcribed on this GPU, merged and decoded (src/long_form.rs:218-245,344-419). */
+/* LongFormTranscriptionPipeline::run_with_config (src/long_form.rs:153-166): audio of at most
+ * max_audio_samples goes through the single-chunk path; longer audio is planned into overlap chunks
+ * (mode 0, Fast) or into speech regions found by the loaded VAD network (mode 1, Vad: sb_vad_load first, else
+ * SB_MISSING_MODEL_ASSET as in long_form.rs:194-199), transcribed on this GPU, merged and decoded
+ * (src/long_form.rs:188-245,344-419). */
 int32_t sb_longform_run(sb_ctx* ctx, const sb_vocab* vocab, const float* audio, int64_t n_samples,
                         const sb_longform_config* cfg, sb_result** out);
 
@@ -395,6 +466,53 @@ int32_t sb_longform_run_multi(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* voca
 int32_t sb_longform_finish(const sb_vocab* vocab, int64_t audio_len, const uint32_t* token_ids,
                            const int64_t* frame_indices, const int64_t* durations, const float* confidences,
                            const int64_t* win_off, int64_t n_windows, sb_result** out);
+
+/* build_parallel_result (src/long_form.rs:344-374) for callers that ran sb_transcribe_chunks themselves on a
+ * plan of region tasks (sb_plan_vad, or one Overlap region for the Fast mode): Overlap regions are merged and
+ * decoded against the recording's duration (decode_overlap_tasks, long_form.rs:404-419); the tasks of a
+ * Segments region are decoded one by one against their own duration and shifted by their start
+ * (decode_segment_tasks, long_form.rs:376-402,649-661); each region with tokens becomes one chunk.  Task i's
+ * tokens are elements [win_off[i], win_off[i+1]) of the arrays. */
+int32_t sb_longform_finish_regions(const sb_vocab* vocab, int64_t audio_len, const sb_chunk_task* tasks,
+                                   int64_t n_tasks, const sb_region_task* region_tasks, int64_t n_regions,
+                                   const uint32_t* token_ids, const int64_t* frame_indices, const int64_t* durations,
+                                   const float* confidences, const int64_t* win_off, sb_result** out);
+
+/* run_vad_long_form (src/long_form.rs:188-216) from the probabilities on: for callers that bring their own
+ * voice-activity detector.  No speech region gives the empty result (TranscriptionResult::empty) with the
+ * recording's duration.  Audio of at most max_audio_samples takes the single-chunk path whatever the mode
+ * (long_form.rs:161-163). */
+int32_t sb_longform_run_with_probabilities(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio,
+                                           int64_t n_samples, const sb_longform_config* cfg,
+                                           const float* probabilities, int64_t n_probabilities, sb_result** out);
+
+/* ------------------------------------------------------------------ VAD network */
+
+/* Loads the streaming voice-activity network that sb_longform_run uses in mode 1 (SileroVad::new,
+ * src/long_form/vad.rs:15-19; asset "vad/silero-vad.mlmodelc", src/models.rs:10).  The network has the public
+ * Silero VAD (16 kHz) shape behind the reference's I/O contract (src/coreml.rs:188-236: audio [576] = 64
+ * context + 512 new samples, h / c [128] in, probability and h / c out):
+ *   "stft.forward_basis_buffer" [258, 1, 256]   real rows 0..128, imaginary rows 129..257; stride 128 over the
+ *                                               576 samples extended by 64 reflected on the right -> 4 frames
+ *   "encoder.{0,1,2,3}.reparam_conv.{weight,bias}"  Conv1d k = 3, padding 1, strides 1, 2, 2, 1:
+ *                                               129 -> 128 -> 64 -> 64 -> 128 channels, ReLU after each
+ *   "decoder.rnn.{weight_ih,weight_hh,bias_ih,bias_hh}"  LSTMCell(128, 128), gate order i, f, g, o
+ *   "decoder.decoder.2.{weight,bias}"           ReLU, Conv1d 128 -> 1 (k = 1), sigmoid
+ * A missing tensor fails with SB_MISSING_MODEL_ASSET. */
+int32_t sb_vad_load(sb_ctx* ctx, const sb_tensor* tensors, int64_t n_tensors);
+/* The same from a weight file in the layout sb_model_load_file reads (names optionally behind "_model."). */
+int32_t sb_vad_load_file(sb_ctx* ctx, const char* path);
+
+/* SileroVad::process (src/long_form/vad.rs:61-98) for a whole recording in host memory: one probability per
+ * 512-sample window; the last window is filled up with its last sample; every window sees the 64 samples
+ * before it (zeros for the first) and the recurrent state left by the window before.  The convolutional part
+ * runs for all windows at once, the recurrence as one persistent kernel.  probabilities needs
+ * sb_vad_num_windows(n_samples) entries.  SB_MISSING_MODEL_ASSET if no network is loaded; empty audio gives
+ * zero probabilities (vad.rs:65-67). */
+int32_t sb_vad_process(sb_ctx* ctx, const float* audio, int64_t n_samples, float* probabilities, int64_t cap,
+                       int64_t* n_probabilities);
+/* The same with the recording and the result in device memory (asynchronous on the context's stream). */
+int32_t sb_vad_process_device(sb_ctx* ctx, const float* d_audio, int64_t n_samples, float* d_probabilities);
 
 /* ------------------------------------------------------------------ GEMM */
 

@@ -29,9 +29,29 @@ class OverlapConfigC(C.Structure):
     _fields_ = [("overlap_seconds", C.c_double), ("context_samples", C.c_int64), ("max_model_samples", C.c_int64)]
 
 
+class VadConfigC(C.Structure):
+    _fields_ = [("default_threshold", C.c_float)]
+
+
+class VadSegmentationConfigC(C.Structure):
+    _fields_ = [("min_speech_duration", C.c_double), ("min_silence_duration", C.c_double),
+                ("max_speech_duration", C.c_double), ("speech_padding", C.c_double),
+                ("silence_threshold_for_split", C.c_float), ("has_negative_threshold", C.c_int32),
+                ("negative_threshold", C.c_float), ("negative_threshold_offset", C.c_float),
+                ("min_silence_at_max_speech", C.c_double), ("use_max_possible_silence_at_max_speech", C.c_int32)]
+
+
 class LongFormConfigC(C.Structure):
     _fields_ = [("mode", C.c_int32), ("worker_count", C.c_int64), ("transcription", TranscriptionConfigC),
-                ("overlap", OverlapConfigC)]
+                ("vad", VadConfigC), ("segmentation", VadSegmentationConfigC), ("overlap", OverlapConfigC)]
+
+
+class SampleRangeC(C.Structure):
+    _fields_ = [("start", C.c_int64), ("end", C.c_int64)]
+
+
+class RegionTaskC(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("first_task", C.c_int64), ("n_tasks", C.c_int64)]
 
 
 class TensorC(C.Structure):
@@ -61,6 +81,8 @@ SIGNATURES = {
     "sb_default_transcription_config": (None, [C.POINTER(TranscriptionConfigC)]),
     "sb_default_overlap_config": (None, [C.POINTER(OverlapConfigC)]),
     "sb_default_longform_config": (None, [C.POINTER(LongFormConfigC)]),
+    "sb_default_vad_config": (None, [C.POINTER(VadConfigC)]),
+    "sb_default_vad_segmentation_config": (None, [C.POINTER(VadSegmentationConfigC)]),
     "sb_ctx_create": (_I32, [_I32, C.POINTER(_VP)]),
     "sb_ctx_destroy": (None, [_VP]),
     "sb_ctx_set_stream": (_I32, [_VP, _VP]),
@@ -88,6 +110,12 @@ SIGNATURES = {
     "sb_parallel_worker_count": (_I64, [_I64, _I64]),
     "sb_apply_time_offsets": (_I32, [_VP, _VP, _VP, _VP, _I64, _I64, _I64, C.POINTER(_I64)]),
     "sb_merge_windows": (_I32, [_VP, _VP, _VP, _VP, _VP, _I64, _VP, _VP, _VP, _VP, _I64, C.POINTER(_I64)]),
+    "sb_vad_num_windows": (_I64, [_I64]),
+    "sb_vad_detect_speech_regions": (_I32, [_VP, _I64, _I64, C.c_float, C.POINTER(VadSegmentationConfigC), _VP, _I64,
+                                            C.POINTER(_I64)]),
+    "sb_vad_plan_region_subsegments": (_I32, [C.POINTER(SampleRangeC), _VP, _I64, C.POINTER(VadSegmentationConfigC), _I64,
+                                              _VP, _I64, C.POINTER(_I64)]),
+    "sb_plan_vad": (_I32, [C.POINTER(LongFormConfigC), _VP, _I64, _VP, _I64, _VP, _I64, C.POINTER(_I64), _VP, _I64]),
     "sb_vocab_load": (_I32, [C.c_char_p, C.POINTER(_VP)]),
     "sb_vocab_from_text": (_I32, [C.c_char_p, _I64, C.POINTER(_VP)]),
     "sb_vocab_free": (None, [_VP]),
@@ -116,6 +144,13 @@ SIGNATURES = {
     "sb_longform_run": (_I32, [_VP, _VP, _VP, _I64, C.POINTER(LongFormConfigC), C.POINTER(_VP)]),
     "sb_longform_run_multi": (_I32, [C.POINTER(_VP), _I64, _VP, _VP, _I64, C.POINTER(LongFormConfigC), C.POINTER(_VP)]),
     "sb_longform_finish": (_I32, [_VP, _I64, _VP, _VP, _VP, _VP, _VP, _I64, C.POINTER(_VP)]),
+    "sb_longform_finish_regions": (_I32, [_VP, _I64, _VP, _I64, _VP, _I64, _VP, _VP, _VP, _VP, _VP, C.POINTER(_VP)]),
+    "sb_longform_run_with_probabilities": (_I32, [C.POINTER(_VP), _I64, _VP, _VP, _I64, C.POINTER(LongFormConfigC), _VP,
+                                                  _I64, C.POINTER(_VP)]),
+    "sb_vad_load": (_I32, [_VP, C.POINTER(TensorC), _I64]),
+    "sb_vad_load_file": (_I32, [_VP, C.c_char_p]),
+    "sb_vad_process": (_I32, [_VP, _VP, _I64, _VP, _I64, C.POINTER(_I64)]),
+    "sb_vad_process_device": (_I32, [_VP, _VP, _I64, _VP]),
     "sb_gemm": (_I32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I64, _I64, _I32, _I32, _I32, C.c_float]),
 }
 

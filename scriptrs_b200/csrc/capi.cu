@@ -15,6 +15,7 @@
 #include "host/weights_file.h"
 #include "model.h"
 #include "pipeline.h"
+#include "vad.h"
 
 namespace sb {
 
@@ -183,10 +184,27 @@ void sb_default_overlap_config(sb_overlap_config* c) {
     c->max_model_samples = 240000;
 }
 
+void sb_default_vad_config(sb_vad_config* c) { c->default_threshold = 0.85f; }
+
+void sb_default_vad_segmentation_config(sb_vad_segmentation_config* c) {
+    c->min_speech_duration = 0.15;
+    c->min_silence_duration = 0.75;
+    c->max_speech_duration = 14.0;
+    c->speech_padding = 0.1;
+    c->silence_threshold_for_split = 0.3f;
+    c->has_negative_threshold = 0;
+    c->negative_threshold = 0.0f;
+    c->negative_threshold_offset = 0.15f;
+    c->min_silence_at_max_speech = 0.098;
+    c->use_max_possible_silence_at_max_speech = 1;
+}
+
 void sb_default_longform_config(sb_longform_config* c) {
     c->mode = 0;
     c->worker_count = 4;
     sb_default_transcription_config(&c->transcription);
+    sb_default_vad_config(&c->vad);
+    sb_default_vad_segmentation_config(&c->segmentation);
     sb_default_overlap_config(&c->overlap);
 }
 
@@ -242,6 +260,10 @@ void sb_ctx_destroy(sb_ctx* c) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
     sb_model_free_internal(c);
+    if (c->vad) {
+        c->vad->release();
+        delete c->vad;
+    }
     c->clip_off.release();
     c->frame_off.release();
     c->pcm_stage.release();
@@ -283,6 +305,18 @@ int32_t sb_ctx_set_option(sb_ctx* c, const char* name, int64_t value) {
     if (n == "simt_attention") c->simt_attention = value != 0;
     else if (n == "simt_subsample") c->simt_subsample = value != 0;
     else if (n == "simt_decode") c->simt_decode = value != 0;
+    else if (n == "vad_segment_windows") {
+        if (value < 1 || value > (1 << 22)) return fail(SB_INVALID_ARGUMENT, "vad_segment_windows must be in [1, 4194304]");
+        c->vad_segment_windows = (int)value;
+    }
+    else if (n == "vad_row_threads") {
+        if (value != 2 && value != 4) return fail(SB_INVALID_ARGUMENT, "vad_row_threads must be 2 or 4");
+        c->vad_row_threads = (int)value;
+    }
+    else if (n == "vad_cluster") {
+        if (value != 4 && value != 8) return fail(SB_INVALID_ARGUMENT, "vad_cluster must be 4 or 8");
+        c->vad_cluster = (int)value;
+    }
     else if (n == "gemm_pair_tiles") sb::gemm_set_pair_tiles((int)(value < 0 ? 0 : (value > 2 ? 2 : value)));
     else if (n == "fp8") {
         if (value && (!c->model || !c->model->has_fp8))
@@ -411,6 +445,46 @@ int32_t sb_model_load_file(sb_ctx* c, const sb_model_desc* desc, const char* pat
     sb_model_desc d = *desc;
     if (d.encoder_layers < 0) d.encoder_layers = max_layer + 1;  // as many Conformer blocks as the file holds
     return model_load(c, &d, tensors.data(), (int64_t)tensors.size());
+}
+
+int32_t sb_vad_load(sb_ctx* c, const sb_tensor* tensors, int64_t n_tensors) {
+    if (!c || n_tensors < 0 || (n_tensors > 0 && !tensors)) return fail(SB_INVALID_ARGUMENT, "null argument");
+    return vad_load(c, tensors, n_tensors);
+}
+
+int32_t sb_vad_load_file(sb_ctx* c, const char* path) {
+    if (!c || !path) return fail(SB_INVALID_ARGUMENT, "null argument");
+    WeightFile wf;
+    bool missing = false;
+    const std::string err = weight_file_open(path, &wf, &missing);
+    if (!err.empty()) return fail(missing ? SB_MISSING_MODEL_ASSET : SB_IO, err);  // models.rs:68-78
+    std::vector<sb_tensor> tensors;
+    for (auto& kv : wf.entries) tensors.push_back(sb_tensor{kv.first.c_str(), wf.as_f32(kv.first), kv.second.numel()});
+    return vad_load(c, tensors.data(), (int64_t)tensors.size());
+}
+
+int32_t sb_vad_process_device(sb_ctx* c, const float* d_audio, int64_t n_samples, float* d_prob) {
+    if (!c || n_samples < 0 || (n_samples > 0 && (!d_audio || !d_prob))) return fail(SB_INVALID_ARGUMENT, "null argument");
+    return vad_process_device(c, d_audio, n_samples, d_prob);
+}
+
+int32_t sb_vad_process(sb_ctx* c, const float* audio, int64_t n_samples, float* prob, int64_t cap, int64_t* n_prob) {
+    if (!c || !n_prob || n_samples < 0 || (n_samples > 0 && !audio)) return fail(SB_INVALID_ARGUMENT, "null argument");
+    if (!c->vad) return fail(SB_MISSING_MODEL_ASSET, "missing model asset: vad network (sb_vad_load)");
+    const int64_t n = n_samples > 0 ? (n_samples + kVadWindow - 1) / kVadWindow : 0;
+    *n_prob = n;
+    if (n == 0) return SB_OK;  // vad.rs:65-67
+    if (!prob || cap < n) return fail(SB_BUFFER_TOO_SMALL, "probability buffer too small");
+    SB_CUDA(cudaSetDevice(c->device));
+    VadModel& m = *c->vad;
+    SB_CUDA(m.audio.ensure(sizeof(float) * (size_t)n_samples));
+    SB_CUDA(m.prob.ensure(sizeof(float) * (size_t)n));
+    SB_CUDA(cudaMemcpyAsync(m.audio.p, audio, sizeof(float) * (size_t)n_samples, cudaMemcpyHostToDevice, c->stream));
+    const int32_t s = vad_process_device(c, m.audio.as<float>(), n_samples, m.prob.as<float>());
+    if (s != SB_OK) return s;
+    SB_CUDA(cudaMemcpyAsync(prob, m.prob.p, sizeof(float) * (size_t)n, cudaMemcpyDeviceToHost, c->stream));
+    SB_CUDA(cudaStreamSynchronize(c->stream));
+    return SB_OK;
 }
 
 int64_t sb_weights_file_list(const char* path, char* buf, int64_t cap) {

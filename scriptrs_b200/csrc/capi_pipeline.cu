@@ -221,6 +221,64 @@ int32_t sb_merge_windows(const uint32_t* tok, const int64_t* frm, const int64_t*
     return SB_OK;
 }
 
+// ------------------------------------------------------------------ VAD planning
+int64_t sb_vad_num_windows(int64_t n_samples) {
+    return n_samples > 0 ? (n_samples + kVadWindowSamples - 1) / kVadWindowSamples : 0;
+}
+
+int32_t sb_vad_detect_speech_regions(const float* prob, int64_t n_prob, int64_t audio_len, float threshold,
+                                     const sb_vad_segmentation_config* cfg, sb_sample_range* regions, int64_t cap,
+                                     int64_t* n_regions) {
+    if (!n_regions || n_prob < 0 || (n_prob > 0 && !prob)) return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_vad_segmentation_config sc;
+    if (cfg) sc = *cfg; else sb_default_vad_segmentation_config(&sc);
+    const std::vector<sb_sample_range> r = detect_speech_regions(prob, n_prob, audio_len, threshold, sc);
+    *n_regions = (int64_t)r.size();
+    if (!regions) return SB_OK;
+    if (cap < (int64_t)r.size()) return fail(SB_BUFFER_TOO_SMALL, "region buffer too small");
+    std::copy(r.begin(), r.end(), regions);
+    return SB_OK;
+}
+
+int32_t sb_vad_plan_region_subsegments(const sb_sample_range* region, const float* prob, int64_t n_prob,
+                                       const sb_vad_segmentation_config* cfg, int64_t max_chunk_samples,
+                                       sb_sample_range* segments, int64_t cap, int64_t* n_segments) {
+    if (!region || !n_segments || n_prob < 0 || (n_prob > 0 && !prob)) return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_vad_segmentation_config sc;
+    if (cfg) sc = *cfg; else sb_default_vad_segmentation_config(&sc);
+    std::vector<sb_sample_range> parts;
+    if (!plan_region_subsegments(*region, prob, n_prob, sc, max_chunk_samples, &parts)) {
+        *n_segments = -1;
+        return SB_OK;
+    }
+    *n_segments = (int64_t)parts.size();
+    if (!segments) return SB_OK;
+    if (cap < (int64_t)parts.size()) return fail(SB_BUFFER_TOO_SMALL, "segment buffer too small");
+    std::copy(parts.begin(), parts.end(), segments);
+    return SB_OK;
+}
+
+int32_t sb_plan_vad(const sb_longform_config* cfg, const sb_sample_range* regions, int64_t n_regions, const float* prob,
+                    int64_t n_prob, sb_chunk_task* tasks, int64_t task_cap, int64_t* n_tasks, sb_region_task* region_tasks,
+                    int64_t region_cap) {
+    if (!n_tasks || n_regions < 0 || (n_regions > 0 && !regions) || n_prob < 0 || (n_prob > 0 && !prob))
+        return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_longform_config lc;
+    if (cfg) lc = *cfg; else sb_default_longform_config(&lc);
+    const ExecutionPlan plan =
+        build_vad_plan(std::vector<sb_sample_range>(regions, regions + n_regions), prob, n_prob, lc);
+    *n_tasks = (int64_t)plan.tasks.size();
+    if (tasks) {
+        if (task_cap < (int64_t)plan.tasks.size()) return fail(SB_BUFFER_TOO_SMALL, "task buffer too small");
+        std::copy(plan.tasks.begin(), plan.tasks.end(), tasks);
+    }
+    if (region_tasks) {
+        if (region_cap < n_regions) return fail(SB_BUFFER_TOO_SMALL, "region task buffer too small");
+        std::copy(plan.regions.begin(), plan.regions.end(), region_tasks);
+    }
+    return SB_OK;
+}
+
 // ------------------------------------------------------------------ vocabulary / text / results
 int32_t sb_vocab_load(const char* path, sb_vocab** out) {
     if (!path || !out) return fail(SB_INVALID_ARGUMENT, "null argument");
@@ -443,27 +501,45 @@ int32_t sb_longform_finish(const sb_vocab* vocab, int64_t audio_len, const uint3
     return SB_OK;
 }
 
-int32_t sb_longform_run_multi(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio,
-                              int64_t n_samples, const sb_longform_config* cfg, sb_result** out) {
-    if (!ctxs || n_ctx <= 0 || !vocab || !out) return fail(SB_INVALID_ARGUMENT, "null argument");
-    sb_longform_config lc;
-    if (cfg) lc = *cfg; else sb_default_longform_config(&lc);
-    if (lc.mode != 0) return fail(SB_INVALID_ARGUMENT, "only the Fast long-form mode is available");
-    int32_t s = check_config(lc.transcription);
-    if (s != SB_OK) return s;
-    if (n_samples <= 0 || !audio) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // long_form.rs:158
-    if (n_samples <= lc.transcription.max_audio_samples)                                 // long_form.rs:161-163
-        return sb_pipeline_run(ctxs[0], vocab, audio, n_samples, &lc.transcription, out);
-    const std::vector<sb_chunk_task> tasks = plan_fast_tasks(n_samples, lc.overlap);
-    const int64_t n_tasks = (int64_t)tasks.size();
-    // long_form.rs:594-600, a worker being a GPU shard here
+int32_t sb_longform_finish_regions(const sb_vocab* vocab, int64_t audio_len, const sb_chunk_task* tasks, int64_t n_tasks,
+                                   const sb_region_task* region_tasks, int64_t n_regions, const uint32_t* tok,
+                                   const int64_t* frm, const int64_t* dur, const float* conf, const int64_t* win_off,
+                                   sb_result** out) {
+    if (!vocab || !out || n_tasks < 0 || n_regions < 0 || (n_tasks > 0 && (!tasks || !win_off)) ||
+        (n_regions > 0 && !region_tasks))
+        return fail(SB_INVALID_ARGUMENT, "null argument");
+    for (int64_t r = 0; r < n_regions; ++r)
+        if (region_tasks[r].first_task < 0 || region_tasks[r].n_tasks < 0 ||
+            region_tasks[r].first_task + region_tasks[r].n_tasks > n_tasks)
+            return fail(SB_INVALID_ARGUMENT, "region task outside the task list");
+    std::vector<RawTokens> raw((size_t)n_tasks);
+    for (int64_t i = 0; i < n_tasks; ++i) raw[(size_t)i] = raw_from_arrays(tok, frm, dur, conf, win_off[i], win_off[i + 1]);
+    sb_result* res = new sb_result();
+    res->r = build_plan_result(vocab->v, audio_len, tasks, region_tasks, n_regions, raw);
+    *out = res;
+    return SB_OK;
+}
+
+namespace {
+
+// execute_plan (src/long_form.rs:232-245): the tasks go to min(worker_count, n_ctx, tasks) GPU shards in
+// contiguous blocks (run_parallel_regions, long_form.rs:266-314); build_parallel_result joins them.
+int32_t execute_plan(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio, int64_t n_samples,
+                     const sb_longform_config& lc, const ExecutionPlan& plan, sb_result** out) {
+    sb_result* res = new sb_result();
+    const int64_t n_tasks = (int64_t)plan.tasks.size();
+    if (n_tasks == 0) {  // TranscriptionResult::empty
+        res->r.duration_seconds = (double)n_samples / 16000.0;
+        *out = res;
+        return SB_OK;
+    }
     const int64_t shards = parallel_worker_count(n_tasks, std::min<int64_t>(lc.worker_count, n_ctx));
     std::vector<std::vector<RawTokens>> parts((size_t)shards);
     std::vector<int32_t> status((size_t)shards, SB_OK);
     std::vector<std::string> errors((size_t)shards);
     auto work = [&](int64_t k) {
         const int64_t a = n_tasks * k / shards, b = n_tasks * (k + 1) / shards;
-        status[k] = transcribe_tasks(ctxs[k], audio, n_samples, tasks.data() + a, b - a, lc.transcription, &parts[k]);
+        status[k] = transcribe_tasks(ctxs[k], audio, n_samples, plan.tasks.data() + a, b - a, lc.transcription, &parts[k]);
         if (status[k] != SB_OK) errors[k] = sb_last_error();
     };
     if (shards == 1) {
@@ -474,15 +550,63 @@ int32_t sb_longform_run_multi(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* voca
         for (auto& t : th) t.join();
     }
     for (int64_t k = 0; k < shards; ++k)  // the first failing shard aborts the call (long_form.rs:328-332)
-        if (status[k] != SB_OK) return fail((sb_status)status[k], errors[k]);
-    OverlapMerger m;
+        if (status[k] != SB_OK) {
+            delete res;
+            return fail((sb_status)status[k], errors[k]);
+        }
+    std::vector<RawTokens> raw;
+    raw.reserve((size_t)n_tasks);
     for (auto& p : parts)
-        for (auto& r : p) m.push(r);
-    TranscriptionResult merged = decode_tokens(vocab->v, m.merged(), (double)n_samples / 16000.0);
-    sb_result* res = new sb_result();
-    res->r = long_form_result(std::move(merged.tokens), n_samples);
+        for (auto& r : p) raw.push_back(std::move(r));
+    res->r = build_plan_result(vocab->v, n_samples, plan.tasks.data(), plan.regions.data(), (int64_t)plan.regions.size(), raw);
     *out = res;
     return SB_OK;
+}
+
+int32_t run_vad_plan(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio, int64_t n_samples,
+                     const sb_longform_config& lc, const float* prob, int64_t n_prob, sb_result** out) {
+    // long_form.rs:200-216; VadSegmentationConfig::threshold returns the VadConfig's value (planner.rs:71-73)
+    const std::vector<sb_sample_range> regions =
+        detect_speech_regions(prob, n_prob, n_samples, lc.vad.default_threshold, lc.segmentation);
+    return execute_plan(ctxs, n_ctx, vocab, audio, n_samples, lc, build_vad_plan(regions, prob, n_prob, lc), out);
+}
+
+}  // namespace
+
+int32_t sb_longform_run_with_probabilities(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio,
+                                           int64_t n_samples, const sb_longform_config* cfg, const float* prob,
+                                           int64_t n_prob, sb_result** out) {
+    if (!ctxs || n_ctx <= 0 || !vocab || !out || n_prob < 0 || (n_prob > 0 && !prob))
+        return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_longform_config lc;
+    if (cfg) lc = *cfg; else sb_default_longform_config(&lc);
+    int32_t s = check_config(lc.transcription);
+    if (s != SB_OK) return s;
+    if (n_samples <= 0 || !audio) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // long_form.rs:158
+    if (n_samples <= lc.transcription.max_audio_samples)                                 // long_form.rs:161-163
+        return sb_pipeline_run(ctxs[0], vocab, audio, n_samples, &lc.transcription, out);
+    return run_vad_plan(ctxs, n_ctx, vocab, audio, n_samples, lc, prob, n_prob, out);
+}
+
+int32_t sb_longform_run_multi(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio,
+                              int64_t n_samples, const sb_longform_config* cfg, sb_result** out) {
+    if (!ctxs || n_ctx <= 0 || !vocab || !out) return fail(SB_INVALID_ARGUMENT, "null argument");
+    sb_longform_config lc;
+    if (cfg) lc = *cfg; else sb_default_longform_config(&lc);
+    if (lc.mode != 0 && lc.mode != 1) return fail(SB_INVALID_ARGUMENT, "long-form mode must be 0 (Fast) or 1 (Vad)");
+    int32_t s = check_config(lc.transcription);
+    if (s != SB_OK) return s;
+    if (n_samples <= 0 || !audio) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // long_form.rs:158
+    if (n_samples <= lc.transcription.max_audio_samples)                                 // long_form.rs:161-163
+        return sb_pipeline_run(ctxs[0], vocab, audio, n_samples, &lc.transcription, out);
+    if (lc.mode == 0) return execute_plan(ctxs, n_ctx, vocab, audio, n_samples, lc, build_fast_plan(n_samples, lc), out);
+    // long_form.rs:193-200: the VAD network is needed only when the mode asks for it
+    if (!ctxs[0]->vad) return fail(SB_MISSING_MODEL_ASSET, "missing model asset: vad/silero-vad (load it with sb_vad_load)");
+    std::vector<float> prob((size_t)sb_vad_num_windows(n_samples));
+    int64_t n_prob = 0;
+    s = sb_vad_process(ctxs[0], audio, n_samples, prob.data(), (int64_t)prob.size(), &n_prob);
+    if (s != SB_OK) return s;
+    return run_vad_plan(ctxs, n_ctx, vocab, audio, n_samples, lc, prob.data(), n_prob, out);
 }
 
 int32_t sb_longform_run(sb_ctx* c, const sb_vocab* vocab, const float* audio, int64_t n_samples,

@@ -50,6 +50,7 @@ struct Profiler {
 struct Model;             // encoder + predictor + joint weights (model.h)
 struct EncoderWorkspace;  // encoder.h
 struct DecodeWorkspace;   // pipeline.cu
+struct VadModel;          // vad.h
 int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensors, int64_t n_tensors);
 
 }  // namespace sb
@@ -67,6 +68,10 @@ struct sb_ctx {
     // frontend workspaces
     sb::Buffer clip_off, frame_off, pcm_stage, feat_stage, enc_stage;
     sb::Model* model = nullptr;
+    sb::VadModel* vad = nullptr;  // voice-activity network of the VAD long-form mode
+    int vad_cluster = 8;          // CTAs in the cluster that runs the VAD recurrence (4 or 8)
+    int vad_row_threads = 2;      // threads that share one row of the recurrent matrix (2 or 4)
+    int vad_segment_windows = 131072;  // windows per pass of the VAD network (268 MB of gate inputs)
     sb::Profiler prof;
     bool fp8 = false;             // FP8 e4m3 GEMMs in the Conformer blocks (needs fp8 weights)
     int fp8_mask = 8;             // which GEMMs take the FP8 path: 1 ff up, 2 ff down, 4 QKV, 8 first pointwise

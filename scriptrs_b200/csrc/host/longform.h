@@ -34,6 +34,27 @@ class OverlapMerger {
 
 RawTokens merge_overlapping_windows(const std::vector<RawTokens>& windows);
 
+// ------------------------------------------------------------------ VAD planning (vad_plan.cpp)
+constexpr int64_t kVadWindowSamples = 512;   // constants.rs:7
+constexpr int64_t kVadContextSamples = 64;   // constants.rs:9
+constexpr int64_t kVadStateSize = 128;       // constants.rs:11
+
+// planner.rs:139-233
+std::vector<sb_sample_range> detect_speech_regions(const float* prob, int64_t n_prob, int64_t audio_len, float threshold,
+                                                   const sb_vad_segmentation_config& cfg);
+// planner.rs:242-284; returns false where the reference returns None
+bool plan_region_subsegments(sb_sample_range region, const float* region_prob, int64_t n_prob,
+                             const sb_vad_segmentation_config& cfg, int64_t max_chunk_samples,
+                             std::vector<sb_sample_range>* out);
+// long_form.rs:421-437,508-582
+struct ExecutionPlan {
+    std::vector<sb_chunk_task> tasks;
+    std::vector<sb_region_task> regions;
+};
+ExecutionPlan build_vad_plan(const std::vector<sb_sample_range>& regions, const float* prob, int64_t n_prob,
+                             const sb_longform_config& cfg);
+ExecutionPlan build_fast_plan(int64_t audio_len, const sb_longform_config& cfg);  // long_form.rs:439-459
+
 // ------------------------------------------------------------------ text
 struct Vocabulary {
     std::vector<std::string> id_to_token;
@@ -63,9 +84,14 @@ struct TranscriptionResult {
 // file could not be read.
 std::string vocabulary_from_file(const std::string& path, Vocabulary* out, bool* io_error);
 std::string vocabulary_from_text(const std::string& text, Vocabulary* out);
+// str::trim (Unicode White_Space) as join_token_text applies it, long_form.rs:613-620
+std::string trim_whitespace(const std::string& s);
 // decode.rs:39-104
 TranscriptionResult decode_tokens(const Vocabulary& vocab, const RawTokens& raw, double duration_seconds);
 // long_form.rs:344-374,602-647 for the single Overlap region of the Fast mode
 TranscriptionResult long_form_result(std::vector<TimedToken> tokens, int64_t audio_len);
+// long_form.rs:344-419,602-661: the result of an execution plan from its tasks' token streams (raw[i] is consumed)
+TranscriptionResult build_plan_result(const Vocabulary& vocab, int64_t audio_len, const sb_chunk_task* tasks,
+                                      const sb_region_task* regions, int64_t n_regions, std::vector<RawTokens>& raw);
 
 }  // namespace sb

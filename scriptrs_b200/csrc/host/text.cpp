@@ -193,6 +193,8 @@ TranscriptionResult decode_tokens(const Vocabulary& vocab, const RawTokens& raw,
     return res;
 }
 
+std::string trim_whitespace(const std::string& s) { return trim(s); }
+
 TranscriptionResult long_form_result(std::vector<TimedToken> tokens, int64_t audio_len) {
     TranscriptionResult res;
     res.duration_seconds = static_cast<double>(audio_len) / 16000.0;

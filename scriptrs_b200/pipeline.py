@@ -87,7 +87,42 @@ class OverlapChunkConfig:
 
 
 class LongFormMode:
+    """src/long_form.rs:89-98"""
     Fast = 0
+    Vad = 1
+
+
+@dataclass
+class VadConfig:
+    """src/long_form/planner.rs:11-27"""
+    default_threshold: float = 0.85
+
+    def to_c(self):
+        return _lib.VadConfigC(self.default_threshold)
+
+
+@dataclass
+class VadSegmentationConfig:
+    """src/long_form/planner.rs:29-81"""
+    min_speech_duration: float = 0.15
+    min_silence_duration: float = 0.75
+    max_speech_duration: float = 14.0
+    speech_padding: float = 0.1
+    silence_threshold_for_split: float = 0.3
+    negative_threshold: float | None = None
+    negative_threshold_offset: float = 0.15
+    min_silence_at_max_speech: float = 0.098
+    use_max_possible_silence_at_max_speech: bool = True
+
+    def threshold(self, default_threshold: float) -> float:
+        return default_threshold
+
+    def to_c(self):
+        return _lib.VadSegmentationConfigC(
+            self.min_speech_duration, self.min_silence_duration, self.max_speech_duration, self.speech_padding,
+            self.silence_threshold_for_split, 0 if self.negative_threshold is None else 1,
+            0.0 if self.negative_threshold is None else self.negative_threshold, self.negative_threshold_offset,
+            self.min_silence_at_max_speech, 1 if self.use_max_possible_silence_at_max_speech else 0)
 
 
 @dataclass
@@ -96,10 +131,69 @@ class LongFormConfig:
     mode: int = LongFormMode.Fast
     worker_count: int = 4
     transcription: TranscriptionConfig = field(default_factory=TranscriptionConfig)
+    vad: VadConfig = field(default_factory=VadConfig)
+    segmentation: VadSegmentationConfig = field(default_factory=VadSegmentationConfig)
     overlap: OverlapChunkConfig = field(default_factory=OverlapChunkConfig)
 
     def to_c(self):
-        return _lib.LongFormConfigC(self.mode, self.worker_count, self.transcription.to_c(), self.overlap.to_c())
+        return _lib.LongFormConfigC(self.mode, self.worker_count, self.transcription.to_c(), self.vad.to_c(),
+                                    self.segmentation.to_c(), self.overlap.to_c())
+
+
+VAD_WINDOW_SAMPLES = 512  # src/constants.rs:7
+
+
+def vad_num_windows(n_samples: int) -> int:
+    return int(_lib.lib().sb_vad_num_windows(n_samples))
+
+
+def detect_speech_regions(probabilities, audio_len: int, threshold: float = 0.85,
+                          config: VadSegmentationConfig | None = None):
+    """src/long_form/planner.rs:139-233: list of (start, end) sample ranges."""
+    p = np.ascontiguousarray(probabilities, np.float32)
+    sc = (config or VadSegmentationConfig()).to_c()
+    n = C.c_int64()
+    L = _lib.lib()
+    check(L.sb_vad_detect_speech_regions(_ptr(p) if p.size else None, p.size, audio_len, threshold, C.byref(sc), None,
+                                         0, C.byref(n)))
+    arr = (_lib.SampleRangeC * max(n.value, 1))()
+    check(L.sb_vad_detect_speech_regions(_ptr(p) if p.size else None, p.size, audio_len, threshold, C.byref(sc), arr,
+                                         n.value, C.byref(n)))
+    return [(r.start, r.end) for r in arr[: n.value]]
+
+
+def plan_region_subsegments(region, region_probabilities, config: VadSegmentationConfig | None = None,
+                            max_chunk_samples: int = 240_000):
+    """src/long_form/planner.rs:242-284: list of (start, end), or None where no usable silence exists."""
+    p = np.ascontiguousarray(region_probabilities, np.float32)
+    sc = (config or VadSegmentationConfig()).to_c()
+    rg = _lib.SampleRangeC(int(region[0]), int(region[1]))
+    cap = p.size + 2
+    arr = (_lib.SampleRangeC * cap)()
+    n = C.c_int64()
+    check(_lib.lib().sb_vad_plan_region_subsegments(C.byref(rg), _ptr(p) if p.size else None, p.size, C.byref(sc),
+                                                    max_chunk_samples, arr, cap, C.byref(n)))
+    if n.value < 0:
+        return None
+    return [(r.start, r.end) for r in arr[: n.value]]
+
+
+def plan_vad(regions, probabilities, config: LongFormConfig | None = None):
+    """build_execution_plan (src/long_form.rs:421-437,508-548): (tasks, region_tasks); a task is (audio_start,
+    audio_end, global_sample_offset, context_samples), a region task (kind, first_task, n_tasks) with kind 0 =
+    Overlap, 1 = Segments."""
+    p = np.ascontiguousarray(probabilities, np.float32)
+    lc = (config or LongFormConfig()).to_c()
+    rg = (_lib.SampleRangeC * max(len(regions), 1))(*[_lib.SampleRangeC(int(a), int(b)) for a, b in regions])
+    n = C.c_int64()
+    L = _lib.lib()
+    check(L.sb_plan_vad(C.byref(lc), rg, len(regions), _ptr(p) if p.size else None, p.size, None, 0, C.byref(n), None, 0))
+    tasks = (_lib.ChunkTaskC * max(n.value, 1))()
+    rts = (_lib.RegionTaskC * max(len(regions), 1))()
+    check(L.sb_plan_vad(C.byref(lc), rg, len(regions), _ptr(p) if p.size else None, p.size, tasks, n.value, C.byref(n),
+                        rts, len(regions)))
+    return ([(t.audio_start, t.audio_end, t.global_sample_offset, t.context_samples) for t in tasks[: n.value]],
+            [(r.kind, r.first_task, r.n_tasks) for r in rts[: len(regions)]])
 
 
 def plan_fast(audio_len: int, overlap: OverlapChunkConfig | None = None):
@@ -320,6 +414,41 @@ def longform_finish(vocab: Vocabulary, audio_len: int, windows) -> Transcription
     return _take_result(h)
 
 
+def longform_finish_regions(vocab: Vocabulary, audio_len: int, tasks, region_tasks, windows) -> TranscriptionResult:
+    """build_parallel_result (src/long_form.rs:344-374) from per-task token streams in task order."""
+    tok, frm, dur, conf, offs, _ = _concat(windows)
+    ts = (_lib.ChunkTaskC * max(len(tasks), 1))(*[_lib.ChunkTaskC(*map(int, t)) for t in tasks])
+    rs = (_lib.RegionTaskC * max(len(region_tasks), 1))(*[_lib.RegionTaskC(*map(int, r)) for r in region_tasks])
+    h = C.c_void_p()
+    check(_lib.lib().sb_longform_finish_regions(vocab._h, audio_len, ts, len(tasks), rs, len(region_tasks), _ptr(tok),
+                                                _ptr(frm), _ptr(dur), _ptr(conf), _ptr(offs), C.byref(h)))
+    return _take_result(h)
+
+
+class SileroVad:
+    """src/long_form/vad.rs:9-29: per-window speech probabilities of a recording, on the context's GPU."""
+
+    def __init__(self, ctx: Context, weights: dict | None = None, path: str | None = None):
+        self.ctx = ctx
+        L = _lib.lib()
+        if path is not None:
+            check(L.sb_vad_load_file(ctx.handle, path.encode()))
+        else:
+            keep = {k: np.ascontiguousarray(v, np.float32) for k, v in weights.items()}
+            arr = (_lib.TensorC * len(keep))()
+            for i, (k, v) in enumerate(keep.items()):
+                arr[i] = _lib.TensorC(k.encode(), v.ctypes.data, v.size)
+            check(L.sb_vad_load(ctx.handle, arr, len(keep)))
+
+    def process(self, audio, config: VadConfig | None = None) -> np.ndarray:
+        a = _audio(audio)
+        out = np.zeros(vad_num_windows(a.size), np.float32)
+        n = C.c_int64()
+        check(_lib.lib().sb_vad_process(self.ctx.handle, _ptr(a) if a.size else None, a.size,
+                                        _ptr(out) if out.size else None, out.size, C.byref(n)))
+        return out[: n.value]
+
+
 class TranscriptionPipeline:
     """Single-chunk pipeline (src/pipeline.rs:21-99).  Audio: mono 16 kHz float32."""
 
@@ -367,7 +496,8 @@ class TranscriptionPipeline:
 
 
 class LongFormTranscriptionPipeline:
-    """Long-form pipeline with overlap chunking (src/long_form.rs:44-174), Fast mode."""
+    """Long-form pipeline (src/long_form.rs:44-174): overlap chunking (Fast) or VAD-planned regions (Vad; load the
+    network with SileroVad(inner.ctx, ...) first, else MissingModelAsset as in long_form.rs:194-199)."""
 
     def __init__(self, inner: TranscriptionPipeline, extra_contexts=()):
         self.inner = inner
@@ -387,4 +517,16 @@ class LongFormTranscriptionPipeline:
         hs = (C.c_void_p * len(self.contexts))(*[c.handle for c in self.contexts])
         check(_lib.lib().sb_longform_run_multi(hs, len(self.contexts), self.inner.vocab._h,
                                                _ptr(a) if a.size else None, a.size, C.byref(cfg), C.byref(h)))
+        return _take_result(h)
+
+    def run_with_probabilities(self, audio, probabilities, config: LongFormConfig | None = None) -> TranscriptionResult:
+        """run_vad_long_form (src/long_form.rs:188-216) with the caller's per-window speech probabilities."""
+        a = _audio(audio)
+        p = np.ascontiguousarray(probabilities, np.float32)
+        cfg = (config or self.default_config).to_c()
+        h = C.c_void_p()
+        hs = (C.c_void_p * len(self.contexts))(*[c.handle for c in self.contexts])
+        check(_lib.lib().sb_longform_run_with_probabilities(hs, len(self.contexts), self.inner.vocab._h,
+                                                            _ptr(a) if a.size else None, a.size, C.byref(cfg),
+                                                            _ptr(p) if p.size else None, p.size, C.byref(h)))
         return _take_result(h)

@@ -204,3 +204,81 @@ def seeded_model(layers: int, encoder_seed: int = 2, decoder_seed: int = 3) -> d
     w = seeded_encoder_weights(layers, seed=encoder_seed, std=0.02, plain_norms=True)
     w.update(seeded_decoder_weights(decoder_seed, std=0.05))
     return w
+
+
+# ---------------------------------------------------------------------------- voice-activity network
+VAD_SHAPES = {
+    "stft.forward_basis_buffer": (258, 1, 256),
+    "encoder.0.reparam_conv.weight": (128, 129, 3), "encoder.0.reparam_conv.bias": (128,),
+    "encoder.1.reparam_conv.weight": (64, 128, 3), "encoder.1.reparam_conv.bias": (64,),
+    "encoder.2.reparam_conv.weight": (64, 64, 3), "encoder.2.reparam_conv.bias": (64,),
+    "encoder.3.reparam_conv.weight": (128, 64, 3), "encoder.3.reparam_conv.bias": (128,),
+    "decoder.rnn.weight_ih": (512, 128), "decoder.rnn.weight_hh": (512, 128),
+    "decoder.rnn.bias_ih": (512,), "decoder.rnn.bias_hh": (512,),
+    "decoder.decoder.2.weight": (1, 128, 1), "decoder.decoder.2.bias": (1,),
+}
+
+
+def vad_stft_basis() -> np.ndarray:
+    """Hann-windowed DFT rows of length 256: 129 real (cos) rows, then 129 imaginary (-sin) rows."""
+    n = np.arange(256, dtype=np.float64)
+    window = 0.5 - 0.5 * np.cos(2.0 * np.pi * n / 256.0)
+    k = np.arange(129, dtype=np.float64)[:, None]
+    ang = 2.0 * np.pi * k * n[None, :] / 256.0
+    return np.concatenate([np.cos(ang) * window, -np.sin(ang) * window]).astype(np.float32).reshape(258, 1, 256)
+
+
+def seeded_vad_weights(seed: int) -> dict:
+    """Random weights with the shapes of the voice-activity network (the reference's network file is not
+    distributed with it): convolutions N(0, 1.4 / sqrt(fan_in)), recurrent matrices N(0, 0.12), output layer
+    N(0, 0.5); the Fourier basis is the true Hann-windowed DFT."""
+    w = {}
+    for name, shape in VAD_SHAPES.items():
+        if name == "stft.forward_basis_buffer":
+            w[name] = vad_stft_basis()
+        elif name.startswith("encoder.") and name.endswith("weight"):
+            w[name] = normal_tensor("vad." + name, shape, 1.4 / np.sqrt(shape[1] * shape[2]), seed)
+        elif name.startswith("decoder.rnn.weight"):
+            w[name] = normal_tensor("vad." + name, shape, 0.12, seed)
+        elif name == "decoder.decoder.2.weight":
+            w[name] = normal_tensor("vad." + name, shape, 0.5, seed)
+        else:
+            w[name] = normal_tensor("vad." + name, shape, 0.1, seed)
+    return w
+
+
+def energy_vad_weights(gain: float = 20.0, offset: float = 2.0) -> dict:
+    """Weights that turn the network into an energy detector, so that end-to-end runs of the VAD mode see
+    probabilities near 1 on sound and near 0 on silence: channel 0 of every layer carries the mean spectral
+    magnitude E of the window, the LSTM cell has input and output gates open and the forget gate shut, the cell
+    candidate is tanh(gain * E - offset), and the output layer is sigmoid(20 * relu(h_0) - 4)."""
+    w = {name: np.zeros(shape, np.float32) for name, shape in VAD_SHAPES.items()}
+    w["stft.forward_basis_buffer"] = vad_stft_basis()
+    w["encoder.0.reparam_conv.weight"][0, :, 1] = 1.0 / 129.0
+    w["encoder.1.reparam_conv.weight"][0, 0, :] = 1.0 / 3.0
+    w["encoder.2.reparam_conv.weight"][0, 0, 1:] = 0.5
+    w["encoder.3.reparam_conv.weight"][0, 0, 1] = 1.0
+    b = w["decoder.rnn.bias_ih"]
+    b[0:128] = 10.0      # input gate open
+    b[128:256] = -10.0   # forget gate shut
+    b[256:384] = -offset
+    b[384:512] = 10.0    # output gate open
+    w["decoder.rnn.weight_ih"][256:384, 0] = gain
+    w["decoder.decoder.2.weight"][0, 0, 0] = 20.0
+    w["decoder.decoder.2.bias"][0] = -4.0
+    return w
+
+
+def sparse_speech_audio(n_samples: int, seed: int, speech_seconds=(2.0, 20.0), silence_seconds=(1.0, 6.0)) -> np.ndarray:
+    """A recording for the VAD mode: stretches of `long_audio`-like sound (durations U(speech_seconds)) separated by
+    near-silence (N(0, 1e-4) noise, durations U(silence_seconds))."""
+    rng = np.random.default_rng(seed)
+    out = rng.normal(0.0, 1e-4, n_samples).astype(np.float32)
+    pos = int(rng.uniform(*silence_seconds) * SAMPLE_RATE)
+    k = 0
+    while pos < n_samples:
+        n = min(int(rng.uniform(*speech_seconds) * SAMPLE_RATE), n_samples - pos)
+        out[pos:pos + n] += clip_audio(n, seed * 1000 + k)
+        pos += n + int(rng.uniform(*silence_seconds) * SAMPLE_RATE)
+        k += 1
+    return out
