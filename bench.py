@@ -359,6 +359,106 @@ def cpu_longform_baseline(threads: int, n_chunks: int, layers: int):
                       f"merge and text; chunks processed one after another"}
 
 
+def cpu_vad_baseline(seconds: float = 120.0):
+    """The numpy port of the voice-activity network (oracle) on a bounded sample, one thread's worth of BLAS calls
+    per window as the recurrence dictates."""
+    from oracle import vad_oracle as vo
+    from scriptrs_b200 import synth
+
+    n = int(seconds * 16000)
+    audio = synth.long_audio(n, 77)
+    w = synth.seeded_vad_weights(5)
+    t0 = time.perf_counter()
+    p = vo.vad_probabilities(w, audio)
+    dt = time.perf_counter() - t0
+    return {"value": (n / 16000) / dt, "unit": "audio-sec/sec", "cores": 1, "kind": "port",
+            "sample": f"{p.size} windows ({seconds:g} s of audio) in {dt:.2f} s: numpy float32 port of the network"}
+
+
+def measure_vad(ctx, sb, torch, stream, device, d_audio, h_audio, n, vocab, lf_steps: int):
+    """The VAD long-form mode (the reference's second planning mode): (1) the voice-activity network alone over the
+    resident recording, with per-kernel times; (2) the whole mode end to end from pinned host memory on a copy of
+    the recording with seeded silences, with a network set up as an energy detector so that the regions are real."""
+    from scriptrs_b200 import synth
+
+    sb.SileroVad(ctx, synth.seeded_vad_weights(5))
+    n_win = sb.vad_num_windows(n)
+    d_prob = torch.empty(n_win, dtype=torch.float32, device=device)
+    L = sb.lib()
+
+    def net():
+        sb.check(L.sb_vad_process_device(ctx.handle, d_audio.data_ptr(), n, d_prob.data_ptr()))
+
+    for _ in range(3):
+        net()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream.synchronize()
+    a.record(stream)
+    for _ in range(5):
+        net()
+    b.record(stream)
+    stream.synchronize()
+    net_ms = a.elapsed_time(b) / 5
+    ctx.set_profiling(True)
+    net()
+    kern = {k: round(v[0], 3) for k, v in ctx.profile_report().items()}
+    ctx.set_profiling(False)
+    out = {"network": {"ms": net_ms, "windows": n_win, "us_per_window": net_ms * 1e3 / n_win,
+                       "audio_sec_per_sec": (n / 16000) / (net_ms * 1e-3), "kernel_ms": kern,
+                       "encode_tflops_fp32": 2 * 0.6e6 * n_win / (kern.get("vad_encode", float("nan")) * 1e-3) / 1e12,
+                       "weights": "seeded (the network file is not distributed with the reference)",
+                       "note": "inputs resident; the recurrence is one 8-CTA cluster, latency-bound by design"}}
+    # (2) seeded silences: stretches of 1-6 s between sounds of 2-20 s
+    rng = np.random.default_rng(4321)
+    keep = np.ones(n_win, bool)
+    w = int(rng.uniform(1, 6) * 31.25)
+    keep[:w] = False
+    while w < n_win:
+        w += int(rng.uniform(2, 20) * 31.25)
+        g = int(rng.uniform(1, 6) * 31.25)
+        keep[w:w + g] = False
+        w += g
+    mask = torch.from_numpy(np.repeat(keep, 512)[:n]).to(device)
+    sparse = torch.where(mask, d_audio, torch.zeros((), device=device))
+    h_sparse = torch.empty(n, dtype=torch.float32, pin_memory=True)
+    h_sparse.copy_(sparse)
+    del sparse, mask
+    torch.cuda.synchronize()
+    energy = sb.SileroVad(ctx, synth.energy_vad_weights())
+    pipe = sb.TranscriptionPipeline(ctx, vocab)
+    lf = sb.LongFormTranscriptionPipeline(pipe)
+    cfg = sb.LongFormConfig(mode=sb.LongFormMode.Vad)
+    arr = h_sparse.numpy()
+    res = lf.run_with_config(arr, cfg)
+    t0 = time.perf_counter()
+    for _ in range(lf_steps):
+        res = lf.run_with_config(arr, cfg)
+    ms = (time.perf_counter() - t0) * 1e3 / lf_steps
+    ctx.set_profiling(True)   # per-kernel times of one more run (CUDA events around every launch, both streams)
+    lf.run_with_config(arr, cfg)
+    prof = ctx.profile_report()
+    ctx.set_profiling(False)
+    vad_k = {k: round(v[0], 3) for k, v in prof.items() if k.startswith("vad_")}
+    other_k = {k: [round(v[0], 3), v[1]] for k, v in prof.items() if not k.startswith("vad_")}
+    other_ms = sum(v[0] for k, v in prof.items() if not k.startswith("vad_"))
+    probs = energy.process(arr)
+    regions = sb.detect_speech_regions(probs, n)
+    tasks, rts = sb.plan_vad(regions, probs)
+    t0 = time.perf_counter()
+    fast = lf.run_with_config(arr, sb.LongFormConfig())
+    fast_ms = (time.perf_counter() - t0) * 1e3
+    out["mode_e2e"] = {"value": (n / 16000) / (ms * 1e-3), "unit": "audio-sec/sec", "ms_per_step": ms, "steps": lf_steps,
+                       "host_memory": "pinned", "sound_fraction": float(keep.mean()), "regions": len(regions),
+                       "tasks": len(tasks), "segment_regions": sum(1 for k, _, _ in rts if k == 1),
+                       "overlap_regions": sum(1 for k, _, _ in rts if k == 0),
+                       "task_audio_sec": sum(t[1] - t[0] for t in tasks) / 16000.0, "chunks": len(res.chunks),
+                       "tokens": len(res.token_ids), "network_kernel_ms_beside_transcription": vad_k,
+                       "transcription_kernel_ms": round(other_ms, 3), "transcription_kernels_ms_launches": other_k, "fast_mode_same_recording_ms": fast_ms,
+                       "fast_mode_tokens": len(fast.token_ids),
+                       "network": "energy detector in the network's shape (seeded silences, zeros)"}
+    return out
+
+
 def run_longform(args, rank, world, local):
     import torch
 
@@ -548,6 +648,11 @@ def run_longform(args, rank, world, local):
         p_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, world, device)
         pageable = {"value": audio_s / (p_ms * 1e-3), "unit": "audio-sec/sec", "ms_per_step": p_ms, "steps": 1}
         del p_audio
+    vad_mode = None
+    if world == 1 and not args.no_vad_line:
+        vad_mode = measure_vad(ctx, sb, torch, stream, device, d_audio, h_audio, n, vocab, max(1, min(args.steps, 2)))
+        if not args.skip_cpu_baseline:
+            vad_mode["network"]["cpu_baseline"] = cpu_vad_baseline()
     # config 1 (the other half of the metric): batched log-mel frontend, 1024 clips x 30 s, inputs resident
     frontend = None
     if not args.no_frontend_line:
@@ -591,6 +696,7 @@ def run_longform(args, rank, world, local):
         "fp8_variant": variant,
         "fp8_gemms": fp8_report,
         "frontend": frontend,
+        "vad_mode": vad_mode,
         "stage_ms_rank0": stage_ms,
         "kernel_ms_rank0": kernel_ms,
         "clocks": clocks,
@@ -786,6 +892,7 @@ def main():
     ap.add_argument("--stage-breakdown", action="store_true", help="longform: also time the three stage entry points")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="profiling runs: leave the CPU leg out")
     ap.add_argument("--no-fp8-variant", action="store_true", help="longform: do not also time the FP8 variant")
+    ap.add_argument("--no-vad-line", action="store_true", help="longform: do not also time the VAD planning mode")
     ap.add_argument("--no-frontend-line", action="store_true", help="longform: do not also time config 1 (frontend)")
     ap.add_argument("--skip-pageable", action="store_true", help="longform: leave out the pageable-memory e2e step")
     args = ap.parse_args()

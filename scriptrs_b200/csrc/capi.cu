@@ -273,6 +273,9 @@ void sb_ctx_destroy(sb_ctx* c) {
     if (c->d_error) cudaFree(c->d_error);
     c->prof.release();
     for (cudaEvent_t e : c->copy_events) cudaEventDestroy(e);
+    for (cudaEvent_t e : c->vad_events) cudaEventDestroy(e);
+    if (c->vad_stream) cudaStreamDestroy(c->vad_stream);
+    if (c->vad_feed_stream) cudaStreamDestroy(c->vad_feed_stream);
     if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     if (c->own_stream) cudaStreamDestroy(c->own_stream);
     delete c;
@@ -309,6 +312,8 @@ int32_t sb_ctx_set_option(sb_ctx* c, const char* name, int64_t value) {
         if (value < 1 || value > (1 << 22)) return fail(SB_INVALID_ARGUMENT, "vad_segment_windows must be in [1, 4194304]");
         c->vad_segment_windows = (int)value;
     }
+    else if (n == "vad_unstreamed") c->vad_unstreamed = value != 0;
+    else if (n == "vad_rows_cap") c->vad_rows_cap = value < 0 ? 0 : value;
     else if (n == "vad_row_threads") {
         if (value != 2 && value != 4) return fail(SB_INVALID_ARGUMENT, "vad_row_threads must be 2 or 4");
         c->vad_row_threads = (int)value;

@@ -14,6 +14,7 @@
 #include "host/longform.h"
 #include "model.h"
 #include "pipeline.h"
+#include "vad.h"
 
 struct sb_vocab { sb::Vocabulary v; };
 struct sb_result { sb::TranscriptionResult r; };
@@ -153,6 +154,99 @@ int32_t transcribe_tasks(sb_ctx* c, const void* pcm_any, int64_t n_samples, cons
     }
     return SB_OK;
 }
+
+// Tasks that arrive in pieces over one recording that is resident on the GPU: every piece goes through the
+// frontend and the encoder as it arrives (asynchronously on the context's stream), the decoder runs once over all
+// pieces' encoder frames at the end.  transcribe_tasks for a plan that is still growing.
+struct PieceRun {
+    sb_ctx* c;
+    const float* d_pcm;  // the whole recording, device memory
+    int64_t n_samples;
+    sb_transcription_config cfg;
+    std::vector<sb_chunk_task> tasks;  // all tasks so far
+    std::vector<RawTokens> raws;       // decoded tasks, in task order (a prefix of `tasks`)
+    std::vector<int64_t> eo{0};        // encoder frame offsets of the tasks that wait for the decoder
+    int64_t max_enc = 0, cap_rows = 0;
+
+    int32_t begin(int64_t rows_hint) {
+        cap_rows = rows_hint;
+        SB_CUDA(cudaSetDevice(c->device));
+        SB_CUDA(c->enc_stage.ensure(sizeof(float) * kDModel * (size_t)cap_rows));
+        return SB_OK;
+    }
+
+    int32_t decode_pending() {
+        const int64_t n = (int64_t)eo.size() - 1;
+        if (n == 0) return SB_OK;
+        const int64_t first = (int64_t)raws.size();
+        const int64_t max_tokens = std::max<int64_t>(1, kMaxSymbols * max_enc);
+        std::vector<uint32_t> tok((size_t)n * max_tokens);
+        std::vector<int64_t> frm((size_t)n * max_tokens), dur((size_t)n * max_tokens), cnt(n);
+        std::vector<float> conf((size_t)n * max_tokens);
+        int32_t s = tdt_decode(c, c->enc_stage.as<float>(), eo.data(), n, max_tokens, tok.data(), frm.data(), dur.data(),
+                               conf.data(), cnt.data(), nullptr, 0, nullptr);
+        if (s != SB_OK) return s;
+        for (int64_t i = 0; i < n; ++i) {
+            const int64_t o = i * max_tokens;
+            raws.push_back(raw_from_arrays(tok.data(), frm.data(), dur.data(), conf.data(), o, o + cnt[i]));
+            const sb_chunk_task& t = tasks[(size_t)(first + i)];
+            apply_time_offsets(raws.back(), t.global_sample_offset / cfg.samples_per_encoder_frame,
+                               t.context_samples / cfg.samples_per_encoder_frame);  // pipeline.rs:132-136
+        }
+        eo.assign(1, 0);
+        max_enc = 0;
+        return SB_OK;
+    }
+
+    int32_t add(const sb_chunk_task* t, int64_t n) {
+        if (n == 0) return SB_OK;
+        if (!c->model || !c->model->has_encoder || !c->model->has_decoder)
+            return fail(SB_MISSING_MODEL_ASSET, "encoder and decoder weights must be loaded first");
+        std::vector<int64_t> start(n), len(n), rel(n + 1);
+        int64_t frames = 0, rows = 0;
+        for (int64_t i = 0; i < n; ++i) {
+            if (t[i].audio_start < 0 || t[i].audio_end > n_samples || t[i].audio_end < t[i].audio_start)
+                return fail(SB_INVALID_ARGUMENT, "task range outside the audio");
+            start[i] = t[i].audio_start;
+            len[i] = t[i].audio_end - t[i].audio_start;
+            if (len[i] == 0) return fail(SB_EMPTY_AUDIO, "audio input was empty");  // pipeline.rs:202
+            if (len[i] > cfg.max_audio_samples) {                                    // pipeline.rs:205-210
+                char msg[160];
+                std::snprintf(msg, sizeof msg, "audio exceeds the single-chunk limit: actual=%.2fs max=%.2fs",
+                              (double)len[i] / (double)cfg.sample_rate, (double)cfg.max_audio_samples / (double)cfg.sample_rate);
+                return fail(SB_AUDIO_TOO_LONG, msg);
+            }
+            const int64_t f = frames_for_samples(len[i]);
+            frames += f;
+            const int64_t e = encoder_out_frames((int)f);
+            rows += e;
+            max_enc = std::max(max_enc, e);
+        }
+        if (n > 65535) return fail(SB_INVALID_ARGUMENT, "more than 65535 tasks in one piece");
+        SB_CUDA(cudaSetDevice(c->device));
+        if (eo.back() + rows > cap_rows) {  // the encoder frames kept for the decoder are full: decode what is there
+            int32_t s = decode_pending();
+            if (s != SB_OK) return s;
+            for (int64_t i = 0; i < n; ++i) max_enc = std::max<int64_t>(max_enc, encoder_out_frames((int)frames_for_samples(len[i])));
+            if (rows > cap_rows) {
+                cap_rows = rows;
+                SB_CUDA(c->enc_stage.ensure(sizeof(float) * kDModel * (size_t)cap_rows));
+            }
+        }
+        SB_CUDA(c->feat_stage.ensure(sizeof(float) * kMels * (size_t)frames));
+        int32_t s = frontend_run(c, d_pcm, kSampleF32, start.data(), len.data(), n, cfg.preemphasis, true,
+                                 c->feat_stage.as<float>(), rel.data());
+        if (s != SB_OK) return s;
+        std::vector<int> eoi(n + 1);
+        SB_CUDA(encoder_forward(c, *c->model, c->feat_stage.as<float>(), rel.data(), (int)n,
+                                c->enc_stage.as<float>() + (size_t)eo.back() * kDModel, eoi.data(), *c->enc_ws,
+                                c->workspace_budget));
+        const int64_t base = eo.back();
+        for (int64_t k = 1; k <= n; ++k) eo.push_back(base + eoi[k]);
+        tasks.insert(tasks.end(), t, t + n);
+        return SB_OK;
+    }
+};
 
 int32_t check_config(const sb_transcription_config& t) {
     if (t.sample_rate != 16000 || t.feature_size != 128 || t.n_fft != 512 || t.win_length != 400 ||
@@ -524,8 +618,11 @@ namespace {
 
 // execute_plan (src/long_form.rs:232-245): the tasks go to min(worker_count, n_ctx, tasks) GPU shards in
 // contiguous blocks (run_parallel_regions, long_form.rs:266-314); build_parallel_result joins them.
+// d_audio0, if not null, is the recording in the memory of ctxs[0]'s GPU (the VAD network left it there): the
+// first shard then reads it in place instead of copying its part from the host again.
 int32_t execute_plan(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio, int64_t n_samples,
-                     const sb_longform_config& lc, const ExecutionPlan& plan, sb_result** out) {
+                     const sb_longform_config& lc, const ExecutionPlan& plan, sb_result** out,
+                     const float* d_audio0 = nullptr) {
     sb_result* res = new sb_result();
     const int64_t n_tasks = (int64_t)plan.tasks.size();
     if (n_tasks == 0) {  // TranscriptionResult::empty
@@ -539,7 +636,9 @@ int32_t execute_plan(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const 
     std::vector<std::string> errors((size_t)shards);
     auto work = [&](int64_t k) {
         const int64_t a = n_tasks * k / shards, b = n_tasks * (k + 1) / shards;
-        status[k] = transcribe_tasks(ctxs[k], audio, n_samples, plan.tasks.data() + a, b - a, lc.transcription, &parts[k]);
+        const bool resident = k == 0 && d_audio0;
+        status[k] = transcribe_tasks(ctxs[k], resident ? d_audio0 : audio, n_samples, plan.tasks.data() + a, b - a,
+                                     lc.transcription, &parts[k], resident);
         if (status[k] != SB_OK) errors[k] = sb_last_error();
     };
     if (shards == 1) {
@@ -564,11 +663,129 @@ int32_t execute_plan(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const 
 }
 
 int32_t run_vad_plan(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio, int64_t n_samples,
-                     const sb_longform_config& lc, const float* prob, int64_t n_prob, sb_result** out) {
+                     const sb_longform_config& lc, const float* prob, int64_t n_prob, sb_result** out,
+                     const float* d_audio0 = nullptr) {
     // long_form.rs:200-216; VadSegmentationConfig::threshold returns the VadConfig's value (planner.rs:71-73)
     const std::vector<sb_sample_range> regions =
         detect_speech_regions(prob, n_prob, n_samples, lc.vad.default_threshold, lc.segmentation);
-    return execute_plan(ctxs, n_ctx, vocab, audio, n_samples, lc, build_vad_plan(regions, prob, n_prob, lc), out);
+    return execute_plan(ctxs, n_ctx, vocab, audio, n_samples, lc, build_vad_plan(regions, prob, n_prob, lc), out, d_audio0);
+}
+
+// The VAD mode on one GPU with the voice-activity network and the transcription overlapped.  The recording goes
+// to the GPU in passes on a second, high-priority stream: copy, network, probabilities back to the host.  The
+// recurrence of the network occupies one 8-CTA cluster for as long as the rest of the GPU needs to transcribe a
+// comparable stretch of audio, so the host plans the regions that pass k made final (SpeechRegionStream) and
+// sends their tasks through the frontend and the encoder on the context's stream while pass k + 1 runs beside
+// them.  Passes start short (the first one is exposed) and double up to "vad_segment_windows".  The decoder runs
+// once at the end.  Regions, tasks and results equal those of the unstreamed path.
+int32_t run_vad_streamed(sb_ctx* c, const sb_vocab* vocab, const float* audio, int64_t n_samples,
+                         const sb_longform_config& lc, sb_result** out) {
+    VadModel& m = *c->vad;
+    SB_CUDA(cudaSetDevice(c->device));
+    const int64_t n_win = sb_vad_num_windows(n_samples);
+    std::vector<int64_t> cut{0};  // pass boundaries, in windows
+    for (int64_t w = 8192; cut.back() < n_win; w = std::min<int64_t>(2 * w, c->vad_segment_windows))
+        cut.push_back(std::min(n_win, cut.back() + std::min<int64_t>(w, c->vad_segment_windows)));
+    const int n_pass = (int)cut.size() - 1;
+    int64_t max_pass = 0;
+    for (int k = 0; k < n_pass; ++k) max_pass = std::max(max_pass, cut[k + 1] - cut[k]);
+    SB_CUDA(m.audio.ensure(sizeof(float) * (size_t)n_samples));
+    SB_CUDA(m.prob.ensure(sizeof(float) * (size_t)n_win));
+    m.host_prob.pinned_host = true;
+    SB_CUDA(m.host_prob.ensure(sizeof(float) * (size_t)n_win));
+    if (!c->vad_stream) {
+        int least = 0, greatest = 0;
+        SB_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+        SB_CUDA(cudaStreamCreateWithPriority(&c->vad_stream, cudaStreamNonBlocking, greatest));
+        SB_CUDA(cudaStreamCreateWithPriority(&c->vad_feed_stream, cudaStreamNonBlocking, greatest));
+    }
+    // events per pass: probabilities on the host | gate inputs ready | recurrence done; plus one that orders the passes
+    // after earlier work
+    while ((int)c->vad_events.size() < 3 * n_pass + 1) {
+        cudaEvent_t ev;
+        SB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        c->vad_events.push_back(ev);
+    }
+    PieceRun run{c, m.audio.as<float>(), n_samples, lc.transcription};
+    // room for the encoder frames of the whole recording windowed with overlap, plus a margin for short regions
+    int32_t s = run.begin(c->vad_rows_cap > 0 ? c->vad_rows_cap : (int64_t)(1.2 * (double)n_samples / 1280.0) + 16384);
+    if (s != SB_OK) return s;
+    // Two streams feed the network: `fs` copies a pass's samples in and computes its gate inputs, `vs` runs the
+    // recurrences one after another; the gate inputs alternate between two buffers, so pass k + 1 is prepared while
+    // pass k recurs.
+    cudaStream_t vs = c->vad_stream, fs = c->vad_feed_stream;
+    cudaEvent_t* ev_host = c->vad_events.data();           // [k]: pass k's probabilities are in host memory
+    cudaEvent_t* ev_fed = c->vad_events.data() + n_pass;   // [k]: pass k's gate inputs are ready
+    cudaEvent_t* ev_rec = c->vad_events.data() + 2 * n_pass;  // [k]: pass k's recurrence has ended
+    cudaEvent_t ev_prior = c->vad_events[3 * n_pass];
+    // work of an earlier call on the context's stream may still read the buffers that the passes overwrite
+    SB_CUDA(cudaEventRecord(ev_prior, c->stream));
+    SB_CUDA(cudaStreamWaitEvent(vs, ev_prior, 0));
+    s = vad_begin(c, max_pass, vs, true);
+    if (s != SB_OK) return s;
+    SB_CUDA(cudaEventRecord(ev_prior, vs));
+    SB_CUDA(cudaStreamWaitEvent(fs, ev_prior, 0));
+    float* h_prob = m.host_prob.as<float>();
+    auto enqueue = [&](int k) -> int32_t {
+        const int64_t a = cut[k] * kVadWindow, b = std::min(n_samples, cut[k + 1] * kVadWindow);
+        const int n = (int)(cut[k + 1] - cut[k]);
+        if (k >= 2) SB_CUDA(cudaStreamWaitEvent(fs, ev_rec[k - 2], 0));  // the buffer's last reader
+        SB_CUDA(cudaMemcpyAsync(m.audio.as<float>() + a, audio + a, sizeof(float) * (size_t)(b - a), cudaMemcpyHostToDevice, fs));
+        int32_t r = vad_encode_pass(c, fs, m.audio.as<float>(), n_samples, cut[k], n, k & 1);
+        if (r != SB_OK) return r;
+        SB_CUDA(cudaEventRecord(ev_fed[k], fs));
+        SB_CUDA(cudaStreamWaitEvent(vs, ev_fed[k], 0));
+        r = vad_recur_pass(c, vs, cut[k], n, k & 1, m.prob.as<float>());
+        if (r != SB_OK) return r;
+        SB_CUDA(cudaEventRecord(ev_rec[k], vs));
+        SB_CUDA(cudaMemcpyAsync(h_prob + cut[k], m.prob.as<float>() + cut[k], sizeof(float) * (size_t)n, cudaMemcpyDeviceToHost, vs));
+        SB_CUDA(cudaEventRecord(ev_host[k], vs));
+        return SB_OK;
+    };
+    // The recurrence kernel holds one SM per CTA of its cluster for the length of a pass, and the GEMM and attention
+    // kernels (one CTA per SM, each with a fixed share of the tiles, nearly all of the SM's shared memory) cannot sit
+    // beside it: launched over all SMs, the CTAs that find their SM taken would run as a second wave.  So while passes
+    // are in flight those kernels are sized for the SMs that are left.
+    const int all_sms = c->sm_count;
+    c->sm_count = std::max(8, all_sms - c->vad_cluster);
+    auto bail = [&](int32_t code) {
+        const std::string msg = sb_last_error();
+        cudaStreamSynchronize(fs);
+        cudaStreamSynchronize(vs);
+        cudaStreamSynchronize(c->stream);
+        c->sm_count = all_sms;
+        return fail((sb_status)code, msg);
+    };
+    s = enqueue(0);
+    if (s != SB_OK) return bail(s);
+    SpeechRegionStream regions(n_samples, lc.vad.default_threshold, lc.segmentation);
+    ExecutionPlan plan;
+    size_t planned = 0;
+    for (int k = 0; k < n_pass; ++k) {
+        if (k + 1 < n_pass && (s = enqueue(k + 1)) != SB_OK) return bail(s);
+        cudaError_t e = cudaEventSynchronize(ev_host[k]);
+        if (e != cudaSuccess) return bail(cuda_fail(e, "cudaEventSynchronize(vad pass)"));
+        regions.push(h_prob + cut[k], cut[k + 1] - cut[k]);
+        if (k + 1 == n_pass) regions.finish();
+        const size_t first_task = plan.tasks.size();
+        for (; planned < regions.regions().size(); ++planned)
+            append_region_plan(&plan, regions.regions()[planned], h_prob, cut[k + 1], lc);
+        if ((s = run.add(plan.tasks.data() + first_task, (int64_t)(plan.tasks.size() - first_task))) != SB_OK) return bail(s);
+    }
+    c->sm_count = all_sms;  // every pass has ended
+    sb_result* res = new sb_result();
+    if (plan.tasks.empty()) {  // TranscriptionResult::empty (long_form.rs:206-208)
+        res->r.duration_seconds = (double)n_samples / 16000.0;
+        *out = res;
+        return SB_OK;
+    }
+    if ((s = run.decode_pending()) != SB_OK) {
+        delete res;
+        return bail(s);
+    }
+    res->r = build_plan_result(vocab->v, n_samples, plan.tasks.data(), plan.regions.data(), (int64_t)plan.regions.size(), run.raws);
+    *out = res;
+    return SB_OK;
 }
 
 }  // namespace
@@ -602,11 +819,14 @@ int32_t sb_longform_run_multi(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* voca
     if (lc.mode == 0) return execute_plan(ctxs, n_ctx, vocab, audio, n_samples, lc, build_fast_plan(n_samples, lc), out);
     // long_form.rs:193-200: the VAD network is needed only when the mode asks for it
     if (!ctxs[0]->vad) return fail(SB_MISSING_MODEL_ASSET, "missing model asset: vad/silero-vad (load it with sb_vad_load)");
+    // one GPU: the network and the transcription overlap; several: the network first, then the tasks in shards
+    if (std::min<int64_t>(lc.worker_count, n_ctx) <= 1 && !ctxs[0]->vad_unstreamed)
+        return run_vad_streamed(ctxs[0], vocab, audio, n_samples, lc, out);
     std::vector<float> prob((size_t)sb_vad_num_windows(n_samples));
     int64_t n_prob = 0;
     s = sb_vad_process(ctxs[0], audio, n_samples, prob.data(), (int64_t)prob.size(), &n_prob);
     if (s != SB_OK) return s;
-    return run_vad_plan(ctxs, n_ctx, vocab, audio, n_samples, lc, prob.data(), n_prob, out);
+    return run_vad_plan(ctxs, n_ctx, vocab, audio, n_samples, lc, prob.data(), n_prob, out, vad_resident_audio(ctxs[0]));
 }
 
 int32_t sb_longform_run(sb_ctx* c, const sb_vocab* vocab, const float* audio, int64_t n_samples,

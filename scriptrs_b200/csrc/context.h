@@ -70,6 +70,11 @@ struct sb_ctx {
     sb::Model* model = nullptr;
     sb::VadModel* vad = nullptr;  // voice-activity network of the VAD long-form mode
     int vad_cluster = 8;          // CTAs in the cluster that runs the VAD recurrence (4 or 8)
+    cudaStream_t vad_stream = nullptr;       // high priority: the VAD network's recurrences beside the transcription
+    cudaStream_t vad_feed_stream = nullptr;  // sample copies and gate inputs of the pass after the one that recurs
+    std::vector<cudaEvent_t> vad_events;    // three per pass, plus one that orders the passes after earlier work
+    int64_t vad_rows_cap = 0;              // streamed VAD mode: encoder frames kept for one decoder run (0 = sized from the recording)
+    bool vad_unstreamed = false;           // VAD mode: run the whole network before the first transcription kernel (tests)
     int vad_row_threads = 2;      // threads that share one row of the recurrent matrix (2 or 4)
     int vad_segment_windows = 131072;  // windows per pass of the VAD network (268 MB of gate inputs)
     sb::Profiler prof;

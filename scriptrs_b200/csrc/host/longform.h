@@ -42,6 +42,26 @@ constexpr int64_t kVadStateSize = 128;       // constants.rs:11
 // planner.rs:139-233
 std::vector<sb_sample_range> detect_speech_regions(const float* prob, int64_t n_prob, int64_t audio_len, float threshold,
                                                    const sb_vad_segmentation_config& cfg);
+// The same computation fed window by window.  regions() grows as regions become final: a region's end depends on
+// where the next kept speech span starts (the gap between them is shared out as padding), so a region is final when
+// the span after it has closed, and the last one when finish() is called.
+class SpeechRegionStream {
+  public:
+    SpeechRegionStream(int64_t audio_len, float threshold, const sb_vad_segmentation_config& cfg);
+    void push(const float* prob, int64_t n);
+    void finish();
+    const std::vector<sb_sample_range>& regions() const { return regions_; }
+    int64_t windows_seen() const { return window_; }
+
+  private:
+    void on_speech(sb_sample_range s);
+    int64_t audio_len_, min_speech_, min_silence_, pad_;
+    float threshold_, negative_;
+    bool triggered_ = false, silence_open_ = false, has_pending_ = false;
+    int64_t speech_start_ = 0, silence_start_ = 0, window_ = 0;
+    sb_sample_range pending_{0, 0};
+    std::vector<sb_sample_range> regions_;
+};
 // planner.rs:242-284; returns false where the reference returns None
 bool plan_region_subsegments(sb_sample_range region, const float* region_prob, int64_t n_prob,
                              const sb_vad_segmentation_config& cfg, int64_t max_chunk_samples,
@@ -51,6 +71,8 @@ struct ExecutionPlan {
     std::vector<sb_chunk_task> tasks;
     std::vector<sb_region_task> regions;
 };
+void append_region_plan(ExecutionPlan* plan, sb_sample_range region, const float* prob, int64_t n_prob,
+                        const sb_longform_config& cfg);  // build_region_plan, long_form.rs:508-548
 ExecutionPlan build_vad_plan(const std::vector<sb_sample_range>& regions, const float* prob, int64_t n_prob,
                              const sb_longform_config& cfg);
 ExecutionPlan build_fast_plan(int64_t audio_len, const sb_longform_config& cfg);  // long_form.rs:439-459

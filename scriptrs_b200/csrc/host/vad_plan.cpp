@@ -2,6 +2,8 @@
 // long regions, and the execution plan of region tasks.  Logic of the reference, restated for the host driver:
 //   VadSegmentationConfig::effective_negative_threshold          src/long_form/planner.rs:75-80
 //   detect_speech_regions                                        src/long_form/planner.rs:139-233
+//     (as a stream: windows go in as the network produces them, a region comes out as soon as nothing later can
+//      change it, which is when the speech span after it has closed)
 //   region_probability_slice                                     src/long_form/planner.rs:235-240
 //   plan_region_subsegments / silence_spans                      src/long_form/planner.rs:242-315
 //   build_execution_plan / build_region_plan / push_*_task       src/long_form.rs:421-459,508-582
@@ -76,52 +78,69 @@ std::vector<sb_sample_range> overlap_plan(sb_sample_range range, const sb_overla
 }
 }  // namespace
 
-std::vector<sb_sample_range> detect_speech_regions(const float* prob, int64_t n_prob, int64_t audio_len, float threshold,
-                                                   const sb_vad_segmentation_config& cfg) {
-    std::vector<sb_sample_range> speech;
-    if (n_prob <= 0 || audio_len <= 0) return speech;
-    const int64_t min_speech = seconds_to_samples(cfg.min_speech_duration);
-    const int64_t min_silence = seconds_to_samples(cfg.min_silence_duration);
-    const int64_t pad = seconds_to_samples(cfg.speech_padding);
-    const float neg = negative_threshold(cfg, threshold);
+SpeechRegionStream::SpeechRegionStream(int64_t audio_len, float threshold, const sb_vad_segmentation_config& cfg)
+    : audio_len_(audio_len),
+      min_speech_(seconds_to_samples(cfg.min_speech_duration)),
+      min_silence_(seconds_to_samples(cfg.min_silence_duration)),
+      pad_(seconds_to_samples(cfg.speech_padding)),
+      threshold_(threshold),
+      negative_(negative_threshold(cfg, threshold)) {}
 
-    bool triggered = false, silence_open = false;
-    int64_t speech_start = 0, silence_start = 0;
-    for (int64_t w = 0; w < n_prob; ++w) {
-        const int64_t at = w * kVadWindowSamples;
-        const float p = prob[w];
-        if (p >= threshold) {
-            silence_open = false;
-            if (!triggered) { triggered = true; speech_start = at; }
+// A raw speech span has closed.  Its start is final once the gap to the span before it is shared out; its end once
+// the span after it is known: so the span before it leaves now, and this one waits.
+void SpeechRegionStream::on_speech(sb_sample_range s) {
+    if (!has_pending_) {
+        s.start = sat_sub(s.start, pad_);  // first region: padding towards the start of the recording
+        pending_ = s;
+        has_pending_ = true;
+        return;
+    }
+    const int64_t gap = sat_sub(s.start, pending_.end);
+    const int64_t grow = gap < 2 * pad_ ? gap / 2 : pad_;
+    pending_.end = std::min(pending_.end + grow, audio_len_);
+    s.start = sat_sub(s.start, grow);
+    if (pending_.end > pending_.start) regions_.push_back(pending_);
+    pending_ = s;
+}
+
+void SpeechRegionStream::push(const float* prob, int64_t n) {
+    if (audio_len_ <= 0) return;
+    for (int64_t i = 0; i < n; ++i, ++window_) {
+        const int64_t at = window_ * kVadWindowSamples;
+        const float p = prob[i];
+        if (p >= threshold_) {
+            silence_open_ = false;
+            if (!triggered_) { triggered_ = true; speech_start_ = at; }
             continue;
         }
-        if (p < neg && triggered) {
-            if (!silence_open) { silence_open = true; silence_start = at; }
-            if (sat_sub(at, silence_start) >= min_silence) {
-                if (sat_sub(silence_start, speech_start) >= min_speech) speech.push_back({speech_start, silence_start});
-                triggered = false;
-                silence_open = false;
+        if (p < negative_ && triggered_) {
+            if (!silence_open_) { silence_open_ = true; silence_start_ = at; }
+            if (sat_sub(at, silence_start_) >= min_silence_) {
+                if (sat_sub(silence_start_, speech_start_) >= min_speech_) on_speech({speech_start_, silence_start_});
+                triggered_ = false;
+                silence_open_ = false;
             }
         }
     }
-    if (triggered && sat_sub(audio_len, speech_start) >= min_speech) speech.push_back({speech_start, audio_len});
-    if (speech.empty()) return speech;
+}
 
-    const size_t n = speech.size();
-    for (size_t i = 0; i < n; ++i) {
-        if (i == 0) speech[i].start = sat_sub(speech[i].start, pad);
-        if (i + 1 < n) {
-            const int64_t gap = sat_sub(speech[i + 1].start, speech[i].end);
-            const int64_t grow = gap < 2 * pad ? gap / 2 : pad;
-            speech[i].end = std::min(speech[i].end + grow, audio_len);
-            speech[i + 1].start = sat_sub(speech[i + 1].start, grow);
-        } else {
-            speech[i].end = std::min(speech[i].end + pad, audio_len);
-        }
+void SpeechRegionStream::finish() {
+    if (audio_len_ <= 0 || window_ == 0) return;
+    if (triggered_ && sat_sub(audio_len_, speech_start_) >= min_speech_) on_speech({speech_start_, audio_len_});
+    triggered_ = false;
+    if (has_pending_) {
+        pending_.end = std::min(pending_.end + pad_, audio_len_);
+        if (pending_.end > pending_.start) regions_.push_back(pending_);
+        has_pending_ = false;
     }
-    speech.erase(std::remove_if(speech.begin(), speech.end(), [](const sb_sample_range& r) { return r.end <= r.start; }),
-                 speech.end());
-    return speech;
+}
+
+std::vector<sb_sample_range> detect_speech_regions(const float* prob, int64_t n_prob, int64_t audio_len, float threshold,
+                                                   const sb_vad_segmentation_config& cfg) {
+    SpeechRegionStream stream(audio_len, threshold, cfg);
+    if (n_prob > 0) stream.push(prob, n_prob);
+    stream.finish();
+    return stream.regions();
 }
 
 bool plan_region_subsegments(sb_sample_range region, const float* region_prob, int64_t n_prob,
@@ -155,31 +174,32 @@ bool plan_region_subsegments(sb_sample_range region, const float* region_prob, i
     return true;
 }
 
+void append_region_plan(ExecutionPlan* plan, sb_sample_range region, const float* prob, int64_t n_prob,
+                        const sb_longform_config& cfg) {
+    const int64_t max_chunk = cfg.transcription.max_audio_samples;
+    sb_region_task rt{1, (int64_t)plan->tasks.size(), 0};
+    if (sat_sub(region.end, region.start) <= max_chunk) {
+        plan->tasks.push_back(segment_task(region));
+    } else {
+        // region_probability_slice
+        const int64_t w0 = std::min(region.start / kVadWindowSamples, n_prob);
+        const int64_t w1 = std::min(div_ceil(region.end, kVadWindowSamples), n_prob);
+        std::vector<sb_sample_range> parts;
+        if (plan_region_subsegments(region, prob + w0, std::max<int64_t>(w1 - w0, 0), cfg.segmentation, max_chunk, &parts)) {
+            for (const sb_sample_range& s : parts) plan->tasks.push_back(segment_task(s));
+        } else {
+            rt.kind = 0;
+            for (const sb_sample_range& s : overlap_plan(region, cfg.overlap)) plan->tasks.push_back(overlap_task(s, cfg.overlap));
+        }
+    }
+    rt.n_tasks = (int64_t)plan->tasks.size() - rt.first_task;
+    plan->regions.push_back(rt);
+}
+
 ExecutionPlan build_vad_plan(const std::vector<sb_sample_range>& regions, const float* prob, int64_t n_prob,
                              const sb_longform_config& cfg) {
     ExecutionPlan plan;
-    const int64_t max_chunk = cfg.transcription.max_audio_samples;
-    for (const sb_sample_range& region : regions) {
-        sb_region_task rt{1, (int64_t)plan.tasks.size(), 0};
-        if (sat_sub(region.end, region.start) <= max_chunk) {
-            plan.tasks.push_back(segment_task(region));
-        } else {
-            // region_probability_slice
-            const int64_t w0 = std::min(region.start / kVadWindowSamples, n_prob);
-            const int64_t w1 = std::min(div_ceil(region.end, kVadWindowSamples), n_prob);
-            std::vector<sb_sample_range> parts;
-            if (plan_region_subsegments(region, prob + w0, std::max<int64_t>(w1 - w0, 0), cfg.segmentation, max_chunk,
-                                        &parts)) {
-                for (const sb_sample_range& s : parts) plan.tasks.push_back(segment_task(s));
-            } else {
-                rt.kind = 0;
-                for (const sb_sample_range& s : overlap_plan(region, cfg.overlap))
-                    plan.tasks.push_back(overlap_task(s, cfg.overlap));
-            }
-        }
-        rt.n_tasks = (int64_t)plan.tasks.size() - rt.first_task;
-        plan.regions.push_back(rt);
-    }
+    for (const sb_sample_range& region : regions) append_region_plan(&plan, region, prob, n_prob, cfg);
     return plan;
 }
 

@@ -516,11 +516,13 @@ cudaError_t upload(const std::vector<float>& v, float** out) {
 void VadModel::release() {
     for (float* p : {basis, w1, b1, w2, b2, w3, b3, w4, b4, wih, bsum, whh, wout})
         if (p) cudaFree(p);
-    gx.release();
+    gx[0].release();
+    gx[1].release();
     hout.release();
     state.release();
     audio.release();
     prob.release();
+    host_prob.release();
 }
 
 cudaError_t vad_configure() {
@@ -607,41 +609,63 @@ int32_t vad_load(sb_ctx* c, const sb_tensor* tensors, int64_t n_tensors) {
     return SB_OK;
 }
 
+const float* vad_resident_audio(const sb_ctx* c) { return c->vad ? c->vad->audio.as<float>() : nullptr; }
+
+int32_t vad_begin(sb_ctx* c, int64_t max_pass_windows, cudaStream_t st, bool two_buffers) {
+    if (!c->vad) return fail(SB_MISSING_MODEL_ASSET, "missing model asset: vad network (sb_vad_load)");
+    VadModel& m = *c->vad;
+    SB_CUDA(cudaSetDevice(c->device));
+    SB_CUDA(m.gx[0].ensure((size_t)max_pass_windows * kVadGates * sizeof(float)));
+    if (two_buffers) SB_CUDA(m.gx[1].ensure((size_t)max_pass_windows * kVadGates * sizeof(float)));
+    SB_CUDA(m.hout.ensure((size_t)max_pass_windows * kVadState * sizeof(float)));
+    SB_CUDA(cudaMemsetAsync(m.state.p, 0, 2 * kVadState * sizeof(float), st));  // vad.rs:73-74
+    return SB_OK;
+}
+
+int32_t vad_encode_pass(sb_ctx* c, cudaStream_t st, const float* d_audio, int64_t n_samples, int64_t first, int n, int buf) {
+    VadModel& m = *c->vad;
+    EncodeParams p{d_audio, n_samples, first, n,       m.basis, m.w1, m.b1, m.w2,
+                   m.b2,    m.w3,      m.b3,  m.w4,    m.b4,    m.wih, m.bsum, m.gx[buf].as<float>()};
+    c->prof.begin("vad_encode", st);
+    vad_encode_kernel<<<(n + kTileWindows - 1) / kTileWindows, kEncThreads, kEncSmem, st>>>(p);
+    c->prof.end(st);
+    SB_CUDA(cudaGetLastError());
+    c->launches += 1;
+    return SB_OK;
+}
+
+int32_t vad_recur_pass(sb_ctx* c, cudaStream_t st, int64_t first, int n, int buf, float* d_prob) {
+    VadModel& m = *c->vad;
+    c->prof.begin("vad_lstm", st);
+    float *gxp = m.gx[buf].as<float>(), *stp = m.state.as<float>(), *hop = m.hout.as<float>();
+    cudaError_t e;
+    if (c->vad_cluster == 4)
+        e = c->vad_row_threads == 4 ? launch_lstm<4, 4>(gxp, m.whh, stp, hop, n, c->d_error, st)
+                                    : launch_lstm<4, 2>(gxp, m.whh, stp, hop, n, c->d_error, st);
+    else
+        e = c->vad_row_threads == 4 ? launch_lstm<8, 4>(gxp, m.whh, stp, hop, n, c->d_error, st)
+                                    : launch_lstm<8, 2>(gxp, m.whh, stp, hop, n, c->d_error, st);
+    c->prof.end(st);
+    SB_CUDA(e);
+    c->prof.begin("vad_prob", st);
+    vad_prob_kernel<<<(n + 7) / 8, 256, 0, st>>>(m.hout.as<float>(), m.wout, m.bout, d_prob + first, n);
+    c->prof.end(st);
+    SB_CUDA(cudaGetLastError());
+    c->launches += 2;
+    return SB_OK;
+}
+
 int32_t vad_process_device(sb_ctx* c, const float* d_audio, int64_t n_samples, float* d_prob) {
     if (!c->vad) return fail(SB_MISSING_MODEL_ASSET, "missing model asset: vad network (sb_vad_load)");
     if (n_samples <= 0) return SB_OK;
-    VadModel& m = *c->vad;
-    SB_CUDA(cudaSetDevice(c->device));
-    cudaStream_t st = c->stream;
     const int64_t total = (n_samples + kVadWindow - 1) / kVadWindow;
     const int64_t seg = std::min<int64_t>(total, c->vad_segment_windows);
-    SB_CUDA(m.gx.ensure((size_t)seg * kVadGates * sizeof(float)));
-    SB_CUDA(m.hout.ensure((size_t)seg * kVadState * sizeof(float)));
-    SB_CUDA(cudaMemsetAsync(m.state.p, 0, 2 * kVadState * sizeof(float), st));  // vad.rs:73-74
+    int32_t s = vad_begin(c, seg, c->stream, false);
+    if (s != SB_OK) return s;
     for (int64_t first = 0; first < total; first += seg) {
         const int n = (int)std::min<int64_t>(seg, total - first);
-        EncodeParams p{d_audio, n_samples, first, n,       m.basis, m.w1, m.b1, m.w2,
-                       m.b2,    m.w3,      m.b3,  m.w4,    m.b4,    m.wih, m.bsum, m.gx.as<float>()};
-        c->prof.begin("vad_encode", st);
-        vad_encode_kernel<<<(n + kTileWindows - 1) / kTileWindows, kEncThreads, kEncSmem, st>>>(p);
-        c->prof.end(st);
-        SB_CUDA(cudaGetLastError());
-        c->prof.begin("vad_lstm", st);
-        float *gxp = m.gx.as<float>(), *stp = m.state.as<float>(), *hop = m.hout.as<float>();
-        cudaError_t e;
-        if (c->vad_cluster == 4)
-            e = c->vad_row_threads == 4 ? launch_lstm<4, 4>(gxp, m.whh, stp, hop, n, c->d_error, st)
-                                        : launch_lstm<4, 2>(gxp, m.whh, stp, hop, n, c->d_error, st);
-        else
-            e = c->vad_row_threads == 4 ? launch_lstm<8, 4>(gxp, m.whh, stp, hop, n, c->d_error, st)
-                                        : launch_lstm<8, 2>(gxp, m.whh, stp, hop, n, c->d_error, st);
-        c->prof.end(st);
-        SB_CUDA(e);
-        c->prof.begin("vad_prob", st);
-        vad_prob_kernel<<<(n + 7) / 8, 256, 0, st>>>(m.hout.as<float>(), m.wout, m.bout, d_prob + first, n);
-        c->prof.end(st);
-        SB_CUDA(cudaGetLastError());
-        c->launches += 3;
+        if ((s = vad_encode_pass(c, c->stream, d_audio, n_samples, first, n, 0)) != SB_OK) return s;
+        if ((s = vad_recur_pass(c, c->stream, first, n, 0, d_prob)) != SB_OK) return s;
     }
     return SB_OK;
 }

@@ -5,7 +5,7 @@ block of tasks, results are put back in task order and merged by one consumer.  
 data-path collective; `torch.distributed` only carries the small per-task token streams."""
 from __future__ import annotations
 
-from .pipeline import RawBatch, RawTranscription, longform_finish
+from .pipeline import RawBatch, RawTranscription, longform_finish, longform_finish_regions
 
 
 def shard_bounds(n_tasks: int, rank: int, world: int):
@@ -102,3 +102,14 @@ def gather_and_finish(vocab, audio_len: int, raws, rank: int, world: int, group=
     if allr is None:
         return None
     return longform_finish(vocab, audio_len, allr)
+
+
+def gather_and_finish_regions(vocab, audio_len: int, tasks, region_tasks, raws, rank: int, world: int, group=None):
+    """The same for a plan of region tasks (the VAD mode): every rank builds the same plan from the same
+    probabilities (the planner is deterministic host logic, so no plan is sent), transcribes its block
+    `shard_bounds(len(tasks), rank, world)` of the tasks, and rank 0 joins the regions
+    (build_parallel_result, src/long_form.rs:344-374).  None on the other ranks."""
+    allr = gather_raws(raws, rank, world, group)
+    if allr is None:
+        return None
+    return longform_finish_regions(vocab, audio_len, tasks, region_tasks, allr)

@@ -154,6 +154,16 @@ def test_vad_mode_equals_its_parts(ctx, pipe):
     same_result(got, want)
     same_result(lf.run_with_probabilities(audio, probs, cfg), want)
     assert len(got.chunks) <= len(regions) and len(got.token_ids) > 0
+    # the run above overlapped the network's passes with the transcription; all of the network first must give the
+    # same, and so must short passes (many pieces) with the decoder run in rounds
+    ctx.set_option("vad_unstreamed", 1)
+    same_result(lf.run_with_config(audio, cfg), want)
+    ctx.set_option("vad_unstreamed", 0)
+    ctx.set_option("vad_segment_windows", 700)
+    ctx.set_option("vad_rows_cap", 1500)
+    same_result(lf.run_with_config(audio, cfg), want)
+    ctx.set_option("vad_segment_windows", 131072)
+    ctx.set_option("vad_rows_cap", 0)
     # chunks are in recording order and inside their regions (with the padding the planner added)
     starts = [c.start for c in got.chunks]
     assert starts == sorted(starts)
