@@ -676,16 +676,19 @@ int32_t run_vad_plan(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const 
 // recurrence of the network occupies one 8-CTA cluster for as long as the rest of the GPU needs to transcribe a
 // comparable stretch of audio, so the host plans the regions that pass k made final (SpeechRegionStream) and
 // sends their tasks through the frontend and the encoder on the context's stream while pass k + 1 runs beside
-// them.  Passes start short (the first one is exposed) and double up to "vad_segment_windows".  The decoder runs
+// them.  Passes start short (the first one is exposed) and double up to 32768 windows (or "vad_segment_windows", if smaller).  The decoder runs
 // once at the end.  Regions, tasks and results equal those of the unstreamed path.
 int32_t run_vad_streamed(sb_ctx* c, const sb_vocab* vocab, const float* audio, int64_t n_samples,
                          const sb_longform_config& lc, sb_result** out) {
     VadModel& m = *c->vad;
     SB_CUDA(cudaSetDevice(c->device));
     const int64_t n_win = sb_vad_num_windows(n_samples);
+    // passes of 8192, 16384, then 32768 windows (17 minutes of audio; measured on an 8 h recording: longer passes
+    // leave a longer stretch to transcribe after the last recurrence, shorter ones make the pieces' kernels small)
+    const int64_t pass_cap = std::min<int64_t>(c->vad_segment_windows, 32768);
     std::vector<int64_t> cut{0};  // pass boundaries, in windows
-    for (int64_t w = 8192; cut.back() < n_win; w = std::min<int64_t>(2 * w, c->vad_segment_windows))
-        cut.push_back(std::min(n_win, cut.back() + std::min<int64_t>(w, c->vad_segment_windows)));
+    for (int64_t w = 8192; cut.back() < n_win; w = std::min<int64_t>(2 * w, pass_cap))
+        cut.push_back(std::min(n_win, cut.back() + std::min<int64_t>(w, pass_cap)));
     const int n_pass = (int)cut.size() - 1;
     int64_t max_pass = 0;
     for (int k = 0; k < n_pass; ++k) max_pass = std::max(max_pass, cut[k + 1] - cut[k]);
