@@ -64,7 +64,37 @@ def planner_cases():
     return {"planner_cases": np.array(rows, np.int64)}
 
 
+def vad_cases():
+    """The voice-activity network's oracle on a short seeded recording, and the planner on a fixed probability track
+    (written to their own file so that the other vectors stay byte for byte what they were)."""
+    from oracle import vad_oracle as vo
+
+    w = synth.seeded_vad_weights(5)
+    audio = synth.sparse_speech_audio(16000 * 8 + 77, 31, speech_seconds=(1.0, 3.0), silence_seconds=(0.3, 1.0))
+    probs = vo.vad_probabilities(w, audio)
+    rng = np.random.default_rng(77)
+    track = np.clip(np.repeat(rng.choice([0.02, 0.5, 0.95], 60, p=[0.3, 0.1, 0.6]), 25) + rng.normal(0, 0.03, 1500), 0, 1)
+    track[200:800] = np.clip(0.95 + rng.normal(0, 0.02, 600), 0, 1)  # 19 s without a silence: overlap windows
+    track = track.astype(np.float32)
+    n = 1500 * 512 - 100
+    regions = vo.detect_speech_regions(track, n, 0.85, vo.Segmentation())
+    tasks, rts = vo.build_execution_plan(regions, track, vo.Segmentation(), 240_000)
+    return {
+        "vad_weights_seed": np.array(5, np.int64), "vad_audio_seed": np.array(31, np.int64),
+        "vad_audio_len": np.array(audio.size, np.int64), "vad_probabilities": probs.astype(np.float32),
+        "plan_track": track, "plan_audio_len": np.array(n, np.int64),
+        "plan_regions": np.array(regions, np.int64).reshape(-1, 2), "plan_tasks": np.array(tasks, np.int64).reshape(-1, 4),
+        "plan_region_tasks": np.array([(k, idx[0], len(idx)) for k, idx in rts], np.int64).reshape(-1, 3),
+    }
+
+
 def main():
+    vad = vad_cases()
+    vpath = os.path.join(HERE, "golden_vad.npz")
+    np.savez_compressed(vpath, **vad)
+    print("wrote", vpath, os.path.getsize(vpath), "bytes;", ", ".join(sorted(vad)))
+    if "--vad-only" in sys.argv:
+        return
     blob = {}
     blob.update(frontend_cases())
     blob.update(decode_case())

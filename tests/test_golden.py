@@ -63,3 +63,45 @@ def test_cuda_frontend_matches_golden(ctx, name):
     else:
         assert np.linalg.norm(feats - gold) / np.linalg.norm(gold) <= 1e-4
         assert np.abs(feats - gold).max() <= 1e-4 * np.abs(gold).max()
+
+
+# ---------------------------------------------------------------- VAD mode
+def _vad_golden():
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_vad.npz"))
+
+
+def test_oracle_vad_reproduces_golden():
+    from oracle import vad_oracle as vo
+    from scriptrs_b200 import synth
+
+    g = _vad_golden()
+    audio = synth.sparse_speech_audio(int(g["vad_audio_len"]), int(g["vad_audio_seed"]), speech_seconds=(1.0, 3.0),
+                                      silence_seconds=(0.3, 1.0))
+    probs = vo.vad_probabilities(synth.seeded_vad_weights(int(g["vad_weights_seed"])), audio)
+    assert np.abs(probs - g["vad_probabilities"]).max() < 1e-5   # BLAS summation order may differ between hosts
+    regions = vo.detect_speech_regions(g["plan_track"], int(g["plan_audio_len"]), 0.85, vo.Segmentation())
+    assert np.array_equal(np.array(regions, np.int64).reshape(-1, 2), g["plan_regions"])
+
+
+def test_vad_plan_golden_host_library():
+    import scriptrs_b200 as sb
+
+    g = _vad_golden()
+    regions = sb.detect_speech_regions(g["plan_track"], int(g["plan_audio_len"]))
+    assert np.array_equal(np.array(regions, np.int64).reshape(-1, 2), g["plan_regions"])
+    tasks, rts = sb.plan_vad(regions, g["plan_track"])
+    assert np.array_equal(np.array(tasks, np.int64).reshape(-1, 4), g["plan_tasks"])
+    assert np.array_equal(np.array(rts, np.int64).reshape(-1, 3), g["plan_region_tasks"])
+    assert {int(k) for k in g["plan_region_tasks"][:, 0]} == {0, 1}
+
+
+@pytest.mark.gpu
+def test_cuda_vad_matches_golden(ctx):
+    import scriptrs_b200 as sb
+    from scriptrs_b200 import synth
+
+    g = _vad_golden()
+    audio = synth.sparse_speech_audio(int(g["vad_audio_len"]), int(g["vad_audio_seed"]), speech_seconds=(1.0, 3.0),
+                                      silence_seconds=(0.3, 1.0))
+    probs = sb.SileroVad(ctx, synth.seeded_vad_weights(int(g["vad_weights_seed"]))).process(audio)
+    assert np.abs(probs - g["vad_probabilities"]).max() < 2e-4

@@ -223,3 +223,26 @@ def test_vad_mode_needs_the_network(pipe):
         assert e.value.status == 3                                     # MissingModelAsset, long_form.rs:194-199
     finally:
         fresh.close()
+
+
+def test_vad_mode_with_two_contexts(ctx, pipe):
+    """Mode 1 of sb_longform_run_multi with two contexts: the first runs the network, the region tasks are dealt to
+    both (the first reads the recording it already holds on the GPU, the second its share from the host)."""
+    import scriptrs_b200 as sb
+
+    second = sb.Context(0)
+    try:
+        w = eo.seeded_weights(eo.EncoderConfig(layers=LAYERS), seed=21, std=0.02, plain_norms=False)
+        w.update(oracle.seeded_decoder_weights(22))
+        sb.load_model(second, w, LAYERS, has_encoder=True, has_decoder=True)
+        sb.SileroVad(ctx, synth.energy_vad_weights())
+        audio = synth.sparse_speech_audio(16000 * 120, 6, speech_seconds=(2.0, 24.0))
+        cfg = sb.LongFormConfig(mode=sb.LongFormMode.Vad)
+        one = sb.LongFormTranscriptionPipeline(pipe).run_with_config(audio, cfg)
+        both = sb.LongFormTranscriptionPipeline(pipe, extra_contexts=[second])
+        k0 = second.kernel_launches()
+        two = both.run_with_config(audio, cfg)
+        same_result(two, one)
+        assert second.kernel_launches() > k0 and len(one.token_ids) > 0
+    finally:
+        second.close()
