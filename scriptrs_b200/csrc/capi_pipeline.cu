@@ -637,8 +637,13 @@ int32_t execute_plan(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const 
     auto work = [&](int64_t k) {
         const int64_t a = n_tasks * k / shards, b = n_tasks * (k + 1) / shards;
         const bool resident = k == 0 && d_audio0;
-        status[k] = transcribe_tasks(ctxs[k], resident ? d_audio0 : audio, n_samples, plan.tasks.data() + a, b - a,
-                                     lc.transcription, &parts[k], resident);
+        // a batch holds at most 65535 tasks (a plan of very short regions over a long recording can hold more)
+        for (int64_t i = a; i < b && status[k] == SB_OK; i += 32768) {
+            std::vector<RawTokens> some;
+            status[k] = transcribe_tasks(ctxs[k], resident ? d_audio0 : audio, n_samples, plan.tasks.data() + i,
+                                         std::min<int64_t>(32768, b - i), lc.transcription, &some, resident);
+            for (auto& r : some) parts[k].push_back(std::move(r));
+        }
         if (status[k] != SB_OK) errors[k] = sb_last_error();
     };
     if (shards == 1) {
@@ -684,7 +689,8 @@ int32_t run_vad_streamed(sb_ctx* c, const sb_vocab* vocab, const float* audio, i
     SB_CUDA(cudaSetDevice(c->device));
     const int64_t n_win = sb_vad_num_windows(n_samples);
     // passes of 8192, 16384, then 32768 windows (17 minutes of audio; measured on an 8 h recording: longer passes
-    // leave a longer stretch to transcribe after the last recurrence, shorter ones make the pieces' kernels small)
+    // leave a longer stretch to transcribe after the last recurrence, shorter ones make the pieces' kernels small;
+    // shorter passes at the end as well changed nothing, the recurrences being the critical path)
     const int64_t pass_cap = std::min<int64_t>(c->vad_segment_windows, 32768);
     std::vector<int64_t> cut{0};  // pass boundaries, in windows
     for (int64_t w = 8192; cut.back() < n_win; w = std::min<int64_t>(2 * w, pass_cap))
