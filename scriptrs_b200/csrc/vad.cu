@@ -270,8 +270,16 @@ __global__ void __launch_bounds__(kEncThreads, 2) vad_encode_kernel(const Encode
     }
 }
 
-// 1 / (1 + e^-x); e^-x overflows to +inf for very negative x and the quotient is then 0
-__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+// 1 / (1 + 2^(k x)) with the hardware's exponential and reciprocal (relative error about 2^-22 each): k = -log2(e)
+// gives the logistic function, k = -2 log2(e) gives (tanh(x) + 1) / 2.  2^(k x) overflows to +inf for very negative
+// x, and the reciprocal of +inf is 0.
+__device__ __forceinline__ float logistic_pow2(float x, float k) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * k));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return r;
+}
+constexpr float kNegLog2e = -1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -361,7 +369,7 @@ vad_lstm_kernel(const float* __restrict__ gx, const float* __restrict__ whh, flo
     __shared__ float gring[kDepth][kThreads];
     __shared__ __align__(8) uint64_t mbar[2];
 
-    float w[kCols];
+    float2 w[kCols / 2];  // pairs, for the two-wide fp32 multiply-add
     {
         // thread `part` of a row holds the 16-byte column chunks part, part + P, ...: the P lanes of a row read
         // neighbouring chunks of h, which lie in different banks
@@ -369,7 +377,8 @@ vad_lstm_kernel(const float* __restrict__ gx, const float* __restrict__ whh, flo
 #pragma unroll
         for (int k = 0; k < kCols / 4; ++k) {
             const float4 v = __ldg(src + k * P);
-            w[4 * k] = v.x; w[4 * k + 1] = v.y; w[4 * k + 2] = v.z; w[4 * k + 3] = v.w;
+            w[2 * k] = make_float2(v.x, v.y);
+            w[2 * k + 1] = make_float2(v.z, v.w);
         }
     }
     if (tid < kVadState) hs[0][tid] = state[tid];
@@ -403,7 +412,9 @@ vad_lstm_kernel(const float* __restrict__ gx, const float* __restrict__ whh, flo
     for (int j = 0; j < kDepth; ++j) fetch(j);
     cluster.sync();  // barriers initialised and hs[0] filled everywhere before the first remote store
 
-    const float gate_scale = q == 2 ? 2.0f : 1.0f;  // tanh(x) = 2 sigmoid(2 x) - 1 for the cell candidate
+    // the cell candidate (gate 2) is a tanh: 2 / (1 + e^(-2 x)) - 1; the other gates are logistic
+    const float gate_k = q == 2 ? 2.0f * kNegLog2e : kNegLog2e;
+    const float gate_mul = q == 2 ? 2.0f : 1.0f, gate_add = q == 2 ? -1.0f : 0.0f;
     const int base = lane - unit_lane;
     bool alive = true;
     for (int s = 0; s < n; ++s) {
@@ -419,27 +430,26 @@ vad_lstm_kernel(const float* __restrict__ gx, const float* __restrict__ whh, flo
             if (tid == 0 && ok && s + 2 <= n) mbar_expect_tx(cur ? mbar1 : mbar0, kVadState * 4);
         }
         const float4* hv = reinterpret_cast<const float4*>(&hs[cur][0]) + part;
-        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        float2 a0 = make_float2(0.0f, 0.0f), a1 = a0, a2 = a0, a3 = a0;
 #pragma unroll
-        for (int k = 0; k < kCols / 4; ++k) {
-            const float4 v = hv[k * P];
-            a0 = fmaf(w[4 * k], v.x, a0);
-            a1 = fmaf(w[4 * k + 1], v.y, a1);
-            a2 = fmaf(w[4 * k + 2], v.z, a2);
-            a3 = fmaf(w[4 * k + 3], v.w, a3);
+        for (int k = 0; k < kCols / 4; k += 2) {
+            const float4 u = hv[k * P], v = hv[(k + 1) * P];
+            a0 = __ffma2_rn(w[2 * k], make_float2(u.x, u.y), a0);
+            a1 = __ffma2_rn(w[2 * k + 1], make_float2(u.z, u.w), a1);
+            a2 = __ffma2_rn(w[2 * k + 2], make_float2(v.x, v.y), a2);
+            a3 = __ffma2_rn(w[2 * k + 3], make_float2(v.z, v.w), a3);
         }
-        float pre = (a0 + a1) + (a2 + a3);
+        float pre = ((a0.x + a0.y) + (a1.x + a1.y)) + ((a2.x + a2.y) + (a3.x + a3.y));
 #pragma unroll
         for (int o = 1; o < P; o <<= 1) pre += __shfl_xor_sync(0xffffffffu, pre, o);
         pre += gxv;
-        const float sg = sigmoid_fast(gate_scale * pre);
-        const float act = q == 2 ? fmaf(2.0f, sg, -1.0f) : sg;
+        const float act = fmaf(gate_mul, logistic_pow2(pre, gate_k), gate_add);
         const float gi = __shfl_sync(0xffffffffu, act, base);
         const float gf = __shfl_sync(0xffffffffu, act, base + P);
         const float gg = __shfl_sync(0xffffffffu, act, base + 2 * P);
         const float go = __shfl_sync(0xffffffffu, act, base + 3 * P);
         c = fmaf(gf, c, gi * gg);
-        h = go * fmaf(2.0f, sigmoid_fast(2.0f * c), -1.0f);
+        h = go * fmaf(2.0f, logistic_pow2(c, 2.0f * kNegLog2e), -1.0f);
         if (unit_lane == 0) stage[unit_local] = h;
         alive = __syncthreads_and(ok);  // the CTA's h values are staged; and did every wait of the CTA succeed?
         if (!alive) {
