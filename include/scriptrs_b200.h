@@ -516,7 +516,8 @@ int32_t sb_vad_load_file(sb_ctx* ctx, const char* path);
  * zero probabilities (vad.rs:65-67). */
 int32_t sb_vad_process(sb_ctx* ctx, const float* audio, int64_t n_samples, float* probabilities, int64_t cap,
                        int64_t* n_probabilities);
-/* The same with the recording and the result in device memory (asynchronous on the context's stream). */
+/* The same with the recording and the result in device memory (asynchronous on the context's stream; a device-side
+ * wait that ran out is reported by sb_ctx_synchronize, and by sb_vad_process itself as SB_TIMEOUT). */
 int32_t sb_vad_process_device(sb_ctx* ctx, const float* d_audio, int64_t n_samples, float* d_probabilities);
 
 /* ------------------------------------------------------------------ GEMM */

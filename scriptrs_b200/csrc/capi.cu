@@ -142,6 +142,17 @@ int32_t frontend_run(sb_ctx* c, const void* d_pcm, SampleFormat fmt, const int64
     return SB_OK;
 }
 
+int32_t take_device_error(sb_ctx* c, cudaStream_t st) {
+    int err = 0;
+    SB_CUDA(cudaMemcpyAsync(&err, c->d_error, sizeof(int), cudaMemcpyDeviceToHost, st));
+    SB_CUDA(cudaStreamSynchronize(st));
+    if (err) {
+        SB_CUDA(cudaMemsetAsync(c->d_error, 0, sizeof(int), st));
+        return fail(SB_TIMEOUT, "a bounded device-side wait ran out (kernel aborted cleanly)");
+    }
+    return SB_OK;
+}
+
 }  // namespace sb
 
 extern "C" {
@@ -488,8 +499,7 @@ int32_t sb_vad_process(sb_ctx* c, const float* audio, int64_t n_samples, float* 
     const int32_t s = vad_process_device(c, m.audio.as<float>(), n_samples, m.prob.as<float>());
     if (s != SB_OK) return s;
     SB_CUDA(cudaMemcpyAsync(prob, m.prob.p, sizeof(float) * (size_t)n, cudaMemcpyDeviceToHost, c->stream));
-    SB_CUDA(cudaStreamSynchronize(c->stream));
-    return SB_OK;
+    return take_device_error(c, c->stream);  // synchronises; a recurrence that gave up waiting fails the call
 }
 
 int64_t sb_weights_file_list(const char* path, char* buf, int64_t cap) {

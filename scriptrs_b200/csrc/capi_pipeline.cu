@@ -782,6 +782,7 @@ int32_t run_vad_streamed(sb_ctx* c, const sb_vocab* vocab, const float* audio, i
         if ((s = run.add(plan.tasks.data() + first_task, (int64_t)(plan.tasks.size() - first_task))) != SB_OK) return bail(s);
     }
     c->sm_count = all_sms;  // every pass has ended
+    if ((s = take_device_error(c, vs)) != SB_OK) return bail(s);  // a recurrence that gave up waiting
     sb_result* res = new sb_result();
     if (plan.tasks.empty()) {  // TranscriptionResult::empty (long_form.rs:206-208)
         res->r.duration_seconds = (double)n_samples / 16000.0;

@@ -52,6 +52,9 @@ struct EncoderWorkspace;  // encoder.h
 struct DecodeWorkspace;   // pipeline.cu
 struct VadModel;          // vad.h
 int32_t model_load(sb_ctx* c, const sb_model_desc* desc, const sb_tensor* tensors, int64_t n_tensors);
+// Reads (after the stream `st` has drained up to here) the flag that a kernel raises when a bounded wait runs out;
+// clears it and fails with SB_TIMEOUT if it was set.
+int32_t take_device_error(sb_ctx* c, cudaStream_t st);
 
 }  // namespace sb
 

@@ -503,6 +503,20 @@ class LongFormTranscriptionPipeline:
         self.inner = inner
         self.contexts = [inner.ctx, *extra_contexts]
         self.default_config = LongFormConfig()
+        self.vad = None
+
+    @classmethod
+    def from_dir(cls, models_dir: str, device: int = 0, fp8_weights: bool = False) -> "LongFormTranscriptionPipeline":
+        """src/long_form.rs:100-123: the base bundle must be present; the VAD network file
+        (`<models_dir>/vad/silero-vad.safetensors`) is optional here and needed only when the Vad mode is used
+        (load_vad, src/long_form.rs:663-670)."""
+        from . import weights
+
+        lf = cls(TranscriptionPipeline.from_dir(models_dir, device=device, fp8_weights=fp8_weights))
+        path = weights.vad_path(models_dir)
+        if os.path.exists(path):
+            lf.vad = SileroVad(lf.inner.ctx, path=path)
+        return lf
 
     def run(self, audio) -> TranscriptionResult:
         return self.run_with_config(audio, self.default_config)

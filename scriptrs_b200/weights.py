@@ -18,6 +18,7 @@ from ._lib import ScriptrsError, check
 
 MODEL_FILE = os.path.join("parakeet-v2", "model.safetensors")
 VOCAB_FILE = os.path.join("parakeet-v2", "vocab.txt")
+VAD_FILE = os.path.join("vad", "silero-vad.safetensors")  # stands where the reference has vad/silero-vad.mlmodelc (src/models.rs:10)
 
 
 def _to_bf16_bytes(a: np.ndarray) -> bytes:
@@ -85,3 +86,17 @@ def validate_bundle(models_dir: str):
         if not os.path.exists(p):
             raise ScriptrsError(3, f"missing model asset: {p}")
     return model, vocab
+
+
+def vad_path(models_dir: str) -> str:
+    """ModelBundle::vad_dir (src/models.rs:96-99)."""
+    return os.path.join(models_dir, VAD_FILE)
+
+
+def validate_with_vad(models_dir: str):
+    """ModelBundle::validate_with_vad (src/models.rs:68-78): the base bundle plus the VAD network file."""
+    model, vocab = validate_bundle(models_dir)
+    vad = vad_path(models_dir)
+    if not os.path.exists(vad):
+        raise ScriptrsError(3, f"missing model asset: {vad}")
+    return model, vocab, vad

@@ -107,6 +107,28 @@ def test_missing_tensor_and_missing_network(ctx, pipe):
         fresh.close()
 
 
+def test_device_side_timeout_flag_fails_the_network_call(ctx, pipe):
+    """Host-side fault injection: the flag that the recurrence kernel raises when its bounded wait for the other
+    thread blocks runs out makes sb_vad_process and the VAD mode fail with SB_TIMEOUT; the context stays usable."""
+    import scriptrs_b200 as sb
+
+    w = synth.seeded_vad_weights(5)
+    vad = sb.SileroVad(ctx, w)
+    audio = synth.sparse_speech_audio(16000 * 20, 3)
+    good = vad.process(audio)
+    ctx.set_option("test_raise_device_error", 1)
+    with pytest.raises(sb.ScriptrsError) as e:
+        vad.process(audio)
+    assert e.value.status == 10
+    assert np.array_equal(vad.process(audio), good)      # the flag was cleared by the failing call
+    lf = sb.LongFormTranscriptionPipeline(pipe)
+    ctx.set_option("test_raise_device_error", 1)
+    with pytest.raises(sb.ScriptrsError) as e:
+        lf.run_with_config(audio, sb.LongFormConfig(mode=sb.LongFormMode.Vad))
+    assert e.value.status == 10
+    ctx.synchronize()
+
+
 def test_energy_detector_weights_find_the_sound(ctx):
     import scriptrs_b200 as sb
 

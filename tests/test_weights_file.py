@@ -119,3 +119,40 @@ def test_pipeline_from_dir(ctx, tmp_path):
     sb.load_model(ctx, w, encoder_layers=1, has_encoder=True, has_decoder=True)
     ref = sb.TranscriptionPipeline(ctx, pipe.vocab).run(synth.clip_audio(64000, 1))
     assert res.text == ref.text and res.tokens == ref.tokens
+
+
+@pytest.mark.gpu
+def test_long_form_from_dir_loads_the_vad_file_if_present(tmp_path):
+    """LongFormTranscriptionPipeline::from_dir + load_vad (src/long_form.rs:100-123,663-670): the VAD network is
+    optional at construction and only needed by the Vad mode; its file (public Silero state-dict names behind
+    "_model.", here as bf16) gives the probabilities of the same weights loaded from memory."""
+    root = str(tmp_path)
+    weights.save_safetensors(os.path.join(root, weights.MODEL_FILE), synth.seeded_model(1))
+    with open(os.path.join(root, weights.VOCAB_FILE), "w", encoding="utf-8") as f:
+        f.write("".join(f"▁t{i} {i}\n" for i in range(1024)) + "<blk> 1024\n")
+    audio = synth.sparse_speech_audio(16000 * 40, 12)
+    lf = sb.LongFormTranscriptionPipeline.from_dir(root)
+    try:
+        assert lf.vad is None
+        with pytest.raises(sb.ScriptrsError) as e:
+            lf.run_with_config(audio, sb.LongFormConfig(mode=sb.LongFormMode.Vad))
+        assert e.value.status == 3
+        assert len(lf.run(audio).chunks) <= 1                      # the Fast mode needs no VAD network
+        with pytest.raises(sb.ScriptrsError) as e:
+            weights.validate_with_vad(root)
+        assert e.value.status == 3 and "silero-vad" in e.value.message
+    finally:
+        lf.inner.ctx.close()
+    vw = synth.energy_vad_weights()
+    weights.save_safetensors(weights.vad_path(root), {"_model." + k: v for k, v in vw.items()})
+    assert weights.validate_with_vad(root)[2].endswith("silero-vad.safetensors")
+    lf = sb.LongFormTranscriptionPipeline.from_dir(root)
+    try:
+        assert lf.vad is not None
+        from_file = lf.vad.process(audio)
+        res = lf.run_with_config(audio, sb.LongFormConfig(mode=sb.LongFormMode.Vad))
+        assert len(res.chunks) >= 1
+        from_memory = sb.SileroVad(lf.inner.ctx, vw).process(audio)
+        assert np.array_equal(from_file, from_memory)
+    finally:
+        lf.inner.ctx.close()
