@@ -10,8 +10,8 @@
 //                       LSTM gates (W_ih e + b_ih + b_hh), written as 512 floats per window;
 //   vad_lstm_kernel     the recurrence, one thread-block cluster for the whole recording: the 512 x 128
 //                       recurrent matrix stays in the registers of the cluster's CTAs (it is as large as one SM's
-//                       register file, hence several SMs), the hidden vector is exchanged through distributed
-//                       shared memory, one cluster barrier per window;
+//                       register file, hence several SMs), the hidden vector goes from SM to SM through
+//                       distributed shared memory, its arrival counted by an mbarrier at the destination;
 //   vad_prob_kernel     ReLU, the 128 -> 1 output layer and the sigmoid, a warp per window.
 //
 // All arithmetic is fp32.
@@ -337,8 +337,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
 // Exchange of the hidden vector: two buffers of 128 floats per CTA, used in turn, each with an mbarrier.  In
 // step s the CTA collects its units' new h in shared memory; after the CTA barrier warp 0 sends them to buffer
 // (s + 1) & 1 of every CTA of the cluster with one st.async instruction (32 / C lanes of 16 bytes per
-// destination: the fewer, larger packets cross between SMs, the shorter the step), each store adding its bytes to
-// the destination's transaction count; a CTA starts step s + 1 when its barrier has counted all 512 bytes.  Nobody
+// destination), each store adding its bytes to the destination's transaction count; a CTA starts step s + 1 when its barrier has counted all 512 bytes.  Nobody
 // can run two steps ahead of anybody (a step needs every CTA's output of the step before), so two buffers are
 // enough and no thread can miss a phase.  Every wait is bounded: a CTA in which a wait gave up raises *error and
 // leaves the loop as a whole (the verdict goes through the CTA barrier), which stops the others' input, so they
