@@ -325,10 +325,6 @@ int32_t sb_ctx_set_option(sb_ctx* c, const char* name, int64_t value) {
     }
     else if (n == "vad_unstreamed") c->vad_unstreamed = value != 0;
     else if (n == "vad_rows_cap") c->vad_rows_cap = value < 0 ? 0 : value;
-    else if (n == "vad_row_threads") {
-        if (value != 2 && value != 4) return fail(SB_INVALID_ARGUMENT, "vad_row_threads must be 2 or 4");
-        c->vad_row_threads = (int)value;
-    }
     else if (n == "vad_cluster") {
         if (value != 4 && value != 8) return fail(SB_INVALID_ARGUMENT, "vad_cluster must be 4 or 8");
         c->vad_cluster = (int)value;

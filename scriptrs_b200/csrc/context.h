@@ -78,7 +78,6 @@ struct sb_ctx {
     std::vector<cudaEvent_t> vad_events;    // three per pass, plus one that orders the passes after earlier work
     int64_t vad_rows_cap = 0;              // streamed VAD mode: encoder frames kept for one decoder run (0 = sized from the recording)
     bool vad_unstreamed = false;           // VAD mode: run the whole network before the first transcription kernel (tests)
-    int vad_row_threads = 2;      // threads that share one row of the recurrent matrix (2 or 4)
     int vad_segment_windows = 131072;  // windows per pass of the VAD network (268 MB of gate inputs)
     sb::Profiler prof;
     bool fp8 = false;             // FP8 e4m3 GEMMs in the Conformer blocks (needs fp8 weights)

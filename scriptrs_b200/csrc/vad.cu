@@ -290,11 +290,10 @@ __device__ __forceinline__ uint32_t cluster_addr(uint32_t local, uint32_t rank) 
     return r;
 }
 
-// 16-byte store into another CTA's shared memory that, once it has landed, counts 16 bytes on that CTA's mbarrier
-__device__ __forceinline__ void store_remote_tx(uint32_t remote_data, float4 v, uint32_t remote_mbar) {
-    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(
-                     remote_data),
-                 "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(remote_mbar)
+// 4-byte store into another CTA's shared memory that, once it has landed, counts 4 bytes on that CTA's mbarrier
+__device__ __forceinline__ void store_remote_tx(uint32_t remote_data, float v, uint32_t remote_mbar) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(remote_data),
+                 "r"(__float_as_uint(v)), "r"(remote_mbar)
                  : "memory");
 }
 
@@ -330,52 +329,52 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
 }
 
 // The recurrence over the n windows of a pass.  A cluster of C CTAs; CTA r owns hidden units [r U, r U + U),
-// U = 128 / C, i.e. gate rows' [4 r U, 4 (r + 1) U) of the permuted matrices.  P threads per row, each with 128 / P
-// columns of the row in registers; the 4 P lanes of a unit (4 gates x P parts) sit next to each other in a warp
-// and all of them end a step holding the unit's new h.
+// U = 128 / C, i.e. gate rows' [4 r U, 4 (r + 1) U) of the permuted matrices.  Two threads per row, each with half
+// of the row's columns in registers; the 8 lanes of a unit (4 gates x 2 halves) sit next to each other in a warp
+// and all of them end a step holding the unit's new h, so a warp holds 4 units.
 //
-// Exchange of the hidden vector: two buffers of 128 floats per CTA, used in turn, each with an mbarrier.  In
-// step s the CTA collects its units' new h in shared memory; after the CTA barrier warp 0 sends them to buffer
-// (s + 1) & 1 of every CTA of the cluster with one st.async instruction (32 / C lanes of 16 bytes per
-// destination), each store adding its bytes to the destination's transaction count; a CTA starts step s + 1 when its barrier has counted all 512 bytes.  Nobody
-// can run two steps ahead of anybody (a step needs every CTA's output of the step before), so two buffers are
-// enough and no thread can miss a phase.  Every wait is bounded: a CTA in which a wait gave up raises *error and
-// leaves the loop as a whole (the verdict goes through the CTA barrier), which stops the others' input, so they
-// give up too, and all meet at the closing cluster barrier.
-template <int C, int P>
-__global__ void __launch_bounds__(P * kVadGates / C, 1)
+// Exchange of the hidden vector: two buffers of 128 floats per CTA, used in turn, each with an mbarrier.  After
+// step s lane j < C of a unit stores the unit's h (4 bytes) into buffer (s + 1) & 1 of CTA j with st.async, which
+// adds 4 bytes to that CTA's transaction count: one instruction per warp, 128 small packets per CTA and step
+// (gathering a warp's four units into one 16-byte store, or a CTA's units into one store per destination behind
+// a CTA barrier, costs more in shuffles and barriers than the fewer packets save: 43.5 and 46.7 ms per hour of
+// audio against 41.8).  A warp starts step s + 1 when its CTA's barrier has counted all 512 bytes.  There is no
+// barrier among the warps of a CTA inside the loop.  A warp can be at most one step ahead of any other warp of
+// the cluster (a step needs everybody's output of the step before), so two buffers are enough, nothing is
+// overwritten while it is still read, and no warp can miss a phase.  Every wait is bounded: a warp whose wait gave
+// up raises *error and leaves the loop, which stops the others' input, so they give up too, and all meet at the
+// closing cluster barrier.
+template <int C>
+__global__ void __launch_bounds__(2 * kVadGates / C, 1)
 vad_lstm_kernel(const float* __restrict__ gx, const float* __restrict__ whh, float* __restrict__ state,
                 float* __restrict__ hout, int n, int* __restrict__ error) {
     constexpr int kRows = kVadGates / C;  // gate rows of this CTA
     constexpr int kUnits = kVadState / C;
-    constexpr int kCols = kVadState / P;  // columns of a row per thread
-    constexpr int kUnitLanes = 4 * P;
+    constexpr int kThreads = 2 * kRows;
     constexpr int kDepth = 16;            // gate inputs are fetched this many windows ahead
-    constexpr int kThreads = P * kVadGates / C;
+    static_assert(C <= 8, "lane j < C sends to CTA j: one lane per unit lane");
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int tid = threadIdx.x, lane = tid & 31;
-    const int part = tid % P, row_local = tid / P, q = row_local & 3, unit_local = row_local >> 2;
+    const int part = tid & 1, row_local = tid >> 1, q = row_local & 3, unit_local = row_local >> 2;
     const int row = rank * kRows + row_local;
     const int unit = rank * kUnits + unit_local;
-    const int unit_lane = lane % kUnitLanes;
 
     __shared__ __align__(16) float hs[2][kVadState];
-    __shared__ __align__(16) float stage[kUnits];
     // Gate inputs on their way from global memory: slot s % kDepth holds step s's value for every thread.  They come
     // by cp.async, one group per step, because loads into registers this far ahead end up waiting for one another
     // (a warp has few scoreboards), which puts a DRAM round trip into every step.
     __shared__ float gring[kDepth][kThreads];
     __shared__ __align__(8) uint64_t mbar[2];
 
-    float2 w[kCols / 2];  // pairs, for the two-wide fp32 multiply-add
+    float2 w[32];  // pairs, for the two-wide fp32 multiply-add
     {
-        // thread `part` of a row holds the 16-byte column chunks part, part + P, ...: the P lanes of a row read
+        // thread `part` of a row holds the 16-byte column chunks part, part + 2, ...: the two lanes of a row read
         // neighbouring chunks of h, which lie in different banks
         const float4* src = reinterpret_cast<const float4*>(whh + (size_t)row * kVadState) + part;
 #pragma unroll
-        for (int k = 0; k < kCols / 4; ++k) {
-            const float4 v = __ldg(src + k * P);
+        for (int k = 0; k < 16; ++k) {
+            const float4 v = __ldg(src + 2 * k);
             w[2 * k] = make_float2(v.x, v.y);
             w[2 * k + 1] = make_float2(v.z, v.w);
         }
@@ -392,10 +391,10 @@ vad_lstm_kernel(const float* __restrict__ gx, const float* __restrict__ whh, flo
         if (n >= 1) mbar_expect_tx(mbar1, kVadState * 4);
         if (n >= 2) mbar_expect_tx(mbar0, kVadState * 4);
     }
-    // warp 0 sends: lane = destination CTA * (32 / C) + piece, a piece being four of this CTA's units
-    constexpr int kPieces = kUnits / 4;  // = 32 / C
-    const uint32_t dst_rank = lane / kPieces, piece = lane % kPieces;
-    const uint32_t dst_h = cluster_addr(smem_u32(&hs[0][rank * kUnits + 4 * piece]), dst_rank);
+    // lane j < C of a unit's eight lanes sends the unit's h to CTA j
+    const int unit_lane = lane & 7;
+    const uint32_t dst_rank = unit_lane < C ? unit_lane : 0;
+    const uint32_t dst_h = cluster_addr(smem_u32(&hs[0][unit]), dst_rank);
     const uint32_t dst_mbar0 = cluster_addr(mbar0, dst_rank), dst_mbar1 = cluster_addr(mbar1, dst_rank);
 
     const float* gx_row = gx + row;
@@ -414,7 +413,7 @@ vad_lstm_kernel(const float* __restrict__ gx, const float* __restrict__ whh, flo
     // the cell candidate (gate 2) is a tanh: 2 / (1 + e^(-2 x)) - 1; the other gates are logistic
     const float gate_k = q == 2 ? 2.0f * kNegLog2e : kNegLog2e;
     const float gate_mul = q == 2 ? 2.0f : 1.0f, gate_add = q == 2 ? -1.0f : 0.0f;
-    const int base = lane - unit_lane;
+    const int base = lane & ~7;
     bool alive = true;
     for (int s = 0; s < n; ++s) {
         const int cur = s & 1;
@@ -422,43 +421,38 @@ vad_lstm_kernel(const float* __restrict__ gx, const float* __restrict__ whh, flo
         asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory");
         const float gxv = gring[s % kDepth][tid];
         fetch(s + kDepth);
-        bool ok = true;
-        if (s > 0) {
-            ok = mbar_wait(cur ? mbar1 : mbar0, (uint32_t)((s - 1) >> 1) & 1u);
-            // this buffer's next phase: the input of step s + 2
-            if (tid == 0 && ok && s + 2 <= n) mbar_expect_tx(cur ? mbar1 : mbar0, kVadState * 4);
-        }
+        const bool ok = s == 0 || mbar_wait(cur ? mbar1 : mbar0, (uint32_t)((s - 1) >> 1) & 1u);
         const float4* hv = reinterpret_cast<const float4*>(&hs[cur][0]) + part;
         float2 a0 = make_float2(0.0f, 0.0f), a1 = a0, a2 = a0, a3 = a0;
 #pragma unroll
-        for (int k = 0; k < kCols / 4; k += 2) {
-            const float4 u = hv[k * P], v = hv[(k + 1) * P];
+        for (int k = 0; k < 16; k += 2) {
+            const float4 u = hv[2 * k], v = hv[2 * k + 2];
             a0 = __ffma2_rn(w[2 * k], make_float2(u.x, u.y), a0);
             a1 = __ffma2_rn(w[2 * k + 1], make_float2(u.z, u.w), a1);
             a2 = __ffma2_rn(w[2 * k + 2], make_float2(v.x, v.y), a2);
             a3 = __ffma2_rn(w[2 * k + 3], make_float2(v.z, v.w), a3);
         }
         float pre = ((a0.x + a0.y) + (a1.x + a1.y)) + ((a2.x + a2.y) + (a3.x + a3.y));
-#pragma unroll
-        for (int o = 1; o < P; o <<= 1) pre += __shfl_xor_sync(0xffffffffu, pre, o);
+        pre += __shfl_xor_sync(0xffffffffu, pre, 1);
         pre += gxv;
         const float act = fmaf(gate_mul, logistic_pow2(pre, gate_k), gate_add);
         const float gi = __shfl_sync(0xffffffffu, act, base);
-        const float gf = __shfl_sync(0xffffffffu, act, base + P);
-        const float gg = __shfl_sync(0xffffffffu, act, base + 2 * P);
-        const float go = __shfl_sync(0xffffffffu, act, base + 3 * P);
+        const float gf = __shfl_sync(0xffffffffu, act, base + 2);
+        const float gg = __shfl_sync(0xffffffffu, act, base + 4);
+        const float go = __shfl_sync(0xffffffffu, act, base + 6);
         c = fmaf(gf, c, gi * gg);
         h = go * fmaf(2.0f, logistic_pow2(c, 2.0f * kNegLog2e), -1.0f);
-        if (unit_lane == 0) stage[unit_local] = h;
-        alive = __syncthreads_and(ok);  // the CTA's h values are staged; and did every wait of the CTA succeed?
+        if (unit_lane < C) store_remote_tx(dst_h + (uint32_t)((cur ^ 1) * kVadState * 4), h, cur ? dst_mbar0 : dst_mbar1);
+        if (unit_lane == 0) hout[(size_t)s * kVadState + unit] = h;
+        // Everything that is not on the path from the others' h to this warp's h comes after the send.  The buffer
+        // just read is armed for its next phase, the input of step s + 2 (its bytes cannot be complete before this
+        // CTA has sent step s + 1, and bytes that arrive before the arming are counted all the same).  And a wait
+        // that gave up ends the warp's loop only here: the arithmetic ran on stale input and the result is void.
+        if (tid == 0 && ok && s > 0 && s + 2 <= n) mbar_expect_tx(cur ? mbar1 : mbar0, kVadState * 4);
+        alive = __all_sync(0xffffffffu, ok);
         if (!alive) {
-            if (!ok) *error = 1;
+            *error = 1;
             break;
-        }
-        if (tid < 32) {
-            const float4 v = reinterpret_cast<const float4*>(stage)[piece];
-            store_remote_tx(dst_h + (uint32_t)((cur ^ 1) * kVadState * 4), v, cur ? dst_mbar0 : dst_mbar1);
-            if (tid < kPieces) *reinterpret_cast<float4*>(hout + (size_t)s * kVadState + rank * kUnits + 4 * tid) = v;
         }
     }
     // the output of the last step is in flight to every CTA's shared memory: wait for it before anyone exits
@@ -487,11 +481,11 @@ __global__ void vad_prob_kernel(const float* __restrict__ hout, const float* __r
 
 constexpr size_t kEncSmem = 2 * kRegionFloats * sizeof(float);
 
-template <int C, int P>
+template <int C>
 cudaError_t launch_lstm(const float* gx, const float* whh, float* state, float* hout, int n, int* error, cudaStream_t st) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(C);
-    cfg.blockDim = dim3(P * kVadGates / C);
+    cfg.blockDim = dim3(2 * kVadGates / C);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -501,7 +495,7 @@ cudaError_t launch_lstm(const float* gx, const float* whh, float* state, float* 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, vad_lstm_kernel<C, P>, gx, whh, state, hout, n, error);
+    return cudaLaunchKernelEx(&cfg, vad_lstm_kernel<C>, gx, whh, state, hout, n, error);
 }
 
 const sb_tensor* find(const sb_tensor* t, int64_t n, const std::string& name) {
@@ -647,13 +641,8 @@ int32_t vad_recur_pass(sb_ctx* c, cudaStream_t st, int64_t first, int n, int buf
     VadModel& m = *c->vad;
     c->prof.begin("vad_lstm", st);
     float *gxp = m.gx[buf].as<float>(), *stp = m.state.as<float>(), *hop = m.hout.as<float>();
-    cudaError_t e;
-    if (c->vad_cluster == 4)
-        e = c->vad_row_threads == 4 ? launch_lstm<4, 4>(gxp, m.whh, stp, hop, n, c->d_error, st)
-                                    : launch_lstm<4, 2>(gxp, m.whh, stp, hop, n, c->d_error, st);
-    else
-        e = c->vad_row_threads == 4 ? launch_lstm<8, 4>(gxp, m.whh, stp, hop, n, c->d_error, st)
-                                    : launch_lstm<8, 2>(gxp, m.whh, stp, hop, n, c->d_error, st);
+    cudaError_t e = c->vad_cluster == 4 ? launch_lstm<4>(gxp, m.whh, stp, hop, n, c->d_error, st)
+                                        : launch_lstm<8>(gxp, m.whh, stp, hop, n, c->d_error, st);
     c->prof.end(st);
     SB_CUDA(e);
     c->prof.begin("vad_prob", st);
