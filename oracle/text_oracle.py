@@ -8,12 +8,14 @@ Restates, for small cases, the reference's
   Vocabulary::from_file           src/vocab.rs:15-52
   join_token_text / build_chunk / build_result   src/long_form.rs:602-647
 Pinned by the reference's known-answer tests decode.rs:151-179.
-`str.isalpha()` plus the letter-number category Nl stands in for Rust's `char::is_alphabetic`
-(Rust additionally counts the Other_Alphabetic marks, which the standard library does not expose).
+Rust's `char::is_alphabetic` is the Unicode derived property Alphabetic; the `regex` package's `\\p{Alphabetic}`
+(Unicode 17.0 tables) stands in for it here.
 """
 from __future__ import annotations
 
-import unicodedata
+import regex
+
+_ALPHABETIC = regex.compile(r"\p{Alphabetic}")
 
 SECONDS_PER_FRAME = 1280 / 16000
 
@@ -57,7 +59,7 @@ def needs_digit_spacing(existing: str, display: str) -> bool:
         return False
     trailing = 0
     for ch in reversed(existing):
-        if ch.isalpha() or unicodedata.category(ch) == "Nl":
+        if _ALPHABETIC.match(ch):
             trailing += 1
         else:
             break

@@ -5,10 +5,9 @@
 //   is_special_token                src/decode.rs:110-112
 //   needs_digit_spacing             src/decode.rs:114-134
 //   join_token_text / build_chunk / build_result   src/long_form.rs:602-647
-// Strings are UTF-8.  `char::is_alphabetic` is evaluated from a generated table of all code points of the
-// Unicode general categories L* and Nl (unicode_alpha_table.h, written by make_alpha_table.py).  Rust's
-// property also includes Other_Alphabetic (combining vowel signs and the like); those few marks count as
-// non-alphabetic here.
+// Strings are UTF-8.  `char::is_alphabetic` is the Unicode derived property Alphabetic; it is evaluated from a
+// generated table of that property's code-point ranges (unicode_alpha_table.h, written by make_alpha_table.py from
+// Unicode 17.0 tables; a Rust toolchain on an older Unicode version differs only on code points assigned later).
 #include <algorithm>
 #include <cstdio>
 #include <fstream>

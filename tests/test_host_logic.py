@@ -141,12 +141,14 @@ def test_text_decode_known_answers():
 
 
 # letters from well outside Latin: Thai above U+0E30, a Hebrew presentation form, Latin Extended-D, a Roman numeral
-# (category Nl), Cherokee, a supplementary-plane letter, and a non-letter symbol
+# (category Nl), Cherokee, a supplementary-plane letter, a non-letter symbol; and Other_Alphabetic marks, which are
+# alphabetic without being letters: a Devanagari vowel sign (Mc), a Hebrew point (Mn), a circled letter (So), and a
+# combining accent that is NOT alphabetic (U+0301)
 VOCAB = ["▁the", "▁a", "a", "s", "1", "23", "▁", "<unk>", "<pad>", "é", "▁Ünï", "ß", "", "x1", "▁4", "<blk>",
-         "ไ", "\ufb2a", "\ua7b5", "\u2167", "\u13a0", "\U00010400", "\u2603", "7"]
+         "ไ", "\ufb2a", "\ua7b5", "\u2167", "\u13a0", "\U00010400", "\u2603", "7", "\u093e", "\u05b0", "\u24b6", "\u0301"]
 
 
-@given(st.lists(st.tuples(st.integers(0, 25), st.integers(0, 6)), max_size=25), st.floats(0.0, 40.0))
+@given(st.lists(st.tuples(st.integers(0, 29), st.integers(0, 6)), max_size=25), st.floats(0.0, 40.0))
 @settings(max_examples=120, deadline=None)
 def test_text_decode_matches_oracle(items, duration):
     tok = [t for t, _ in items]
@@ -171,3 +173,21 @@ def test_long_form_finish_builds_the_region_chunk():
     assert r.duration_seconds == 30.0
     empty = sb.longform_finish(vocab, 16000, [raw([], [])])
     assert empty.text == "" and empty.chunks == [] and empty.tokens == []
+
+
+def test_alphabetic_table_is_the_unicode_derived_property():
+    """needs_digit_spacing (src/decode.rs:114-134) asks char::is_alphabetic: a digit token gets a space in front when
+    two or more alphabetic characters end the text so far.  Probed through the text decoder for every kind of
+    character the general categories alone would get wrong."""
+    import regex
+
+    alpha = regex.compile(r"\p{Alphabetic}")
+    probes = ["\u0345", "\u05b0", "\u093e", "\u0903", "\u24b6", "\u2167", "\u0301", "\u20e3", "\u2603", "\u1885",
+              "\U0001e947", "\U00016f51", "\u0e31", "\u0e47"]
+    for ch in probes:
+        vocab = ["x" + ch, "7", "<blk>"]
+        r = sb.ParakeetTdtDecoder(sb.Vocabulary.from_tokens(vocab)).decode(raw([0, 1], [0, 2]), 1.0)
+        want = "x" + ch + (" 7" if alpha.match(ch) else "7")
+        assert r.text == want, (hex(ord(ch)), r.text)
+        o = text_oracle.decode(vocab, [0, 1], [0, 2], [0.9, 0.9], 1.0)
+        assert o["text"] == want
