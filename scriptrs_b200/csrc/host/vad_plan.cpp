@@ -137,8 +137,9 @@ void SpeechRegionStream::finish() {
 
 std::vector<sb_sample_range> detect_speech_regions(const float* prob, int64_t n_prob, int64_t audio_len, float threshold,
                                                    const sb_vad_segmentation_config& cfg) {
+    // fed in pieces, the way the streamed mode feeds it pass by pass (the result does not depend on the pieces)
     SpeechRegionStream stream(audio_len, threshold, cfg);
-    if (n_prob > 0) stream.push(prob, n_prob);
+    for (int64_t at = 0; at < n_prob; at += 1000) stream.push(prob + at, std::min<int64_t>(1000, n_prob - at));
     stream.finish();
     return stream.regions();
 }
