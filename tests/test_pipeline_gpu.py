@@ -143,6 +143,12 @@ def test_pieced_host_copy_equals_resident_path(ctx, pipe):
     dev = sb.transcribe_chunks(ctx, None, tasks, audio_ptr=d_audio.data_ptr(), n_samples=audio.size, on_device=True)
     for x, y in zip(host.flat(), dev.flat()):
         assert np.array_equal(x, y)
+    # 64 to 511 tasks go up in two pieces (what a GPU sees of an 8 h recording shared by eight)
+    some = tasks[100:300]
+    host2 = sb.transcribe_chunks(ctx, audio, some)
+    for k in range(len(some)):
+        assert np.array_equal(host2[k].token_ids, dev[100 + k].token_ids)
+        assert np.array_equal(host2[k].frame_indices, dev[100 + k].frame_indices)
     # unordered tasks fall back to one copy and must still give each task its own result
     perm = list(reversed(range(n_tasks)))
     shuffled = sb.transcribe_chunks(ctx, audio, [tasks[i] for i in perm])
