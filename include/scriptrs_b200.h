@@ -459,7 +459,10 @@ int32_t sb_longform_run(sb_ctx* ctx, const sb_vocab* vocab, const float* audio, 
 /* The same over several GPUs of one process: run_parallel_regions (src/long_form.rs:266-314) with
  * min(worker_count, n_ctx, tasks) workers, each worker being one context's GPU with its own host
  * thread; tasks are dealt in contiguous blocks and results are reassembled in task order
- * (src/long_form.rs:316-342).  The first failing worker fails the call. */
+ * (src/long_form.rs:316-342).  The first failing worker fails the call.  In mode 1 the first context runs the VAD
+ * network (one recurrence per recording: it does not shard); with one worker its passes run beside the
+ * transcription of the regions already found, with several the whole network runs first, as in the reference
+ * (src/long_form.rs:188-216). */
 int32_t sb_longform_run_multi(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const float* audio,
                               int64_t n_samples, const sb_longform_config* cfg, sb_result** out);
 
