@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(kEncThreads, 2) vad_encode_kernel(const Encode
 #pragma unroll
             for (int t = 0; t < 4; ++t) re[j][t] = im[j][t] = 0.0f;
         const float* xs = r0 + w * kXsStride;
-#pragma unroll 2
+#pragma unroll 4
         for (int n = 0; n < kVadFilter; n += 4) {
             float4 a[4];
 #pragma unroll
@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(kEncThreads, 2) vad_encode_kernel(const Encode
 #pragma unroll
                 for (int t = 0; t < 4; ++t) acc[j][t] = b[j];
         }
+#pragma unroll 3
         for (int ci = 0; ci < kVadBins; ++ci) {
             const float2* mp = reinterpret_cast<const float2*>(r1 + ci * (kTileWindows * kT1) + w * kT1);
             const float2 m01 = mp[0], m23 = mp[1], m45 = mp[2];
