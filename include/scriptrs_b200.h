@@ -157,6 +157,7 @@ int64_t sb_ctx_kernel_launches(const sb_ctx* ctx);
  * "vad_unstreamed" (0/1): in the VAD long-form mode run the whole voice-activity network before the first
  * transcription kernel instead of beside the transcription; "vad_rows_cap" (default 0 = sized from the recording): encoder
  * frames the streamed VAD mode keeps before it runs the decoder over them (more tasks than fit are decoded in rounds);
+ * "vad_stream_pass_windows" (default 49152): largest pass of the network in the streamed VAD mode;
  * "vad_cluster" (4 or 8, default 8): thread blocks in the cluster that runs the VAD network's recurrence;
  * "vad_segment_windows" (default 131072): windows the VAD network processes per pass (its work buffers hold 2560 bytes
  * per window; the recurrent state is carried from pass to pass);

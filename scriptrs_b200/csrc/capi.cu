@@ -324,6 +324,10 @@ int32_t sb_ctx_set_option(sb_ctx* c, const char* name, int64_t value) {
         c->vad_segment_windows = (int)value;
     }
     else if (n == "vad_unstreamed") c->vad_unstreamed = value != 0;
+    else if (n == "vad_stream_pass_windows") {
+        if (value < 1 || value > (1 << 22)) return fail(SB_INVALID_ARGUMENT, "vad_stream_pass_windows must be in [1, 4194304]");
+        c->vad_stream_pass_windows = (int)value;
+    }
     else if (n == "vad_rows_cap") c->vad_rows_cap = value < 0 ? 0 : value;
     else if (n == "vad_cluster") {
         if (value != 4 && value != 8) return fail(SB_INVALID_ARGUMENT, "vad_cluster must be 4 or 8");

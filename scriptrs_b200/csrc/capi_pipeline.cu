@@ -681,17 +681,17 @@ int32_t run_vad_plan(sb_ctx** ctxs, int64_t n_ctx, const sb_vocab* vocab, const 
 // recurrence of the network occupies one 8-CTA cluster for as long as the rest of the GPU needs to transcribe a
 // comparable stretch of audio, so the host plans the regions that pass k made final (SpeechRegionStream) and
 // sends their tasks through the frontend and the encoder on the context's stream while pass k + 1 runs beside
-// them.  Passes start short (the first one is exposed) and double up to 32768 windows (or "vad_segment_windows", if smaller).  The decoder runs
+// them.  Passes start short (the first one is exposed) and double up to "vad_stream_pass_windows" (or "vad_segment_windows", if smaller).  The decoder runs
 // once at the end.  Regions, tasks and results equal those of the unstreamed path.
 int32_t run_vad_streamed(sb_ctx* c, const sb_vocab* vocab, const float* audio, int64_t n_samples,
                          const sb_longform_config& lc, sb_result** out) {
     VadModel& m = *c->vad;
     SB_CUDA(cudaSetDevice(c->device));
     const int64_t n_win = sb_vad_num_windows(n_samples);
-    // passes of 8192, 16384, then 32768 windows (17 minutes of audio; measured on an 8 h recording: longer passes
-    // leave a longer stretch to transcribe after the last recurrence, shorter ones make the pieces' kernels small;
-    // shorter passes at the end as well changed nothing, the recurrences being the critical path)
-    const int64_t pass_cap = std::min<int64_t>(c->vad_segment_windows, 32768);
+    // passes of 8192, 16384, 32768, then 49152 windows (26 minutes of audio; measured on an 8 h recording with 76 % sound,
+    // largest pass 131072 / 65536 / 49152 / 32768 / 24576 windows: 456 / 425 / 422 / 433 / 472 ms: longer passes leave a
+    // longer stretch to transcribe after the last recurrence, shorter ones make the pieces' kernels small)
+    const int64_t pass_cap = std::min<int64_t>(c->vad_segment_windows, c->vad_stream_pass_windows);
     std::vector<int64_t> cut{0};  // pass boundaries, in windows
     for (int64_t w = 8192; cut.back() < n_win; w = std::min<int64_t>(2 * w, pass_cap))
         cut.push_back(std::min(n_win, cut.back() + std::min<int64_t>(w, pass_cap)));

@@ -76,6 +76,7 @@ struct sb_ctx {
     cudaStream_t vad_stream = nullptr;       // high priority: the VAD network's recurrences beside the transcription
     cudaStream_t vad_feed_stream = nullptr;  // sample copies and gate inputs of the pass after the one that recurs
     std::vector<cudaEvent_t> vad_events;    // three per pass, plus one that orders the passes after earlier work
+    int vad_stream_pass_windows = 49152;   // streamed VAD mode: largest pass (26 minutes of audio)
     int64_t vad_rows_cap = 0;              // streamed VAD mode: encoder frames kept for one decoder run (0 = sized from the recording)
     bool vad_unstreamed = false;           // VAD mode: run the whole network before the first transcription kernel (tests)
     int vad_segment_windows = 131072;  // windows per pass of the VAD network (268 MB of gate inputs)
