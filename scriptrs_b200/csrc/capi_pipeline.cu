@@ -588,9 +588,10 @@ int32_t sb_longform_finish(const sb_vocab* vocab, int64_t audio_len, const uint3
     OverlapMerger m;
     for (int64_t w = 0; w < n_windows; ++w) m.push(raw_from_arrays(tok, frm, dur, conf, win_off[w], win_off[w + 1]));
     // long_form.rs:404-419: decode the merged stream against the whole recording's duration
-    TranscriptionResult merged = decode_tokens(vocab->v, m.merged(), (double)audio_len / 16000.0);
+    std::string joined;
+    TranscriptionResult merged = decode_tokens(vocab->v, m.merged(), (double)audio_len / 16000.0, &joined);
     sb_result* res = new sb_result();
-    res->r = long_form_result(std::move(merged.tokens), audio_len);
+    res->r = long_form_result(std::move(merged.tokens), joined, audio_len);
     *out = res;
     return SB_OK;
 }

@@ -81,6 +81,13 @@ ExecutionPlan build_fast_plan(int64_t audio_len, const sb_longform_config& cfg);
 struct Vocabulary {
     std::vector<std::string> id_to_token;
     int64_t blank_id = 0;
+    // what the text decoder needs of every token, worked out once when the vocabulary is read
+    struct Shown {
+        std::string display;  // the token with the word-boundary mark turned into a space (decode.rs:64)
+        bool special;         // <...> other than <unk> (decode.rs:110-112)
+        bool digits;          // only ASCII digits (true for the empty token, as in the reference)
+    };
+    std::vector<Shown> shown;
 };
 
 struct TimedToken {
@@ -108,10 +115,13 @@ std::string vocabulary_from_file(const std::string& path, Vocabulary* out, bool*
 std::string vocabulary_from_text(const std::string& text, Vocabulary* out);
 // str::trim (Unicode White_Space) as join_token_text applies it, long_form.rs:613-620
 std::string trim_whitespace(const std::string& s);
-// decode.rs:39-104
-TranscriptionResult decode_tokens(const Vocabulary& vocab, const RawTokens& raw, double duration_seconds);
-// long_form.rs:344-374,602-647 for the single Overlap region of the Fast mode
-TranscriptionResult long_form_result(std::vector<TimedToken> tokens, int64_t audio_len);
+// decode.rs:39-104.  untrimmed, if not null, receives the text before its final trim (the concatenation of the
+// token texts, which is what the long-form chunks are rebuilt from, long_form.rs:613-620).
+TranscriptionResult decode_tokens(const Vocabulary& vocab, const RawTokens& raw, double duration_seconds,
+                                  std::string* untrimmed = nullptr);
+// long_form.rs:344-374,602-647 for the single Overlap region of the Fast mode; `joined` is the concatenation of the
+// tokens' texts (decode_tokens' untrimmed text)
+TranscriptionResult long_form_result(std::vector<TimedToken> tokens, const std::string& joined, int64_t audio_len);
 // long_form.rs:344-419,602-661: the result of an execution plan from its tasks' token streams (raw[i] is consumed)
 TranscriptionResult build_plan_result(const Vocabulary& vocab, int64_t audio_len, const sb_chunk_task* tasks,
                                       const sb_region_task* regions, int64_t n_regions, std::vector<RawTokens>& raw);

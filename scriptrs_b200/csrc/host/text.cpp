@@ -91,10 +91,9 @@ bool is_special_token(const std::string& t) {
     return !t.empty() && t.front() == '<' && t.back() == '>' && t != "<unk>";
 }
 
-bool needs_digit_spacing(const std::string& existing, const std::string& display) {
-    if (existing.empty() || (!display.empty() && display[0] == ' ')) return false;
-    for (char ch : display)
-        if (ch < '0' || ch > '9') return false;  // vacuously true for an empty token, as in the reference
+// needs_digit_spacing (decode.rs:114-134) for a display string known to hold only digits and no leading space
+bool digits_need_space(const std::string& existing) {
+    if (existing.empty()) return false;
     size_t trailing = 0, end = existing.size();
     while (end > 0) {
         uint32_t cp;
@@ -152,6 +151,14 @@ std::string vocabulary_from_text(const std::string& text, Vocabulary* out) {
     }
     if (out->id_to_token.empty()) return "vocabulary was empty";
     out->blank_id = have_blank ? blank : static_cast<int64_t>(out->id_to_token.size()) - 1;
+    out->shown.clear();
+    out->shown.reserve(out->id_to_token.size());
+    for (const std::string& tok : out->id_to_token) {
+        Vocabulary::Shown sh{replace_underline(tok), is_special_token(tok), true};
+        for (char ch : sh.display)
+            if (ch < '0' || ch > '9') sh.digits = false;
+        out->shown.push_back(std::move(sh));
+    }
     return "";
 }
 
@@ -164,43 +171,49 @@ std::string vocabulary_from_file(const std::string& path, Vocabulary* out, bool*
     return vocabulary_from_text(ss.str(), out);
 }
 
-TranscriptionResult decode_tokens(const Vocabulary& vocab, const RawTokens& raw, double duration_seconds) {
+TranscriptionResult decode_tokens(const Vocabulary& vocab, const RawTokens& raw, double duration_seconds,
+                                  std::string* untrimmed) {
     TranscriptionResult res;
     res.duration_seconds = duration_seconds;
+    if (untrimmed) untrimmed->clear();
     if (raw.token_ids.empty()) return res;
     std::string text;
     res.tokens.reserve(raw.token_ids.size());
     text.reserve(raw.token_ids.size() * 4);
-    for (size_t index = 0; index < raw.token_ids.size(); ++index) {
+    const size_t n = raw.token_ids.size();
+    for (size_t index = 0; index < n; ++index) {
         const uint32_t id = raw.token_ids[index];
-        if (id >= vocab.id_to_token.size()) continue;
-        const std::string& tok = vocab.id_to_token[id];
-        if (is_special_token(tok)) continue;
+        if (id >= vocab.shown.size()) continue;
+        const Vocabulary::Shown& sh = vocab.shown[id];
+        if (sh.special) continue;
         const double start = frame_to_seconds(raw.frame_indices[index]);
         double end;
-        if (index + 1 < raw.frame_indices.size()) end = frame_to_seconds(raw.frame_indices[index + 1]);
+        if (index + 1 < n) end = frame_to_seconds(raw.frame_indices[index + 1]);
         else end = std::min(start + kSecondsPerFrame, duration_seconds);
-        std::string display = replace_underline(tok);
-        if (needs_digit_spacing(text, display)) display.insert(display.begin(), ' ');
-        text += display;
         const float conf = index < raw.confidences.size() ? raw.confidences[index] : 0.0f;
-        res.tokens.push_back(TimedToken{id, std::move(display), start, end, conf});
+        // a digit token directly after a word gets a space in front (decode.rs:66-68)
+        if (sh.digits && digits_need_space(text)) {
+            text += ' ';
+            text += sh.display;
+            res.tokens.push_back(TimedToken{id, " " + sh.display, start, end, conf});
+        } else {
+            text += sh.display;
+            res.tokens.push_back(TimedToken{id, sh.display, start, end, conf});
+        }
     }
     res.text = trim(text);
     if (!res.text.empty() && !res.tokens.empty())
         res.chunks.push_back(TranscriptChunk{res.tokens.front().start, res.tokens.back().end, res.text});
+    if (untrimmed) *untrimmed = std::move(text);
     return res;
 }
 
 std::string trim_whitespace(const std::string& s) { return trim(s); }
 
-TranscriptionResult long_form_result(std::vector<TimedToken> tokens, int64_t audio_len) {
+TranscriptionResult long_form_result(std::vector<TimedToken> tokens, const std::string& joined, int64_t audio_len) {
     TranscriptionResult res;
     res.duration_seconds = static_cast<double>(audio_len) / 16000.0;
     if (!tokens.empty()) {
-        std::string joined;
-        joined.reserve(tokens.size() * 4);
-        for (const auto& t : tokens) joined += t.text;
         res.chunks.push_back(TranscriptChunk{tokens.front().start, tokens.back().end, trim(joined)});
         res.tokens = std::move(tokens);
     }

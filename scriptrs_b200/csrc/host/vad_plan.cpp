@@ -218,10 +218,12 @@ TranscriptionResult build_plan_result(const Vocabulary& vocab, int64_t audio_len
     for (int64_t r = 0; r < n_regions; ++r) {
         const sb_region_task& rt = regions[r];
         std::vector<TimedToken> tokens;
+        std::string joined, part_text;  // the region's token texts, concatenated (join_token_text, long_form.rs:613-620)
         if (rt.kind == 1) {
             for (int64_t i = rt.first_task; i < rt.first_task + rt.n_tasks; ++i) {
                 const int64_t len = sat_sub(tasks[i].audio_end, tasks[i].audio_start);
-                TranscriptionResult part = decode_tokens(vocab, raw[(size_t)i], static_cast<double>(len) / kRate);
+                TranscriptionResult part = decode_tokens(vocab, raw[(size_t)i], static_cast<double>(len) / kRate, &part_text);
+                joined += part_text;
                 const double shift = static_cast<double>(tasks[i].audio_start) / kRate;
                 for (TimedToken& t : part.tokens) {
                     t.start += shift;
@@ -232,11 +234,9 @@ TranscriptionResult build_plan_result(const Vocabulary& vocab, int64_t audio_len
         } else {
             OverlapMerger m;
             for (int64_t i = rt.first_task; i < rt.first_task + rt.n_tasks; ++i) m.push(raw[(size_t)i]);
-            tokens = decode_tokens(vocab, m.merged(), res.duration_seconds).tokens;
+            tokens = decode_tokens(vocab, m.merged(), res.duration_seconds, &joined).tokens;
         }
         if (tokens.empty()) continue;  // build_chunk returns None
-        std::string joined;
-        for (const TimedToken& t : tokens) joined += t.text;
         res.chunks.push_back(TranscriptChunk{tokens.front().start, tokens.back().end, trim_whitespace(joined)});
         for (TimedToken& t : tokens) res.tokens.push_back(std::move(t));
     }
