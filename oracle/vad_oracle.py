@@ -16,7 +16,8 @@ Two parts:
   (src/long_form/vad.rs:61-98: 512-sample windows, 64 samples of context, last window filled with its last
   sample, zero initial state) around the public Silero VAD (16 kHz) network shape.  The reference keeps the
   network in a CoreML file that is not part of its repository, so the network arithmetic is PARITY UNPINNED:
-  there is no golden output to check it against, only the I/O contract of src/coreml.rs:188-236.
+  there is no golden output to check it against, only the I/O contract of src/coreml.rs:188-236 (and an independent
+  implementation of the same layers with torch, tests/test_oracle_vad.py).
 """
 from __future__ import annotations
 
