@@ -1,6 +1,7 @@
 """Pins the frontend oracle against the reference's own frontend tests
 (src/frontend.rs:243-301) and against the facts its source implies."""
 import numpy as np
+import pytest
 
 import oracle
 
@@ -69,3 +70,30 @@ def test_port_mode_stays_close_to_gold():
     g = oracle.frontend_extract(a)
     p = oracle.frontend_extract(a, port_f32=True)
     assert np.linalg.norm(g - p) / np.linalg.norm(g) < 1e-4
+
+
+@pytest.mark.parametrize("n,seed", [(16000 * 2 + 123, 11), (4321, 12), (161, 13)])
+def test_oracle_matches_library_stft_and_mel(n, seed):
+    """The same features assembled from independent library pieces: torch.stft (with the reference's framing: 256
+    zeros on either side, the 400-sample window at the START of each 512-sample frame, src/frontend.rs:121-147), the
+    Slaney filterbank of transformers.audio_utils, numpy's log, mean and standard deviation (n - 1, + 1e-5)."""
+    torch = pytest.importorskip("torch")
+    mel_filter_bank = pytest.importorskip("transformers.audio_utils").mel_filter_bank
+    from scriptrs_b200 import synth
+
+    a = synth.clip_audio(n, seed)
+    feats, raw, power = oracle.frontend_extract(a, want_raw=True, want_power=True)
+    x = torch.from_numpy(a)
+    pre = torch.cat([x[:1], x[1:] - 0.97 * x[:-1]]).double()
+    padded = torch.cat([torch.zeros(256, dtype=torch.float64), pre, torch.zeros(256, dtype=torch.float64)])
+    window = torch.cat([torch.from_numpy(oracle.hann_window(400)).double(), torch.zeros(112, dtype=torch.float64)])
+    spec = torch.stft(padded, n_fft=512, hop_length=160, win_length=512, window=window, center=False, return_complex=True)
+    p = (spec.real ** 2 + spec.imag ** 2).T.numpy()
+    assert p.shape == power.T.shape
+    assert np.abs(p - power.T).max() <= 1e-6 * np.abs(p).max()
+    lib_fb = mel_filter_bank(257, 128, 0.0, 8000.0, 16000, norm="slaney", mel_scale="slaney")   # [257, 128]
+    assert np.abs(lib_fb.T - oracle.mel_filterbank()).max() < 1e-8
+    logmel = np.log(p @ lib_fb + 2.0 ** -24)
+    assert np.abs(logmel - raw).max() < 2e-4          # f32 sums of 257 terms against f64
+    norm = (logmel - logmel.mean(0)) / (logmel.std(0, ddof=1) + 1e-5)
+    assert np.linalg.norm(norm - feats) <= 1e-5 * np.linalg.norm(feats)
