@@ -304,7 +304,7 @@ int32_t sb_merge_windows(const uint32_t* tok, const int64_t* frm, const int64_t*
                          float* oconf, int64_t out_cap, int64_t* n_out) {
     if (!win_off || !n_out || n_windows < 0) return fail(SB_INVALID_ARGUMENT, "null argument");
     OverlapMerger m;
-    for (int64_t w = 0; w < n_windows; ++w) m.push(raw_from_arrays(tok, frm, dur, conf, win_off[w], win_off[w + 1]));
+    for (int64_t w = 0; w < n_windows; ++w) m.push(RawView{tok + win_off[w], frm + win_off[w], dur + win_off[w], conf + win_off[w], (size_t)(win_off[w + 1] - win_off[w])});
     const RawTokens& r = m.merged();
     *n_out = (int64_t)r.token_ids.size();
     if (*n_out > out_cap) return fail(SB_BUFFER_TOO_SMALL, "merge output buffer too small");
@@ -586,7 +586,7 @@ int32_t sb_longform_finish(const sb_vocab* vocab, int64_t audio_len, const uint3
                            sb_result** out) {
     if (!vocab || !out || !win_off || n_windows < 0) return fail(SB_INVALID_ARGUMENT, "null argument");
     OverlapMerger m;
-    for (int64_t w = 0; w < n_windows; ++w) m.push(raw_from_arrays(tok, frm, dur, conf, win_off[w], win_off[w + 1]));
+    for (int64_t w = 0; w < n_windows; ++w) m.push(RawView{tok + win_off[w], frm + win_off[w], dur + win_off[w], conf + win_off[w], (size_t)(win_off[w + 1] - win_off[w])});
     // long_form.rs:404-419: decode the merged stream against the whole recording's duration
     std::string joined;
     TranscriptionResult merged = decode_tokens(vocab->v, m.merged(), (double)audio_len / 16000.0, &joined);

@@ -88,7 +88,7 @@ void apply_time_offsets(RawTokens& raw, int64_t frame_offset, int64_t context_fr
 }
 
 // ---------------------------------------------------------------------------- merge
-void OverlapMerger::append(const RawTokens& src, size_t from, size_t to) {
+void OverlapMerger::append(const RawView& src, size_t from, size_t to) {
     for (size_t i = from; i < to; ++i) {
         m_.token_ids.push_back(src.token_ids[i]);
         m_.frame_indices.push_back(src.frame_indices[i]);
@@ -107,8 +107,8 @@ void OverlapMerger::truncate(size_t n) {
     prefix_max_.resize(n);
 }
 
-void OverlapMerger::push(const RawTokens& right) {
-    const size_t nr = right.token_ids.size();
+void OverlapMerger::push(const RawView& right) {
+    const size_t nr = right.n;
     if (nr == 0) return;                       // merge.rs:19-21
     const size_t nl = m_.token_ids.size();
     if (nl == 0) { append(right, 0, nr); return; }  // merge.rs:16-18
@@ -124,10 +124,18 @@ void OverlapMerger::push(const RawTokens& right) {
                std::llabs(m_.frame_indices[li] - right.frame_indices[ri]) <= kMatchFrames;
     };
     // merge.rs:36-60: first strictly-longest diagonal run in (left, right) scan order
+    // right tokens later than every left frame + 25 cannot match either: only the others are visited
+    const int64_t left_reach = prefix_max_.back() + kMatchFrames;
+    std::vector<uint32_t>& near = near_;
+    near.clear();
+    for (size_t ri = 0; ri < nr; ++ri)
+        if (right.frame_indices[ri] <= left_reach) near.push_back((uint32_t)ri);
     size_t best = 0, bl = 0, br = 0;
     for (size_t li = lo; li < nl; ++li)
-        for (size_t ri = 0; ri < nr; ++ri) {
+        for (const uint32_t ri : near) {
             if (!match(li, ri)) continue;
+            // the tail of a run that began one step up the diagonal: that run was met first and is longer
+            if (li > lo && ri > 0 && match(li - 1, ri - 1)) continue;
             size_t a = li, b = ri, len = 0;
             while (a < nl && b < nr && match(a, b)) { ++a; ++b; ++len; }
             if (len > best) { best = len; bl = li; br = ri; }
@@ -151,7 +159,9 @@ void OverlapMerger::push(const RawTokens& right) {
         tail.confidences.push_back(m_.confidences[i]);
     }
     truncate(first_ge);
-    append(tail, 0, tail.token_ids.size());
+    append(RawView{tail.token_ids.data(), tail.frame_indices.data(), tail.durations.data(), tail.confidences.data(),
+                   tail.token_ids.size()},
+           0, tail.token_ids.size());
     for (size_t i = 0; i < nr; ++i)
         if (right.frame_indices[i] >= midpoint) append(right, i, i + 1);
 }

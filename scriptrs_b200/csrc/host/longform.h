@@ -19,17 +19,30 @@ void apply_time_offsets(RawTokens& raw, int64_t frame_offset, int64_t context_fr
 
 // Left fold of the reference's overlap merge, one window at a time, in cost proportional to the
 // overlap rather than to the transcript so far.
+// One window's token stream where it lies (no copy).
+struct RawView {
+    const uint32_t* token_ids;
+    const int64_t* frame_indices;
+    const int64_t* durations;
+    const float* confidences;
+    size_t n;
+};
+
 class OverlapMerger {
   public:
-    void push(const RawTokens& window);
+    void push(const RawView& window);
+    void push(const RawTokens& w) {
+        push(RawView{w.token_ids.data(), w.frame_indices.data(), w.durations.data(), w.confidences.data(), w.token_ids.size()});
+    }
     RawTokens take() { prefix_max_.clear(); return std::move(m_); }
     const RawTokens& merged() const { return m_; }
 
   private:
-    void append(const RawTokens& src, size_t from, size_t to);
+    void append(const RawView& src, size_t from, size_t to);
     void truncate(size_t n);
     RawTokens m_;
     std::vector<int64_t> prefix_max_;  // running maximum of m_.frame_indices
+    std::vector<uint32_t> near_;       // scratch: the right window's tokens that can match at all
 };
 
 RawTokens merge_overlapping_windows(const std::vector<RawTokens>& windows);
